@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the Mega EMA layer path: fused TimestepNorm -> EMA forward, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c4|c1] [--scaling weak|strong]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  The default
+workload is BASELINE config 4: bf16 x of shape (B=64, L=32768, D=2048), per-feature
+TimestepNorm (weight=1, bias=0, eps=1e-5, prior count 2) followed by the causal ndim=16 EMA.
+Under torchrun every rank runs the same per-rank batch on its own seed ("weak", the default)
+or a 1/N shard of the global batch ("strong"); no collective sits on the data path.
+
+Prints ONE JSON line (rank 0).  `value` = whole-job tokens/s with inputs resident in HBM,
+timed with CUDA events, max over ranks.  `e2e` = the same metric through the host-buffer API
+(pinned host input -> device -> kernel -> pinned host output inside the timed region).
+`roofline` compares algorithmic bytes (2 * D * sizeof(elem) per token) per launch with the
+measured HBM copy peak.  `cpu_baseline` times the reference's CPU path (its TimestepNorm C++
+op from oracle/_ref when built, and the oracle's restatement of its FFT convolution) on a
+bounded sample.  `--impl reference` prints that CPU measurement as its own line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, L, D, dtype)
+    "c4": (64, 32768, 2048, "bf16"),
+    "c1": (16, 4096, 1024, "bf16"),
+    "tiny": (4, 2048, 256, "bf16"),
+}
+NDIM = 16
+FALLBACK_HBM_GBS = 6650.0
+
+
+def make_ema_params(gen, dim, ndim):
+    import torch
+    alpha = torch.randn(dim, ndim, 1, generator=gen) * 0.2
+    delta = torch.randn(dim, ndim, 1, generator=gen) * 0.2
+    val = torch.ones(ndim, 1)
+    val[1::2] = -1.0
+    beta = torch.randn(dim, ndim, 1, generator=gen) * 0.02 + val
+    gamma = torch.randn(dim, ndim, generator=gen)
+    omega = torch.randn(dim, generator=gen)
+    return alpha, delta, beta, gamma, omega
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            f = [v.strip() for v in r.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except Exception:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU reference arm
+def cpu_reference_step_factory(dim, length, sample_b, sample_d):
+    """Builds the reference's CPU path on a bounded sample: TimestepNorm through the
+    reference's own C++ op (oracle/_ref) when it is built, else the oracle port, followed by
+    the EMA through the oracle's restatement of the reference's FFT convolution."""
+    import torch
+    from oracle import mega_oracle as O
+    from oracle.build_ref import load_ref
+    ref = load_ref()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(4321)
+    x = torch.randn(sample_b, length, sample_d, generator=gen).to(torch.bfloat16)
+    prm = make_ema_params(gen, sample_d, NDIM)
+    pc = torch.full((sample_b,), 2, dtype=torch.int64)
+    pm = torch.zeros(sample_b, sample_d, dtype=torch.bfloat16)
+    pv = torch.ones(sample_b, sample_d, dtype=torch.bfloat16)
+    gamma = torch.ones(sample_d, dtype=torch.bfloat16)
+    beta = torch.zeros(sample_d, dtype=torch.bfloat16)
+    kind = "reference+port" if ref is not None else "port"
+
+    def step():
+        with torch.no_grad():
+            if ref is not None:
+                xn = ref.ops.timestep_norm_fwd(x, pc, pm, pv, gamma, beta, None, 1e-5)[0]
+            else:
+                xn = O.timestep_norm(x, pc, pm.float(), pv.float(), gamma.float(), beta.float(), None)[0]
+            y = O.ema_forward_fft(xn.transpose(1, 2).contiguous(), *prm)
+        return y
+
+    return step, kind, cores
+
+
+def time_cpu(step, steps, warmup):
+    for _ in range(warmup):
+        step()
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        ts.append(time.perf_counter() - t0)
+    return sum(ts) / len(ts)
+
+
+def run_reference(args, B, L, D, dtype_name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_b, sample_d = min(B, os.cpu_count() or 1), min(D, 64)
+    step, kind, cores = cpu_reference_step_factory(D, L, sample_b, sample_d)
+    sec = time_cpu(step, max(1, args.steps), max(0, args.warmup))
+    tokens = sample_b * L * (sample_d / D)
+    val = tokens / sec
+    sample = "B=%d, L=%d, %d of %d channels per step (tokens scaled by the channel fraction)" % (
+        sample_b, L, sample_d, D)
+    line = {
+        "impl": "reference", "metric": "mega_ema_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": dtype_name,
+        "data": "synthetic",
+        "config": {"workload": workload_name(args, B, L, D, dtype_name), "ndim": NDIM,
+                   "path": "reference CPU path: TimestepNorm C++ op + torch.fft convolution"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores,
+                         "kind": "reference" if kind.startswith("reference") else "port", "sample": sample,
+                         "detail": kind},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args, B, L, D, dtype_name):
+    return "%s: TimestepNorm+MultiHeadEMA causal fwd, B=%d L=%d D=%d %s (per rank)" % (
+        args.workload, B, L, D, dtype_name)
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args, B, L, D, dtype_name):
+    import torch
+    import torch.distributed as dist
+    import fairseq_apollo_b200 as M
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.scaling == "strong":
+        assert B % world == 0
+        Bl = B // world
+    else:
+        Bl = B
+    dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    es = 2 if dtype_name == "bf16" else 4
+
+    gen = torch.Generator().manual_seed(1238 + rank)
+    prm = [t.to(dev) for t in make_ema_params(gen, D, NDIM)]
+    norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+    move = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+    with torch.no_grad():
+        for dst, src in zip((move.alpha, move.delta, move.beta, move.gamma, move.omega), prm):
+            dst.copy_(src)
+    dgen = torch.Generator(device=dev).manual_seed(1238 + rank)
+    x = torch.empty(Bl, L, D, dtype=dtype, device=dev)
+    for b in range(Bl):
+        x[b] = torch.randn(L, D, generator=dgen, device=dev, dtype=torch.float32 if L * D < (1 << 26) else dtype).to(dtype)
+    p, q, g = move.coeffs()
+    p, q = p.squeeze(-1).contiguous(), q.squeeze(-1).contiguous()
+    pc = norm.prior_count.expand(Bl).contiguous()
+    pm = torch.zeros(Bl, D, device=dev)
+    pv = torch.ones(Bl, D, device=dev)
+    gamma = torch.ones(D, device=dev)
+    beta = torch.zeros(D, device=dev)
+    y = torch.empty_like(x)
+    cnt = torch.empty(Bl, dtype=torch.int64, device=dev)
+    mo = torch.empty(Bl, D, device=dev)
+    vo = torch.empty(Bl, D, device=dev)
+    from fairseq_apollo_b200 import _lib
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream()
+
+    def step(xi=x, yi=y, bl=Bl):
+        _lib.check(lib.mega_tsn_ema_fwd(
+            xi.data_ptr(), yi.data_ptr(), None, 1 if dtype_name == "bf16" else 0, bl, L, D,
+            *xi.stride(), *yi.stride(), pc.data_ptr(), pm.data_ptr(), pv.data_ptr(), gamma.data_ptr(),
+            beta.data_ptr(), 1e-5, cnt.data_ptr(), mo.data_ptr(), vo.data_ptr(), p.data_ptr(), q.data_ptr(),
+            g.data_ptr(), move.omega.data_ptr(), NDIM, None, None, None, 0, stream.cuda_stream), "tsn_ema_fwd")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    l0 = M.launch_count()
+    barrier()
+    t0 = time.time()
+    evs[0].record(stream)
+    for i in range(args.steps):
+        step()
+        evs[i + 1].record(stream)
+    barrier()
+    t1 = time.time()
+    launches = M.launch_count() - l0
+    clocks = sampler.stop(t0, t1) if sampler else None
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_step = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    tm = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    total_ms = float(tm.item())
+    tokens_per_step = Bl * L * world
+    value = tokens_per_step * args.steps / (total_ms * 1e-3)
+
+    # ---- end-to-end through host buffers: pinned host x -> device -> kernel -> pinned host y
+    # The per-rank batch streams through in slices on three streams (H2D, compute, D2H).
+    sl = max(1, min(Bl, args.e2e_slice))
+    nsl = (Bl + sl - 1) // sl
+    hx = torch.empty(sl, L, D, dtype=dtype).pin_memory()
+    hy = torch.empty(sl, L, D, dtype=dtype).pin_memory()
+    hx.copy_(x[:sl].cpu())
+    dx = [torch.empty(sl, L, D, dtype=dtype, device=dev) for _ in range(2)]
+    dy = [torch.empty(sl, L, D, dtype=dtype, device=dev) for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    pc_s = pc[:sl].contiguous()
+
+    def e2e_step():
+        ev_in = [torch.cuda.Event() for _ in range(nsl)]
+        ev_k = [torch.cuda.Event() for _ in range(nsl)]
+        ev_out = [torch.cuda.Event() for _ in range(nsl)]
+        for i in range(nsl):
+            k = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_k[i - 2])          # buffer k consumed by the kernel
+                dx[k].copy_(hx, non_blocking=True)
+                ev_in[i].record(s_in)
+            stream.wait_event(ev_in[i])
+            if i >= 2:
+                stream.wait_event(ev_out[i - 2])          # output buffer k drained
+            _lib.check(lib.mega_tsn_ema_fwd(
+                dx[k].data_ptr(), dy[k].data_ptr(), None, 1 if dtype_name == "bf16" else 0, sl, L, D,
+                *dx[k].stride(), *dy[k].stride(), pc_s.data_ptr(), pm.data_ptr(), pv.data_ptr(), gamma.data_ptr(),
+                beta.data_ptr(), 1e-5, cnt.data_ptr(), mo.data_ptr(), vo.data_ptr(), p.data_ptr(), q.data_ptr(),
+                g.data_ptr(), move.omega.data_ptr(), NDIM, None, None, None, 0, stream.cuda_stream), "tsn_ema_fwd")
+            ev_k[i].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[i])
+                hy.copy_(dy[k], non_blocking=True)
+                ev_out[i].record(s_out)
+        stream.wait_stream(s_out)
+        stream.wait_stream(s_in)
+
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    em = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(em, op=dist.ReduceOp.MAX)
+    e2e_tokens = nsl * sl * L * world * e2e_steps
+    e2e_val = e2e_tokens / (float(em.item()) * 1e-3)
+    bytes_dir = nsl * sl * L * D * es
+
+    # ---- one verification gather (outside every timed region): checksum of a small slice
+    chk = y[0, :64].float().sum().reshape(1)
+    if world > 1:
+        outs = [torch.empty_like(chk) for _ in range(world)]
+        dist.all_gather(outs, chk)
+
+    if rank == 0:
+        peak, peak_kind = hbm_peak()
+        kern_ms = sum(per_step) / len(per_step)
+        alg_bytes = 2.0 * D * es * Bl * L
+        achieved = alg_bytes / (kern_ms * 1e-3) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            sample_b, sample_d = min(Bl, os.cpu_count() or 1), min(D, 64)
+            cstep, kind, cores = cpu_reference_step_factory(D, L, sample_b, sample_d)
+            sec = time_cpu(cstep, 3, 1)
+            cpu = {"value": sample_b * L * (sample_d / D) / sec, "unit": "tokens/s", "cores": cores,
+                   "kind": "reference" if kind.startswith("reference") else "port", "detail": kind,
+                   "sample": "B=%d, L=%d, %d of %d channels, 3 timed passes (tokens scaled by the channel fraction)"
+                             % (sample_b, L, sample_d, D)}
+        line = {
+            "metric": "mega_ema_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": dtype_name,
+            "data": "synthetic",
+            "config": {"workload": workload_name(args, Bl, L, D, dtype_name), "ndim": NDIM,
+                       "global_batch": Bl * world, "l2": "inputs (%.1f GiB per rank) exceed the 126 MB L2"
+                       % (Bl * L * D * es / 2**30), "parallelism": "batch shards, no data-path collective"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "tsn_ema fused forward", "algorithmic_bytes_per_launch": alg_bytes,
+                         "kernel_ms": kern_ms},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_dir,
+                    "d2h_bytes_per_step": bytes_dir, "steps": e2e_steps,
+                    "note": "pinned host slices of %d sequences streamed on 3 streams" % sl},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
+    ap.add_argument("--e2e-slice", type=int, default=8)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    B, L, D, dtype_name = WORKLOADS[args.workload]
+    if args.batch:
+        B = args.batch
+    if args.impl == "reference":
+        run_reference(args, B, L, D, dtype_name)
+    else:
+        run_ours(args, B, L, D, dtype_name)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,8 @@
+"""mega_b200: Mega's EMA layer, TimestepNorm and SequenceNorm on hand-written sm_100a CUDA
+kernels behind the reference's module API.  Import name: ``fairseq_apollo_b200``."""
+from . import ops
+from ._lib import LIB_PATH, MegaError, launch_count
+from .modules import MultiHeadEMA, SequenceNorm, TimestepNorm, timestep_norm_ema
+
+__all__ = ["ops", "MultiHeadEMA", "TimestepNorm", "SequenceNorm", "timestep_norm_ema",
+           "MegaError", "launch_count", "LIB_PATH"]

@@ -1,0 +1,81 @@
+"""ctypes binding of libmega_b200.so (declared in include/mega_b200.h).
+
+There is no CPU or PyTorch fallback: if the shared library is missing, loading raises, and
+every op raises when handed a non-CUDA tensor.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmega_b200.so")
+
+c_p = ctypes.c_void_p
+c_i = ctypes.c_int
+c_u = ctypes.c_uint
+c_l = ctypes.c_int64
+c_d = ctypes.c_double
+
+# name -> argument types, in the order of include/mega_b200.h
+SIGNATURES = {
+    "mega_ema_coeffs": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p],
+    "mega_ema_kernel": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p],
+    "mega_ema_bias": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p, c_p],
+    "mega_ema_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p, c_p, c_i,
+                     c_p, c_p, c_p, c_u, c_i, c_p],
+    "mega_ema_step": [c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_u, c_p],
+    "mega_timestep_norm_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                               c_p, c_p, c_p, c_i, c_d, c_p, c_p, c_p, c_p],
+    "mega_sequence_norm_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                               c_i, c_d, c_p, c_p, c_p, c_p],
+    "mega_tsn_ema_fwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                         c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
+    "mega_gate_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
+    "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
+    "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
+}
+OTHER = {
+    "mega_status_string": ([c_i], ctypes.c_char_p),
+    "mega_last_cuda_error": ([], ctypes.c_char_p),
+    "mega_abi_version": ([], c_i),
+    "mega_launch_count": ([], ctypes.c_uint64),
+}
+
+_lib = None
+
+
+class MegaError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded library; raises if it was never built (python fairseq-apollo_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "libmega_b200.so is missing at %s: build it with `python fairseq-apollo_b200/build.py` "
+                "(there is no CPU fallback)" % LIB_PATH)
+        l = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            f = getattr(l, name)
+            f.argtypes = args
+            f.restype = c_i
+        for name, (args, res) in OTHER.items():
+            f = getattr(l, name)
+            f.argtypes = args
+            f.restype = res
+        _lib = l
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        l = lib()
+        msg = l.mega_status_string(status).decode()
+        if status == 8:
+            msg += " (%s)" % l.mega_last_cuda_error().decode()
+        raise MegaError("%s: %s" % (what, msg))
+
+
+def launch_count():
+    return int(lib().mega_launch_count())

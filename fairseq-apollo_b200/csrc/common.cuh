@@ -1,0 +1,89 @@
+// Shared device/host helpers for the mega_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "mega_b200.h"
+
+namespace mega {
+
+// ---- launch bookkeeping ---------------------------------------------------
+extern std::atomic<uint64_t> g_launches;
+extern thread_local char g_cuda_err[256];
+int check_launch(const char* what);
+
+template <typename... KArgs, typename... Args>
+static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
+                          Args... args) {
+  kernel<<<grid, block, smem, (cudaStream_t)stream>>>(static_cast<KArgs>(args)...);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// ---- element I/O ------------------------------------------------------------
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld(const __nv_bfloat16* p) {
+    return __bfloat162float(__ldg(p));
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+  }
+};
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ float ld(const __half* p) { return __half2float(__ldg(p)); }
+  static __device__ __forceinline__ void st(__half* p, float v) { *p = __float2half_rn(v); }
+};
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float siluf_(float v) { return v / (1.0f + __expf(-v)); }
+
+static inline int elem_size(int dtype) { return dtype == MEGA_F32 ? 4 : 2; }
+
+static inline bool valid_dtype(int dtype) {
+  return dtype == MEGA_F32 || dtype == MEGA_BF16 || dtype == MEGA_F16;
+}
+
+static inline bool aligned_to(const void* p, size_t a) {
+  return (reinterpret_cast<uintptr_t>(p) % a) == 0;
+}
+
+static inline int next_pow2_ndim(int n) {
+  int v = 2;
+  while (v < n) v <<= 1;
+  return v;
+}
+
+// Dispatch helpers: call f.template operator()<T>() for the activation dtype.
+#define MEGA_DISPATCH_DTYPE(dtype, ...)                 \
+  switch (dtype) {                                      \
+    case MEGA_F32: { using T = float; __VA_ARGS__; } break;           \
+    case MEGA_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;  \
+    case MEGA_F16: { using T = __half; __VA_ARGS__; } break;          \
+    default: return MEGA_ERR_DTYPE;                     \
+  }
+
+#define MEGA_DISPATCH_NP(np, ...)                       \
+  switch (np) {                                         \
+    case 2: { constexpr int NP = 2; __VA_ARGS__; } break;   \
+    case 4: { constexpr int NP = 4; __VA_ARGS__; } break;   \
+    case 8: { constexpr int NP = 8; __VA_ARGS__; } break;   \
+    case 16: { constexpr int NP = 16; __VA_ARGS__; } break; \
+    case 32: { constexpr int NP = 32; __VA_ARGS__; } break; \
+    default: return MEGA_ERR_NDIM;                      \
+  }
+
+}  // namespace mega

@@ -1,0 +1,151 @@
+// Fused per-feature TimestepNorm -> causal EMA: one pass over x, one write of y.
+//
+// Generic variant: one thread per (batch, channel), sequential over time, so every
+// per-channel quantity (Welford state, pole states) lives in registers.  Works for any
+// strides; coalesced when the channel stride is 1.
+#include "common.cuh"
+
+namespace mega {
+
+struct FusedArgs {
+  const void* x;
+  void* y;
+  void* xn;
+  int B, L, D, N;
+  long long xsb, xsl, xsd, ysb, ysl, ysd;
+  const long long* prev_count;
+  const float *prev_mean, *prev_var, *gamma, *beta;
+  float eps;
+  long long* count_out;
+  float *mean_out, *var_out;
+  const float *p, *q, *g, *omega;
+  const unsigned char* mask;
+  const float* h_in;
+  float* h_out;
+  int silu;
+};
+
+template <typename T, int NP, bool kState>
+__global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
+  long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)a.B * a.D) return;
+  const int d = (int)(gid % a.D);
+  const int b = (int)(gid / a.D);
+  float q[NP], c[NP], s[NP], pp[kState ? NP : 1];
+#pragma unroll
+  for (int n = 0; n < NP; ++n) {
+    float pn = 0.f, qn = 0.f, gn = 0.f;
+    if (n < a.N) {
+      pn = __ldg(a.p + (size_t)d * a.N + n);
+      qn = __ldg(a.q + (size_t)d * a.N + n);
+      gn = __ldg(a.g + (size_t)d * a.N + n);
+    }
+    q[n] = qn;
+    if (kState) {
+      c[n] = gn; pp[n] = pn;
+      s[n] = (a.h_in != nullptr && n < a.N) ? __ldg(a.h_in + (size_t)gid * a.N + n) : 0.f;
+    } else {
+      c[n] = pn * gn; s[n] = 0.f;
+    }
+  }
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
+  T* np_ = a.xn ? reinterpret_cast<T*>(a.xn) + b * a.ysb + d * a.ysd : nullptr;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  long long cnt = a.prev_count[b];
+  float mean = a.prev_mean[gid], var = a.prev_var[gid];
+  const float w = __ldg(a.gamma + d), bb = __ldg(a.beta + d), om = __ldg(a.omega + d);
+  constexpr int U = 8;
+  for (int t0 = 0; t0 < a.L; t0 += U) {
+    float xv[U];
+    bool mk[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u;
+      xv[u] = 0.f; mk[u] = true;
+      if (t < a.L) {
+        xv[u] = Elem<T>::ld(xp + t * a.xsl);
+        mk[u] = mp != nullptr && mp[t] != 0;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u;
+      if (t < a.L) {
+        float m1, m2;
+        const float coef = __frcp_rn((float)(cnt + 1));
+        const float d1 = xv[u] - mean;
+        m1 = fmaf(coef, d1, mean);
+        const float d2 = fmaf(d1, xv[u] - m1, -var);
+        m2 = fmaf(coef, d2, var);
+        const float rstd = rsqrtf(m2 + a.eps);
+        const float xn = mk[u] ? 0.f : fmaf((xv[u] - m1) * rstd, w, bb);
+        if (!mk[u]) { mean = m1; var = m2; ++cnt; }
+        if (np_) Elem<T>::st(np_ + t * a.ysl, xn);
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < NP; n += 2) {
+          if (kState) {
+            s[n] = fmaf(q[n], s[n], pp[n] * xn);
+            s[n + 1] = fmaf(q[n + 1], s[n + 1], pp[n + 1] * xn);
+          } else {
+            s[n] = fmaf(q[n], s[n], xn);
+            s[n + 1] = fmaf(q[n + 1], s[n + 1], xn);
+          }
+          a0 = fmaf(c[n], s[n], a0);
+          a1 = fmaf(c[n + 1], s[n + 1], a1);
+        }
+        float v = fmaf(om, xn, a0 + a1);
+        if (a.silu) v = siluf_(v);
+        Elem<T>::st(yp + t * a.ysl, v);
+      }
+    }
+  }
+  a.mean_out[gid] = mean;
+  a.var_out[gid] = var;
+  if (d == 0) a.count_out[b] = cnt;
+  if (kState && a.h_out) {
+#pragma unroll
+    for (int n = 0; n < NP; ++n)
+      if (n < a.N) a.h_out[(size_t)gid * a.N + n] = s[n];
+  }
+}
+
+}  // namespace mega
+
+using namespace mega;
+
+extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D,
+                                int64_t xsb, int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                                const float* gamma, const float* beta, double eps, int64_t* count_out,
+                                float* mean_out, float* var_out, const float* p, const float* q,
+                                const float* gamma_hat, const float* omega, int N, const uint8_t* pad_mask,
+                                const float* h_in, float* h_out, unsigned flags, mega_stream_t stream) {
+  if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
+      !var_out || !p || !q || !gamma_hat || !omega)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (flags & MEGA_EMA_BIDIRECTIONAL) return MEGA_ERR_UNSUPPORTED;
+  if (!aligned_to(x, elem_size(dtype)) || !aligned_to(y, elem_size(dtype)) ||
+      (xn_out && !aligned_to(xn_out, elem_size(dtype))))
+    return MEGA_ERR_ALIGN;
+  FusedArgs a{};
+  a.x = x; a.y = y; a.xn = xn_out; a.B = B; a.L = L; a.D = D; a.N = N;
+  a.xsb = xsb; a.xsl = xsl; a.xsd = xsd; a.ysb = ysb; a.ysl = ysl; a.ysd = ysd;
+  a.prev_count = (const long long*)prev_count; a.prev_mean = prev_mean; a.prev_var = prev_var;
+  a.gamma = gamma; a.beta = beta; a.eps = (float)eps;
+  a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
+  a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask; a.h_in = h_in; a.h_out = h_out;
+  a.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  const int np = next_pow2_ndim(N);
+  const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+  const bool state = h_in || h_out;
+  MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, {
+    if (state) launch(tsn_ema_rows_kernel<T, NP, true>, grid, 128, 0, stream, a);
+    else launch(tsn_ema_rows_kernel<T, NP, false>, grid, 128, 0, stream, a);
+  }));
+  return check_launch("tsn_ema_fwd");
+}

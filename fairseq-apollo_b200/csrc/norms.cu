@@ -1,0 +1,388 @@
+// TimestepNorm (plain + grouped) and SequenceNorm (plain + grouped, any memory order).
+//
+// TimestepNorm is a causal cumulative normalisation: the statistics at step t are the Welford
+// moments of the unmasked prefix (plus a prior that acts as prev_count pseudo-samples).
+// SequenceNorm normalises with the masked moments of the whole sequence.
+#include "common.cuh"
+
+namespace mega {
+
+struct TsnArgs {
+  const void* x;
+  void* y;
+  int B, L, D, G;
+  long long xsb, xsl, xsd, ysb, ysl, ysd;
+  const long long* prev_count;
+  const float *prev_mean, *prev_var, *gamma, *beta;
+  const unsigned char* mask;
+  float eps;
+  long long* count_out;
+  float *mean_out, *var_out;
+};
+
+// Welford step with the update rule of the reference (fairseq/csrc/utils.h:56-65).
+__device__ __forceinline__ void welford_step(float coef, float x, float mean, float var, float& m1,
+                                             float& m2) {
+  const float d1 = x - mean;
+  m1 = fmaf(coef, d1, mean);
+  const float d2 = fmaf(d1, x - m1, -var);
+  m2 = fmaf(coef, d2, var);
+}
+
+// One thread per (batch, feature), feature fastest; sequential over time.
+template <typename T>
+__global__ void __launch_bounds__(128) tsn_plain_kernel(TsnArgs a) {
+  long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)a.B * a.D) return;
+  const int d = (int)(gid % a.D);
+  const int b = (int)(gid / a.D);
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  long long cnt = a.prev_count[b];
+  float mean = a.prev_mean[gid], var = a.prev_var[gid];
+  const float w = __ldg(a.gamma + d), bb = __ldg(a.beta + d);
+  constexpr int U = 8;
+  for (int t0 = 0; t0 < a.L; t0 += U) {
+    float xv[U];
+    bool mk[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u;
+      xv[u] = 0.f; mk[u] = true;
+      if (t < a.L) {
+        xv[u] = Elem<T>::ld(xp + t * a.xsl);
+        mk[u] = mp != nullptr && mp[t] != 0;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int t = t0 + u;
+      if (t < a.L) {
+        float m1, m2;
+        const float coef = __frcp_rn((float)(cnt + 1));
+        welford_step(coef, xv[u], mean, var, m1, m2);
+        const float rstd = rsqrtf(m2 + a.eps);
+        const float out = mk[u] ? 0.f : fmaf((xv[u] - m1) * rstd, w, bb);
+        Elem<T>::st(yp + t * a.ysl, out);
+        if (!mk[u]) { mean = m1; var = m2; ++cnt; }
+      }
+    }
+  }
+  a.mean_out[gid] = mean;
+  a.var_out[gid] = var;
+  if (d == 0) a.count_out[b] = cnt;
+}
+
+// Grouped: one warp per (batch, group); per step the group's D/G features are reduced to
+// (mean, var), combined into the running state with weight 1, then normalised.
+template <typename T>
+__global__ void __launch_bounds__(128) tsn_group_kernel(TsnArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= (long long)a.B * a.G) return;
+  const int g = (int)(wid % a.G);
+  const int b = (int)(wid / a.G);
+  const int gs = a.D / a.G;
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + (long long)g * gs * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + (long long)g * gs * a.ysd;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  long long cnt = a.prev_count[b];
+  float mean = a.prev_mean[wid], var = a.prev_var[wid];
+  const float inv_gs = 1.0f / (float)gs;
+  for (int t = 0; t < a.L; ++t) {
+    const T* xr = xp + t * a.xsl;
+    float s = 0.f;
+    for (int k = lane; k < gs; k += 32) s += Elem<T>::ld(xr + k * a.xsd);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float gm = s * inv_gs;
+    float v = 0.f;
+    for (int k = lane; k < gs; k += 32) {
+      const float dlt = Elem<T>::ld(xr + k * a.xsd) - gm;
+      v = fmaf(dlt, dlt, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const float gv = v * inv_gs;
+    // WelfordCombine(cnt, mean, var, 1, gm, gv)  (fairseq/csrc/utils.h:67-76)
+    const float m0 = (float)(cnt + 1);
+    const float c1 = (float)cnt / m0, c2 = 1.0f / m0;
+    const float dl = gm - mean;
+    const float m1 = c1 * mean + c2 * gm;
+    const float m2 = c1 * var + c2 * gv + (c1 * dl) * (c2 * dl);
+    const float rstd = rsqrtf(m2 + a.eps);
+    const bool mk = mp != nullptr && mp[t] != 0;
+    T* yr = yp + t * a.ysl;
+    for (int k = lane; k < gs; k += 32) {
+      const int f = g * gs + k;
+      const float xv = Elem<T>::ld(xr + k * a.xsd);
+      const float out = mk ? 0.f : fmaf((xv - m1) * rstd, __ldg(a.gamma + f), __ldg(a.beta + f));
+      Elem<T>::st(yr + k * a.ysd, out);
+    }
+    if (!mk) { mean = m1; var = m2; ++cnt; }
+  }
+  if (lane == 0) {
+    a.mean_out[wid] = mean;
+    a.var_out[wid] = var;
+    if (g == 0) a.count_out[b] = cnt;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SequenceNorm
+// ---------------------------------------------------------------------------
+struct SqnArgs {
+  const void* x;
+  void* y;
+  int B, D, L, G;
+  long long xsb, xsd, xsl, ysb, ysd, ysl;
+  const float *gamma, *beta;
+  const unsigned char* mask;
+  float eps;
+  long long* count_out;
+  float *mean_out, *rstd_out;
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = 0.f;
+  const int nw = (blockDim.x + 31) >> 5;
+  for (int i = 0; i < nw; ++i) r += red[i];
+  return r;
+}
+
+// One CTA per (batch, group): the group's gs channels x L positions.  Two reduction passes
+// (mean, then centred second moment) and a normalisation pass; when the segment fits the
+// dynamic shared memory it is cached there after the first read.
+template <typename T>
+__global__ void __launch_bounds__(256) sqn_segment_kernel(SqnArgs a, int cache_elems) {
+  extern __shared__ float cache[];
+  __shared__ float red[8];
+  const int g = blockIdx.x % a.G;
+  const int b = blockIdx.x / a.G;
+  const int gs = a.D / a.G;
+  const long long n = (long long)gs * a.L;
+  const bool len_fast = a.xsl <= a.xsd;  // iterate the contiguous axis fastest
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + (long long)g * gs * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + (long long)g * gs * a.ysd;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  const bool cached = n <= cache_elems;
+
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const int j = len_fast ? (int)(i / a.L) : (int)(i % gs);
+    const int t = len_fast ? (int)(i % a.L) : (int)(i / gs);
+    const float xv = Elem<T>::ld(xp + j * a.xsd + t * a.xsl);
+    if (cached) cache[i] = xv;
+    const bool mk = mp != nullptr && mp[t] != 0;
+    if (!mk) s += xv;
+  }
+  __shared__ int valid_steps;
+  if (threadIdx.x == 0) valid_steps = 0;
+  __syncthreads();
+  int c = 0;
+  for (int t = threadIdx.x; t < a.L; t += blockDim.x) c += (mp == nullptr || mp[t] == 0) ? 1 : 0;
+  if (c) atomicAdd(&valid_steps, c);
+  __syncthreads();
+  const float tot = (float)valid_steps * (float)gs;
+  const float sum = block_sum(s, red);
+  const float mean = tot > 0.f ? sum / tot : 0.f;
+  float v = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const int j = len_fast ? (int)(i / a.L) : (int)(i % gs);
+    const int t = len_fast ? (int)(i % a.L) : (int)(i / gs);
+    const float xv = cached ? cache[i] : Elem<T>::ld(xp + j * a.xsd + t * a.xsl);
+    const bool mk = mp != nullptr && mp[t] != 0;
+    if (!mk) { const float dl = xv - mean; v = fmaf(dl, dl, v); }
+  }
+  const float var = tot > 0.f ? block_sum(v, red) / tot : 0.f;
+  const float rstd = rsqrtf(var + a.eps);
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const int j = len_fast ? (int)(i / a.L) : (int)(i % gs);
+    const int t = len_fast ? (int)(i % a.L) : (int)(i / gs);
+    const float xv = cached ? cache[i] : Elem<T>::ld(xp + j * a.xsd + t * a.xsl);
+    const bool mk = mp != nullptr && mp[t] != 0;
+    const int f = g * gs + j;
+    const float out = mk ? 0.f : fmaf((xv - mean) * rstd, __ldg(a.gamma + f), __ldg(a.beta + f));
+    Elem<T>::st(yp + j * a.ysd + t * a.ysl, out);
+  }
+  if (threadIdx.x == 0) {
+    a.mean_out[blockIdx.x] = mean;
+    a.rstd_out[blockIdx.x] = rstd;
+    if (g == 0) a.count_out[b] = (long long)valid_steps;
+  }
+}
+
+// Plain SequenceNorm on channel-contiguous memory: one thread per (batch, channel) column,
+// masked Welford over time, then a second sweep that normalises.
+template <typename T>
+__global__ void __launch_bounds__(128) sqn_column_kernel(SqnArgs a) {
+  long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)a.B * a.D) return;
+  const int d = (int)(gid % a.D);
+  const int b = (int)(gid / a.D);
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  long long cnt = 0;
+  float mean = 0.f, var = 0.f;
+  for (int t = 0; t < a.L; ++t) {
+    const bool mk = mp != nullptr && mp[t] != 0;
+    if (!mk) {
+      const float xv = Elem<T>::ld(xp + t * a.xsl);
+      float m1, m2;
+      welford_step(__frcp_rn((float)(cnt + 1)), xv, mean, var, m1, m2);
+      mean = m1; var = m2; ++cnt;
+    }
+  }
+  const float rstd = rsqrtf(var + a.eps);
+  const float w = __ldg(a.gamma + d), bb = __ldg(a.beta + d);
+  for (int t = 0; t < a.L; ++t) {
+    const bool mk = mp != nullptr && mp[t] != 0;
+    const float xv = Elem<T>::ld(xp + t * a.xsl);
+    Elem<T>::st(yp + t * a.ysl, mk ? 0.f : fmaf((xv - mean) * rstd, w, bb));
+  }
+  a.mean_out[gid] = mean;
+  a.rstd_out[gid] = rstd;
+  if (d == 0) a.count_out[b] = cnt;
+}
+
+// ---------------------------------------------------------------------------
+// gates
+// ---------------------------------------------------------------------------
+template <typename T, int OP>
+__global__ void gate_kernel(const T* a, long long lda, const T* b, long long ldb, const T* c, long long ldc,
+                            const T* d, long long ldd, T* y, long long ldy, long long rows, int cols) {
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols;
+    const int col = (int)(i % cols);
+    float out;
+    if (OP == 0) {  // silu(a [+ b])
+      float v = Elem<T>::ld(a + r * lda + col);
+      if (b) v += Elem<T>::ld(b + r * ldb + col);
+      out = siluf_(v);
+    } else if (OP == 1) {  // a * silu(b)
+      out = Elem<T>::ld(a + r * lda + col) * siluf_(Elem<T>::ld(b + r * ldb + col));
+    } else {  // a = residual, b = u, c = hx, d = h_lin
+      const float res = Elem<T>::ld(a + r * lda + col);
+      const float u = sigmoidf_(Elem<T>::ld(b + r * ldb + col));
+      const float h = siluf_(Elem<T>::ld(c + r * ldc + col) + Elem<T>::ld(d + r * ldd + col));
+      out = fmaf(u, h - res, res);
+    }
+    Elem<T>::st(y + r * ldy + col, out);
+  }
+}
+
+}  // namespace mega
+
+using namespace mega;
+
+extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb,
+                                      int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                      const int64_t* prev_count, const float* prev_mean,
+                                      const float* prev_var, const float* gamma, const float* beta,
+                                      const uint8_t* pad_mask, int num_groups, double eps,
+                                      int64_t* count_out, float* mean_out, float* var_out,
+                                      mega_stream_t stream) {
+  if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
+      !var_out)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  const int G = (num_groups <= 0 || num_groups == D) ? D : num_groups;
+  if (D % G != 0) return MEGA_ERR_SHAPE;
+  if (!aligned_to(x, elem_size(dtype)) || !aligned_to(y, elem_size(dtype))) return MEGA_ERR_ALIGN;
+  TsnArgs a{};
+  a.x = x; a.y = y; a.B = B; a.L = L; a.D = D; a.G = G;
+  a.xsb = xsb; a.xsl = xsl; a.xsd = xsd; a.ysb = ysb; a.ysl = ysl; a.ysd = ysd;
+  a.prev_count = (const long long*)prev_count; a.prev_mean = prev_mean; a.prev_var = prev_var;
+  a.gamma = gamma; a.beta = beta; a.mask = pad_mask; a.eps = (float)eps;
+  a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
+  if (G == D) {
+    const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+    MEGA_DISPATCH_DTYPE(dtype, launch(tsn_plain_kernel<T>, grid, 128, 0, stream, a));
+  } else {
+    const unsigned grid = (unsigned)(((long long)B * G * 32 + 127) / 128);
+    MEGA_DISPATCH_DTYPE(dtype, launch(tsn_group_kernel<T>, grid, 128, 0, stream, a));
+  }
+  return check_launch("timestep_norm_fwd");
+}
+
+extern "C" int mega_sequence_norm_fwd(const void* x, void* y, int dtype, int B, int D, int L, int64_t xsb,
+                                      int64_t xsd, int64_t xsl, int64_t ysb, int64_t ysd, int64_t ysl,
+                                      const float* gamma, const float* beta, const uint8_t* pad_mask,
+                                      int num_groups, double eps, int64_t* count_out, float* mean_out,
+                                      float* rstd_out, mega_stream_t stream) {
+  if (!x || !y || !gamma || !beta || !count_out || !mean_out || !rstd_out) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  const int G = (num_groups <= 0 || num_groups == D) ? D : num_groups;
+  if (D % G != 0) return MEGA_ERR_SHAPE;
+  if (!aligned_to(x, elem_size(dtype)) || !aligned_to(y, elem_size(dtype))) return MEGA_ERR_ALIGN;
+  SqnArgs a{};
+  a.x = x; a.y = y; a.B = B; a.D = D; a.L = L; a.G = G;
+  a.xsb = xsb; a.xsd = xsd; a.xsl = xsl; a.ysb = ysb; a.ysd = ysd; a.ysl = ysl;
+  a.gamma = gamma; a.beta = beta; a.mask = pad_mask; a.eps = (float)eps;
+  a.count_out = (long long*)count_out; a.mean_out = mean_out; a.rstd_out = rstd_out;
+  if (G == D && xsd == 1 && xsl != 1) {
+    const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+    MEGA_DISPATCH_DTYPE(dtype, launch(sqn_column_kernel<T>, grid, 128, 0, stream, a));
+  } else {
+    if ((long long)B * G > 0x7fffffffLL) return MEGA_ERR_SHAPE;
+    const long long n = (long long)(D / G) * L;
+    const int cap = 40 * 1024 / 4;  // fits the default dynamic shared-memory limit
+    const int cache_elems = n <= cap ? (int)n : 0;
+    MEGA_DISPATCH_DTYPE(dtype, launch(sqn_segment_kernel<T>, (unsigned)(B * G), 256,
+                                      (size_t)cache_elems * sizeof(float), stream, a, cache_elems));
+  }
+  return check_launch("sequence_norm_fwd");
+}
+
+static int gate_common(int op, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+                       int64_t ldc, const void* d, int64_t ldd, void* y, int64_t ldy, int dtype,
+                       int64_t rows, int cols, mega_stream_t stream) {
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (rows <= 0 || cols <= 0) return MEGA_ERR_SHAPE;
+  const long long n = rows * cols;
+  const unsigned grid = (unsigned)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  MEGA_DISPATCH_DTYPE(dtype, {
+    if (op == 0)
+      launch(gate_kernel<T, 0>, grid, 256, 0, stream, (const T*)a, lda, (const T*)b, ldb, (const T*)c, ldc,
+             (const T*)d, ldd, (T*)y, ldy, rows, cols);
+    else if (op == 1)
+      launch(gate_kernel<T, 1>, grid, 256, 0, stream, (const T*)a, lda, (const T*)b, ldb, (const T*)c, ldc,
+             (const T*)d, ldd, (T*)y, ldy, rows, cols);
+    else
+      launch(gate_kernel<T, 2>, grid, 256, 0, stream, (const T*)a, lda, (const T*)b, ldb, (const T*)c, ldc,
+             (const T*)d, ldd, (T*)y, ldy, rows, cols);
+  });
+  return check_launch("gate");
+}
+
+extern "C" int mega_gate_silu(const void* a, int64_t ld_a, const void* b, int64_t ld_b, void* y,
+                              int64_t ld_y, int dtype, int64_t rows, int cols, mega_stream_t stream) {
+  if (!a || !y) return MEGA_ERR_NULL;
+  return gate_common(0, a, ld_a, b, ld_b, nullptr, 0, nullptr, 0, y, ld_y, dtype, rows, cols, stream);
+}
+
+extern "C" int mega_gate_mul_silu(const void* a, int64_t ld_a, const void* r, int64_t ld_r, void* y,
+                                  int64_t ld_y, int dtype, int64_t rows, int cols, mega_stream_t stream) {
+  if (!a || !r || !y) return MEGA_ERR_NULL;
+  return gate_common(1, a, ld_a, r, ld_r, nullptr, 0, nullptr, 0, y, ld_y, dtype, rows, cols, stream);
+}
+
+extern "C" int mega_gate_output(const void* residual, int64_t ld_res, const void* u, int64_t ld_u,
+                                const void* hx, int64_t ld_hx, const void* h_lin, int64_t ld_h, void* out,
+                                int64_t ld_out, int dtype, int64_t rows, int cols, mega_stream_t stream) {
+  if (!residual || !u || !hx || !h_lin || !out) return MEGA_ERR_NULL;
+  return gate_common(2, residual, ld_res, u, ld_u, hx, ld_hx, h_lin, ld_h, out, ld_out, dtype, rows, cols,
+                     stream);
+}

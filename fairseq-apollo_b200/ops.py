@@ -1,0 +1,309 @@
+"""Operator level of the package: torch tensors in, torch tensors out, every op a call into
+libmega_b200.so on the current CUDA stream.
+
+The functions mirror the operator surface the reference's Python wrappers expect from
+``fairseq.mega2_extension.ops`` (fairseq/modules/fused_ops/*.py,
+fairseq/modules/norm_layer/*.py), with the FFT convolution, its bias and the hidden-state
+update folded into one ``ema_forward``.  Outputs are allocated here with torch (device
+memory plumbing); the library itself allocates nothing.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+F32, BF16, F16 = 0, 1, 2
+EMA_BIDIRECTIONAL, EMA_NO_SHIFT, EMA_SILU = 1, 2, 4
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError("mega_b200 supports float32, bfloat16 and float16 activations, got %s" % t.dtype)
+
+
+def _cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("mega_b200 ops run on CUDA tensors only (there is no CPU fallback)")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _f32c(t):
+    """fp32, contiguous (parameters, statistics, states are tiny)."""
+    if t is None:
+        return None
+    t = t.detach()
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t.contiguous()
+
+
+def _mask_u8(mask, bsz, length):
+    if mask is None:
+        return None
+    if mask.shape != (bsz, length):
+        raise ValueError("padding_mask must be (batch, length) = (%d, %d), got %s" % (bsz, length, tuple(mask.shape)))
+    if mask.dtype == torch.bool:
+        return mask.contiguous().view(torch.uint8)
+    return (mask != 0).contiguous().view(torch.uint8)
+
+
+# ----------------------------------------------------------------------------- EMA
+def ema_coeffs(alpha, delta, beta, gamma):
+    """(p, q, gamma_hat), each (K, N) fp32 — MultiHeadEMA._calc_coeffs."""
+    _cuda(alpha, delta, beta, gamma)
+    k, n = alpha.shape[0], alpha.shape[1]
+    dt = alpha.dtype
+    args = [t.detach().to(dt).contiguous() for t in (alpha, delta, beta, gamma)]
+    p = torch.empty(k, n, device=alpha.device, dtype=torch.float32)
+    q = torch.empty_like(p)
+    g = torch.empty_like(p)
+    with torch.cuda.device(alpha.device):
+        _lib.check(_lib.lib().mega_ema_coeffs(*[a.data_ptr() for a in args], _dt(args[0]), k, n,
+                                              p.data_ptr(), q.data_ptr(), g.data_ptr(), _stream()), "ema_coeffs")
+    return p, q, g
+
+
+def ema_kernel(p, q, g, length):
+    """k (K, L) fp32: the materialised convolution kernel."""
+    _cuda(p, q, g)
+    p, q, g = _f32c(p), _f32c(q), _f32c(g)
+    k, n = p.shape
+    out = torch.empty(k, length, device=p.device, dtype=torch.float32)
+    with torch.cuda.device(p.device):
+        _lib.check(_lib.lib().mega_ema_kernel(p.data_ptr(), q.data_ptr(), g.data_ptr(), k, n, length,
+                                              out.data_ptr(), _stream()), "ema_kernel")
+    return out
+
+
+def ema_bias(q, g, h, length):
+    """(B, D, L) fp32 output term of a carried state h (B, D, N)."""
+    _cuda(q, g, h)
+    q, g, h = _f32c(q), _f32c(g), _f32c(h)
+    b, d, n = h.shape
+    out = torch.empty(b, d, length, device=h.device, dtype=torch.float32)
+    with torch.cuda.device(h.device):
+        _lib.check(_lib.lib().mega_ema_bias(q.data_ptr(), g.data_ptr(), h.data_ptr(), b, d, n, length,
+                                            out.data_ptr(), _stream()), "ema_bias")
+    return out
+
+
+def ema_forward(x, p, q, g, omega, padding_mask=None, h_in=None, want_state=False,
+                bidirectional=False, shift=True, truncation=None, silu=False, out=None):
+    """EMA layer forward on x (B, D, L) with any strides (a transposed view of (B, L, D)
+    memory is addressed in place).  Returns y shaped and strided like x, and the new state
+    (B, D, N) when ``want_state``."""
+    _cuda(x, p, q, g, omega, padding_mask, h_in)
+    bsz, dim, length = x.shape
+    p, q, g, omega = _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
+    n = p.shape[1]
+    if p.shape[0] != (2 * dim if bidirectional else dim):
+        raise ValueError("coefficient rows %d do not match embed_dim %d" % (p.shape[0], dim))
+    mask = _mask_u8(padding_mask, bsz, length)
+    if out is None:
+        out = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
+            if _dense(x) else torch.empty_like(x, memory_format=torch.contiguous_format)
+    h_in = _f32c(h_in)
+    h_out = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32) if want_state else None
+    flags = (EMA_BIDIRECTIONAL if bidirectional else 0) | (0 if shift else EMA_NO_SHIFT) | (EMA_SILU if silu else 0)
+    trunc = 0 if truncation is None or truncation < 1 else int(truncation)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_ema_fwd(
+            x.data_ptr(), out.data_ptr(), _dt(x), bsz, dim, length, *x.stride(), *out.stride(),
+            p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n,
+            _ptr(mask), _ptr(h_in), _ptr(h_out), flags, trunc, _stream()), "ema_fwd")
+    return (out, h_out) if want_state else out
+
+
+def _dense(t):
+    """True when t's strides describe a permutation of a contiguous block."""
+    exp = 1
+    for size, stride in sorted(zip(t.shape, t.stride()), key=lambda v: v[1]):
+        if size == 1:
+            continue
+        if stride != exp:
+            return False
+        exp *= size
+    return True
+
+
+def ema_step(x, p, q, g, omega, h=None, silu=False):
+    """One decode step.  x (B, D) or (B, D, 1); returns (y like x, h' (B, D, N))."""
+    _cuda(x, p, q, g, omega, h)
+    shape = x.shape
+    x2 = x.reshape(shape[0], shape[1]).contiguous()
+    bsz, dim = x2.shape
+    p, q, g, omega = _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
+    n = p.shape[1]
+    h = _f32c(h)
+    h_out = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32)
+    y = torch.empty_like(x2)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_ema_step(x2.data_ptr(), y.data_ptr(), _dt(x2), bsz, dim, p.data_ptr(),
+                                            q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(h),
+                                            h_out.data_ptr(), EMA_SILU if silu else 0, _stream()), "ema_step")
+    return y.view(shape), h_out
+
+
+# --------------------------------------------------------------------------- norms
+def timestep_norm_fwd(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=None,
+                      eps=1e-5, num_groups=None, out=None):
+    """x (B, L, D) any strides -> (y, count (B) int64, mean, var (B, G) fp32).
+    gamma is the effective scale (module weight + 1)."""
+    _cuda(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask)
+    bsz, length, dim = x.shape
+    groups = dim if num_groups is None else int(num_groups)
+    prev_count = prev_count.detach().to(torch.int64).contiguous()
+    prev_mean, prev_var = _f32c(prev_mean), _f32c(prev_var)
+    if prev_mean.shape != (bsz, groups) or prev_var.shape != (bsz, groups):
+        raise ValueError("prev_mean/prev_var must be (batch, groups) = (%d, %d)" % (bsz, groups))
+    gamma, beta = _f32c(gamma), _f32c(beta)
+    mask = _mask_u8(padding_mask, bsz, length)
+    if out is None:
+        out = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
+            if _dense(x) else torch.empty_like(x, memory_format=torch.contiguous_format)
+    count = torch.empty(bsz, device=x.device, dtype=torch.int64)
+    mean = torch.empty(bsz, groups, device=x.device, dtype=torch.float32)
+    var = torch.empty_like(mean)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_timestep_norm_fwd(
+            x.data_ptr(), out.data_ptr(), _dt(x), bsz, length, dim, *x.stride(), *out.stride(),
+            prev_count.data_ptr(), prev_mean.data_ptr(), prev_var.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+            _ptr(mask), groups, float(eps), count.data_ptr(), mean.data_ptr(), var.data_ptr(), _stream()),
+            "timestep_norm_fwd")
+    return out, count, mean, var
+
+
+def sequence_norm_fwd(x, gamma, beta, padding_mask=None, eps=1e-5, length_last=True, num_groups=None, out=None):
+    """x (B, D, L) when ``length_last`` else (B, L, D); any strides.
+    Returns (y, count (B) int64, mean, rstd (B, G) fp32)."""
+    _cuda(x, gamma, beta, padding_mask)
+    if length_last:
+        bsz, dim, length = x.shape
+    else:
+        bsz, length, dim = x.shape
+    groups = dim if num_groups is None else int(num_groups)
+    gamma, beta = _f32c(gamma), _f32c(beta)
+    mask = _mask_u8(padding_mask, bsz, length)
+    if out is None:
+        out = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
+            if _dense(x) else torch.empty_like(x, memory_format=torch.contiguous_format)
+    xs, ys = x.stride(), out.stride()
+    if not length_last:
+        xs = (xs[0], xs[2], xs[1])
+        ys = (ys[0], ys[2], ys[1])
+    count = torch.empty(bsz, device=x.device, dtype=torch.int64)
+    mean = torch.empty(bsz, groups, device=x.device, dtype=torch.float32)
+    rstd = torch.empty_like(mean)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_sequence_norm_fwd(
+            x.data_ptr(), out.data_ptr(), _dt(x), bsz, dim, length, *xs, *ys, gamma.data_ptr(), beta.data_ptr(),
+            _ptr(mask), groups, float(eps), count.data_ptr(), mean.data_ptr(), rstd.data_ptr(), _stream()),
+            "sequence_norm_fwd")
+    return out, count, mean, rstd
+
+
+def tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma, beta, eps, p, q, g, omega,
+                    padding_mask=None, h_in=None, want_state=False, silu=False, want_normed=False):
+    """Fused per-feature TimestepNorm -> causal EMA on x (B, L, D).
+    Returns dict(y, count, mean, var[, h][, xn]); y and xn are (B, L, D) like x."""
+    _cuda(x, prev_count, prev_mean, prev_var, gamma, beta, p, q, g, omega, padding_mask, h_in)
+    bsz, length, dim = x.shape
+    prev_count = prev_count.detach().to(torch.int64).contiguous()
+    prev_mean, prev_var, gamma, beta = _f32c(prev_mean), _f32c(prev_var), _f32c(gamma), _f32c(beta)
+    p, q, g, omega = _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
+    n = p.shape[1]
+    mask = _mask_u8(padding_mask, bsz, length)
+    y = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
+        if _dense(x) else torch.empty_like(x, memory_format=torch.contiguous_format)
+    xn = torch.empty_strided(y.shape, y.stride(), dtype=x.dtype, device=x.device) if want_normed else None
+    count = torch.empty(bsz, device=x.device, dtype=torch.int64)
+    mean = torch.empty(bsz, dim, device=x.device, dtype=torch.float32)
+    var = torch.empty_like(mean)
+    h_in = _f32c(h_in)
+    h_out = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32) if want_state else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_tsn_ema_fwd(
+            x.data_ptr(), y.data_ptr(), _ptr(xn), _dt(x), bsz, length, dim, *x.stride(), *y.stride(),
+            prev_count.data_ptr(), prev_mean.data_ptr(), prev_var.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+            float(eps), count.data_ptr(), mean.data_ptr(), var.data_ptr(),
+            p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), _ptr(h_in), _ptr(h_out),
+            EMA_SILU if silu else 0, _stream()), "tsn_ema_fwd")
+    res = {"y": y, "count": count, "mean": mean, "var": var}
+    if want_state:
+        res["h"] = h_out
+    if want_normed:
+        res["xn"] = xn
+    return res
+
+
+# --------------------------------------------------------------------------- gates
+def _rows(t):
+    """View t (..., cols) as `rows` rows of `cols` elements with one row pitch; copies only
+    when the memory is not a uniform-pitch row-major matrix (e.g. after a transpose)."""
+    cols = t.shape[-1]
+    if t.dim() == 1:
+        t = t.unsqueeze(0)
+    ok = t.stride(-1) == 1 or cols == 1
+    ld = t.stride(-2) if t.shape[-2] > 1 else max(cols, t.stride(-2))
+    exp = ld
+    for size, stride in zip(reversed(t.shape[:-1]), reversed(t.stride()[:-1])):
+        if size != 1 and stride != exp:
+            ok = False
+        exp *= size
+    if not ok or ld < cols:
+        t = t.contiguous()
+        ld = cols
+    return t, t.numel() // cols, cols, ld
+
+
+def gate_silu(a, b=None):
+    """silu(a [+ b]) elementwise; a, b may be column slices of wider row-major matrices."""
+    _cuda(a, b)
+    a_, rows, cols, lda = _rows(a)
+    ldb, b_ = 0, None
+    if b is not None:
+        b_, _, _, ldb = _rows(b)
+    y = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.lib().mega_gate_silu(a_.data_ptr(), lda, _ptr(b_), ldb, y.data_ptr(), cols, _dt(a),
+                                             rows, cols, _stream()), "gate_silu")
+    return y
+
+
+def gate_mul_silu(a, r):
+    """a * silu(r)."""
+    _cuda(a, r)
+    a_, rows, cols, lda = _rows(a)
+    r_, _, _, ldr = _rows(r)
+    y = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.lib().mega_gate_mul_silu(a_.data_ptr(), lda, r_.data_ptr(), ldr, y.data_ptr(), cols,
+                                                 _dt(a), rows, cols, _stream()), "gate_mul_silu")
+    return y
+
+
+def gate_output(residual, u, hx, h_lin):
+    """residual + sigmoid(u) * (silu(hx + h_lin) - residual); u is the PRE-sigmoid gate."""
+    _cuda(residual, u, hx, h_lin)
+    r_, rows, cols, ldr = _rows(residual)
+    u_, _, _, ldu = _rows(u)
+    x_, _, _, ldx = _rows(hx)
+    h_, _, _, ldh = _rows(h_lin)
+    y = torch.empty(residual.shape, dtype=residual.dtype, device=residual.device)
+    with torch.cuda.device(residual.device):
+        _lib.check(_lib.lib().mega_gate_output(r_.data_ptr(), ldr, u_.data_ptr(), ldu, x_.data_ptr(), ldx,
+                                               h_.data_ptr(), ldh, y.data_ptr(), cols, _dt(residual), rows, cols,
+                                               _stream()), "gate_output")
+    return y

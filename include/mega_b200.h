@@ -1,0 +1,199 @@
+/*
+ * mega_b200 — C ABI of the B200 (sm_100a) implementation of Mega's EMA layer
+ * and its fused neighbours (TimestepNorm, SequenceNorm, gates, decode step).
+ *
+ * Conventions shared by every entry point
+ *   - Plain pointers and sizes only.  Every pointer is a DEVICE pointer unless
+ *     the parameter comment says "host".  The caller allocates every input and
+ *     output and keeps it alive until the work queued on `stream` has run.
+ *   - The library never allocates, frees or synchronises; every launch goes to
+ *     the `stream` argument (a cudaStream_t passed as void*; NULL = default
+ *     stream).
+ *   - Return value: MEGA_OK or one of the MEGA_ERR_* codes below; nothing is
+ *     launched when an argument is rejected.  No exception crosses the ABI and
+ *     no kernel traps or asserts.
+ *   - Activations may be fp32, bf16 or fp16 (mega_dtype); coefficients,
+ *     statistics and recurrent states are always fp32; counts are int64.
+ *   - Strides are in ELEMENTS.  An activation tensor is addressed as
+ *     base + b*stride_b + d*stride_d + l*stride_l, so both the (B, D, L)
+ *     "length last" and the (B, L, D) "channel last" memory orders (and the
+ *     time-major (L, B, D) order) are views of the same entry points.
+ *   - Padding masks are uint8 (B, L) contiguous, non-zero = padded position.
+ *   - Re-entrant: no global state except a launch counter.
+ *
+ * "Replaces" comments cite the reference interface each entry point stands in
+ * for, as file:line within the fairseq-apollo checkout.
+ */
+#ifndef MEGA_B200_H_
+#define MEGA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MEGA_API __attribute__((visibility("default")))
+#else
+#define MEGA_API
+#endif
+
+#define MEGA_ABI_VERSION 1
+
+enum mega_status {
+  MEGA_OK = 0,
+  MEGA_ERR_NULL = 1,        /* a required pointer is NULL */
+  MEGA_ERR_DTYPE = 2,       /* unknown mega_dtype */
+  MEGA_ERR_SHAPE = 3,       /* non-positive or inconsistent extent */
+  MEGA_ERR_STRIDE = 4,      /* stride combination the kernels cannot address */
+  MEGA_ERR_ALIGN = 5,       /* pointer not aligned for its element type */
+  MEGA_ERR_NDIM = 6,        /* ndim outside 1..MEGA_MAX_NDIM */
+  MEGA_ERR_UNSUPPORTED = 7, /* valid request this build does not implement */
+  MEGA_ERR_CUDA = 8         /* a CUDA launch failed; see mega_last_cuda_error */
+};
+
+enum mega_dtype { MEGA_F32 = 0, MEGA_BF16 = 1, MEGA_F16 = 2 };
+
+#define MEGA_MAX_NDIM 32
+
+/* flags of mega_ema_fwd / mega_tsn_ema_fwd */
+#define MEGA_EMA_BIDIRECTIONAL 1u /* coefficient arrays hold 2*D rows: causal half then anti-causal half */
+#define MEGA_EMA_NO_SHIFT 2u      /* anti-causal half includes lag 0 (reference shift=False) */
+#define MEGA_EMA_SILU 4u          /* apply SiLU to (conv + omega*x) before storing */
+
+typedef void* mega_stream_t;
+
+MEGA_API const char* mega_status_string(int status);
+MEGA_API const char* mega_last_cuda_error(void);
+MEGA_API int mega_abi_version(void);
+/* Number of kernels this library has launched in this process (monotonic). */
+MEGA_API uint64_t mega_launch_count(void);
+
+/*
+ * EMA coefficients: p = sigmoid(alpha)*beta, q = 1 - sigmoid(alpha)*sigmoid(delta),
+ * gamma_hat = gamma/sqrt(N).  alpha/delta/beta (K,N[,1]) and gamma (K,N) in
+ * `param_dtype`; outputs fp32 (K,N).
+ * Replaces: MultiHeadEMA._calc_coeffs, fairseq/modules/exponential_moving_average.py:71-80.
+ */
+MEGA_API int mega_ema_coeffs(const void* alpha, const void* delta, const void* beta, const void* gamma,
+                    int param_dtype, int K, int N, float* p, float* q, float* gamma_hat,
+                    mega_stream_t stream);
+
+/*
+ * EMA convolution kernel k[r,l] = sum_n p*gamma_hat*q^l for l < L; out (K,L) fp32.
+ * Replaces: MultiHeadEMA._compute_kernel (exponential_moving_average.py:82-90) and the
+ * weight half of ema_parameters_fwd (fairseq/csrc/ops/ema_parameters.cc:37-52).
+ */
+MEGA_API int mega_ema_kernel(const float* p, const float* q, const float* gamma_hat, int K, int N, int L,
+                    float* kernel_out, mega_stream_t stream);
+
+/*
+ * Output term of a carried state: bias[b,d,l] = sum_n gamma_hat*q^(l+1)*h[b,d,n]; out (B,D,L) fp32.
+ * Replaces: the bias half of ema_parameters_fwd (fairseq/csrc/ops/ema_parameters.cc:54-77).
+ */
+MEGA_API int mega_ema_bias(const float* q, const float* gamma_hat, const float* h, int B, int D, int N, int L,
+                  float* bias_out, mega_stream_t stream);
+
+/*
+ * The EMA layer forward: y = conv(k, x*(1-mask)) [+ carried-state term] + omega*x [then SiLU].
+ * x, y: activations (B,D,L) by strides.  p, q, gamma_hat: (K,N) with K = D, or 2*D when
+ * MEGA_EMA_BIDIRECTIONAL.  omega (D).  pad_mask NULL or (B,L).  h_in NULL or (B,D,N): state
+ * carried in; h_out NULL or (B,D,N): state after the last position (ema_hidden).  States are
+ * rejected for bidirectional calls.  truncation <= 0 or >= L: full-length kernel; otherwise
+ * the kernel support is its first `truncation` taps (bidirectional only, as in the reference).
+ * Replaces: BaseMovingLayer.forward (fairseq/modules/base_moving_average.py:120-172) with
+ * fftconv / bidirectional_fftconv (fairseq/modules/fused_ops/fftconv.py:13-27,85-100),
+ * ema_parameters bias (ema_parameters.cc:54-77) and ema_hidden_fwd (ema_hidden.cc:15-64).
+ */
+MEGA_API int mega_ema_fwd(const void* x, void* y, int dtype, int B, int D, int L,
+                 int64_t x_stride_b, int64_t x_stride_d, int64_t x_stride_l,
+                 int64_t y_stride_b, int64_t y_stride_d, int64_t y_stride_l,
+                 const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                 const uint8_t* pad_mask, const float* h_in, float* h_out,
+                 unsigned flags, int truncation, mega_stream_t stream);
+
+/*
+ * Single-token decode step: h' = p*x + q*h, y = sum_n gamma_hat*h' + omega*x [then SiLU].
+ * x, y (B,D) contiguous activations; h_in NULL (zero state) or (B,D,N); h_out (B,D,N), may alias h_in.
+ * Replaces: BaseMovingLayer.one_step (base_moving_average.py:105-118) and the L == 1 case of
+ * BaseMovingLayer.forward's incremental branch (:144-160).
+ */
+MEGA_API int mega_ema_step(const void* x, void* y, int dtype, int B, int D,
+                  const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                  const float* h_in, float* h_out, unsigned flags, mega_stream_t stream);
+
+/*
+ * TimestepNorm forward.  x, y (B,L,D) by strides.  prev_count (B) int64, prev_mean/prev_var
+ * (B,G) fp32 with G = D for num_groups <= 0 or == D, else num_groups.  gamma is the EFFECTIVE
+ * scale (module weight + 1), beta the bias, both (D) fp32.  Outputs count_out (B) int64,
+ * mean_out/var_out (B,G) fp32 (may alias the prev_* arrays).  Padded steps output 0 and do not
+ * advance the statistics.
+ * Replaces: timestep_norm_fwd / group_timestep_norm_fwd (fairseq/csrc/ops/timestep_norm.cc:23-103,
+ * 218-316; CUDA fairseq/csrc/ops/timestep_norm_kernel.cu:26-185,269-484) minus the cummean/cumrstd
+ * tensors saved for backward.
+ */
+MEGA_API int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, int L, int D,
+                           int64_t x_stride_b, int64_t x_stride_l, int64_t x_stride_d,
+                           int64_t y_stride_b, int64_t y_stride_l, int64_t y_stride_d,
+                           const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                           const float* gamma, const float* beta, const uint8_t* pad_mask,
+                           int num_groups, double eps,
+                           int64_t* count_out, float* mean_out, float* var_out,
+                           mega_stream_t stream);
+
+/*
+ * SequenceNorm forward: masked mean/variance over the sequence axis per (batch, channel) or per
+ * (batch, group).  x, y (B,D,L) by strides (pass the strides of a (B,L,D) tensor for the
+ * reference's length_last=False).  count_out (B) int64; mean_out/rstd_out (B,G) fp32.
+ * Replaces: sequence_norm_fwd / group_sequence_norm_fwd (fairseq/csrc/ops/sequence_norm.cc:258-372,
+ * 531-655; CUDA fairseq/csrc/ops/sequence_norm_kernel.cu:27-213,425-599).
+ */
+MEGA_API int mega_sequence_norm_fwd(const void* x, void* y, int dtype, int B, int D, int L,
+                           int64_t x_stride_b, int64_t x_stride_d, int64_t x_stride_l,
+                           int64_t y_stride_b, int64_t y_stride_d, int64_t y_stride_l,
+                           const float* gamma, const float* beta, const uint8_t* pad_mask,
+                           int num_groups, double eps,
+                           int64_t* count_out, float* mean_out, float* rstd_out,
+                           mega_stream_t stream);
+
+/*
+ * Fused per-feature TimestepNorm -> EMA (causal): y = EMA(TimestepNorm(x)) in one pass over x.
+ * x (B,L,D) by strides; y by strides; xn_out NULL or a tensor (same strides as y) receiving the
+ * normalised activations (the Mega block feeds them to v_proj).  TimestepNorm state as in
+ * mega_timestep_norm_fwd with G = D; EMA arguments as in mega_ema_fwd (causal only; flags may
+ * carry MEGA_EMA_SILU).
+ * Replaces: the sequence self.norm(...) -> transpose -> self.move(...) [-> move_act] of
+ * MovingAverageGatedAttention.forward (fairseq/modules/moving_average_gated_attention.py:306-316).
+ */
+MEGA_API int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D,
+                     int64_t x_stride_b, int64_t x_stride_l, int64_t x_stride_d,
+                     int64_t y_stride_b, int64_t y_stride_l, int64_t y_stride_d,
+                     const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                     const float* gamma, const float* beta, double eps,
+                     int64_t* count_out, float* mean_out, float* var_out,
+                     const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                     const uint8_t* pad_mask, const float* h_in, float* h_out,
+                     unsigned flags, mega_stream_t stream);
+
+/*
+ * Mega gate elementwise ops on (rows, D) contiguous activations.
+ *   mega_gate_silu:    y = silu(a [+ b])            (b may be NULL)
+ *   mega_gate_mul_silu y = a * silu(r)              (attn * silu(r) with r pre-activation)
+ *   mega_gate_output:  out = residual + sigmoid(u) * (silu(hx + h_lin) - residual)
+ * u, hx may be column slices of a wider matrix: `ld_*` are their row pitches in elements.
+ * Replaces: moving_average_gated_attention.py:308,316,322,330,407-412 (sigmoid / silu / addcmul chain).
+ */
+MEGA_API int mega_gate_silu(const void* a, int64_t ld_a, const void* b, int64_t ld_b, void* y, int64_t ld_y,
+                   int dtype, int64_t rows, int cols, mega_stream_t stream);
+MEGA_API int mega_gate_mul_silu(const void* a, int64_t ld_a, const void* r, int64_t ld_r, void* y, int64_t ld_y,
+                       int dtype, int64_t rows, int cols, mega_stream_t stream);
+MEGA_API int mega_gate_output(const void* residual, int64_t ld_res, const void* u, int64_t ld_u,
+                     const void* hx, int64_t ld_hx, const void* h_lin, int64_t ld_h,
+                     void* out, int64_t ld_out, int dtype, int64_t rows, int cols,
+                     mega_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGA_B200_H_ */

@@ -1,0 +1,90 @@
+"""GPU parity of the fused TimestepNorm -> EMA entry point against the oracle (TimestepNorm
+restated from the reference CPU op, then the fp64 recurrence)."""
+import pytest
+import torch
+
+from _util import make_ema_params, rel_l2, right_pad_mask
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1e-2}
+
+
+def _mods():
+    import fairseq_apollo_b200 as M
+    from oracle import mega_oracle as O
+    return M, O
+
+
+def _reference(O, x, pc, pm, pv, gamma, beta, prm, mask, silu=False):
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, mask, acc_dtype=torch.float64)
+    y = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, mask, silu=silu).transpose(1, 2)
+    return xn, y, cnt, mean, var
+
+
+@pytest.mark.parametrize("bsz,length,dim", [(1, 1, 1), (2, 77, 33), (3, 300, 128), (2, 1024, 72), (9, 40, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("masked", [False, True])
+def test_fused_grid(bsz, length, dim, dtype, masked):
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(length + dim)
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.1).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.3) if masked else None
+    pc = torch.full((bsz,), 2, dtype=torch.int64)
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    xn, y, cnt, mean, var = _reference(O, x, pc, pm, pv, gamma, beta, prm, mask)
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    res = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                p, q, g, prm[4].cuda(), None if mask is None else mask.cuda(), want_normed=True)
+    assert torch.equal(res["count"].cpu(), cnt)
+    assert rel_l2(res["y"].float(), y) < TOL[dtype]
+    assert rel_l2(res["xn"].float(), xn) < TOL[dtype]
+    assert rel_l2(res["mean"], mean) < 1e-5 and rel_l2(res["var"], var) < 1e-5
+    if mask is not None:
+        assert (res["xn"].cpu()[mask] == 0).all()
+
+
+def test_fused_equals_unfused_modules_and_incremental():
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(4)
+    dim, bsz, length = 48, 3, 96
+    norm = M.TimestepNorm(dim, prior_count=2).cuda().eval()
+    move = M.MultiHeadEMA(dim, ndim=16).cuda().eval()
+    x = torch.randn(bsz, length, dim, generator=gen).cuda()
+    mask = right_pad_mask(gen, bsz, length, 0.25).cuda()
+    with torch.no_grad():
+        norm.weight.normal_(0, 0.1)
+        norm.bias.normal_(0, 0.1)
+        xn = norm(x, mask)
+        ref = torch.nn.functional.silu(move(xn.transpose(1, 2), mask).transpose(1, 2))
+        mx, xn2 = M.timestep_norm_ema(norm, move, x, mask, None, activation='silu', return_normed=True)
+        assert rel_l2(mx, ref) < 1e-5 and rel_l2(xn2, xn) < 1e-6
+        # chunked with both modules' incremental buffers
+        st = {}
+        outs = [M.timestep_norm_ema(norm, move, x[:, i:i + 32], None, st) for i in range(0, length, 32)]
+        full = M.timestep_norm_ema(norm, move, x)
+        assert rel_l2(torch.cat(outs, 1), full) < 1e-5
+        st1 = {}
+        outs = [M.timestep_norm_ema(norm, move, x[:, i:i + 1], None, st1) for i in range(length)]
+        assert rel_l2(torch.cat(outs, 1), full) < 1e-5
+
+
+def test_config1_reduced_bf16():
+    """BASELINE config 1 at reduced batch (B=2 of 16): L=4096, D=1024, bf16 activations, fp32
+    parameters, TimestepNorm weight=1 bias=0 eps=1e-5, no padding."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(1235)
+    bsz, length, dim = 2, 4096, 1024
+    prm = make_ema_params(gen, dim, 16)
+    x = torch.randn(bsz, length, dim, generator=gen).to(torch.bfloat16)
+    pc = torch.zeros(bsz, dtype=torch.int64)
+    pm = torch.zeros(bsz, dim)
+    pv = torch.ones(bsz, dim)
+    xn, y, cnt, mean, var = _reference(O, x, pc, pm, pv, torch.ones(dim), torch.zeros(dim), prm, None)
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    res = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), torch.ones(dim).cuda(),
+                                torch.zeros(dim).cuda(), 1e-5, p, q, g, prm[4].cuda())
+    assert rel_l2(res["y"].float(), y) < 1e-2
