@@ -32,6 +32,8 @@ SIGNATURES = {
     "mega_gate_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
+    "mega_set_option": [c_i, c_i],
+    "mega_debug_device_error": [ctypes.POINTER(c_i), c_i],
 }
 OTHER = {
     "mega_status_string": ([c_i], ctypes.c_char_p),
@@ -79,3 +81,14 @@ def check(status, what):
 
 def launch_count():
     return int(lib().mega_launch_count())
+
+
+def set_option(key, value):
+    check(lib().mega_set_option(int(key), int(value)), "set_option")
+
+
+def device_error(reset=False):
+    """Synchronising read of the device-side error word (0 = no bounded wait ever gave up)."""
+    v = c_i(0)
+    check(lib().mega_debug_device_error(ctypes.byref(v), 1 if reset else 0), "device_error")
+    return v.value

@@ -15,6 +15,8 @@ namespace mega {
 // ---- launch bookkeeping ---------------------------------------------------
 extern std::atomic<uint64_t> g_launches;
 extern thread_local char g_cuda_err[256];
+extern std::atomic<int> g_options[8];
+enum { OPT_DISABLE_STREAM = 0 };
 int check_launch(const char* what);
 
 template <typename... KArgs, typename... Args>
@@ -31,6 +33,7 @@ struct Elem;
 template <>
 struct Elem<float> {
   static __device__ __forceinline__ float ld(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ float ld_shared(const float* p) { return *p; }
   static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
 };
 template <>
@@ -38,6 +41,7 @@ struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ float ld(const __nv_bfloat16* p) {
     return __bfloat162float(__ldg(p));
   }
+  static __device__ __forceinline__ float ld_shared(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) {
     *p = __float2bfloat16_rn(v);
   }
@@ -45,6 +49,7 @@ struct Elem<__nv_bfloat16> {
 template <>
 struct Elem<__half> {
   static __device__ __forceinline__ float ld(const __half* p) { return __half2float(__ldg(p)); }
+  static __device__ __forceinline__ float ld_shared(const __half* p) { return __half2float(*p); }
   static __device__ __forceinline__ void st(__half* p, float v) { *p = __float2half_rn(v); }
 };
 

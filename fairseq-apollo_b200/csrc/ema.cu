@@ -5,6 +5,7 @@
 // order-N diagonal recurrence h_t = q h_{t-1} + p x_t, y_t = sum_n gamma_n h_{n,t}:
 // O(L) work per row, no length cap, one pass over x.
 #include "common.cuh"
+#include "stream_cl.cuh"
 
 namespace mega {
 
@@ -400,6 +401,14 @@ extern "C" int mega_ema_fwd(const void* x, void* y, int dtype, int B, int D, int
   a.x = x; a.y = y; a.B = B; a.D = D; a.L = L; a.N = N;
   a.xsb = xsb; a.xsd = xsd; a.xsl = xsl; a.ysb = ysb; a.ysd = ysd; a.ysl = ysl;
   a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask; a.h_in = h_in; a.h_out = h_out;
+  if (!bidir && x != y) {
+    StreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
+    sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+    if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, true, sa, (cudaStream_t)stream))
+      return check_launch("ema_fwd(stream)");
+  }
   return ema_fwd_simt(a, flags, truncation, dtype, (cudaStream_t)stream);
 }
 

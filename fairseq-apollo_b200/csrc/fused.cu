@@ -4,6 +4,7 @@
 // per-channel quantity (Welford state, pole states) lives in registers.  Works for any
 // strides; coalesced when the channel stride is 1.
 #include "common.cuh"
+#include "stream_cl.cuh"
 
 namespace mega {
 
@@ -140,6 +141,16 @@ extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype,
   a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
   a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask; a.h_in = h_in; a.h_out = h_out;
   a.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  {
+    StreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.prev_count = a.prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var; sa.gamma = gamma;
+    sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
+    sa.silu = a.silu;
+    if (stream_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, true, sa, (cudaStream_t)stream))
+      return check_launch("tsn_ema_fwd(stream)");
+  }
   const int np = next_pow2_ndim(N);
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
   const bool state = h_in || h_out;

@@ -4,6 +4,7 @@
 // moments of the unmasked prefix (plus a prior that acts as prev_count pseudo-samples).
 // SequenceNorm normalises with the masked moments of the whole sequence.
 #include "common.cuh"
+#include "stream_cl.cuh"
 
 namespace mega {
 
@@ -307,6 +308,15 @@ extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, 
   a.gamma = gamma; a.beta = beta; a.mask = pad_mask; a.eps = (float)eps;
   a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
   if (G == D) {
+    if (x != y) {
+      StreamArgs sa{};
+      sa.B = B; sa.L = L; sa.D = D; sa.N = 0;
+      sa.prev_count = a.prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var; sa.gamma = gamma;
+      sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
+      sa.mask = pad_mask;
+      if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, false, sa, (cudaStream_t)stream))
+        return check_launch("timestep_norm_fwd(stream)");
+    }
     const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
     MEGA_DISPATCH_DTYPE(dtype, launch(tsn_plain_kernel<T>, grid, 128, 0, stream, a));
   } else {

@@ -1,0 +1,29 @@
+// Interface of the streamed channel-contiguous kernels (stream_cl.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace mega {
+
+struct StreamArgs {
+  int B, L, D, N;
+  const long long* prev_count;
+  const float *prev_mean, *prev_var, *gamma, *beta;
+  float eps;
+  long long* count_out;
+  float *mean_out, *var_out;
+  const float *p, *q, *g, *omega;
+  const float* h_in;
+  float* h_out;
+  const unsigned char* mask;
+  int silu;
+  int has_xn;
+};
+
+// Tries the streamed TMA path for TimestepNorm (norm), causal EMA (ema) or both fused.  Returns
+// false, having launched nothing, when the call is outside its envelope (channel stride != 1,
+// ndim > 16, bases or strides not 16-byte aligned, more than 65535 sequences).
+bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
+                   long long ysb, long long ysl, long long ysd, bool norm, bool ema, const StreamArgs& a,
+                   cudaStream_t s);
+
+}  // namespace mega

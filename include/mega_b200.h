@@ -69,6 +69,17 @@ MEGA_API const char* mega_last_cuda_error(void);
 MEGA_API int mega_abi_version(void);
 /* Number of kernels this library has launched in this process (monotonic). */
 MEGA_API uint64_t mega_launch_count(void);
+/*
+ * Process-wide switches meant for tests.  key MEGA_OPT_DISABLE_STREAM (0): non-zero routes every
+ * call to the generic kernels instead of the TMA-streamed ones.
+ */
+#define MEGA_OPT_DISABLE_STREAM 0
+MEGA_API int mega_set_option(int key, int value);
+/*
+ * Debug aid (synchronises the device): reads the device-side error word that a kernel raises
+ * when one of its bounded waits gives up; `reset` != 0 clears it.  host_value is a HOST pointer.
+ */
+MEGA_API int mega_debug_device_error(int* host_value, int reset);
 
 /*
  * EMA coefficients: p = sigmoid(alpha)*beta, q = 1 - sigmoid(alpha)*sigmoid(delta),

@@ -88,3 +88,60 @@ def test_config1_reduced_bf16():
     res = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), torch.ones(dim).cuda(),
                                 torch.zeros(dim).cuda(), 1e-5, p, q, g, prm[4].cuda())
     assert rel_l2(res["y"].float(), y) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("bsz,length,dim", [(2, 1, 8), (3, 31, 72), (2, 32, 64), (2, 33, 136), (1, 1000, 200), (5, 257, 8)])
+def test_streamed_path_matches_generic(dtype, bsz, length, dim):
+    """The TMA-streamed kernels and the generic kernels are two implementations of the same
+    entry points: run both (a test switch disables the streamed one) on shapes inside the
+    streamed envelope and compare them with each other and with the oracle."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(bsz * 31 + length + dim)
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.1).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.4)
+    if length > 3:
+        mask[0, 1] = True
+    pc = torch.full((bsz,), 3, dtype=torch.int64)
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    h0 = torch.randn(bsz, dim, 16, generator=gen) * 0.3
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    tol = {torch.float32: 1e-5, torch.bfloat16: 1e-2, torch.float16: 2e-3}[dtype]
+    outs = []
+    for disable in (0, 1):
+        _lib.set_option(0, disable)
+        try:
+            fused = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                          p, q, g, prm[4].cuda(), mask.cuda(), h_in=h0.cuda(), want_state=True,
+                                          want_normed=True, silu=True)
+            plain = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                          p, q, g, prm[4].cuda(), None)
+            tsn = M.ops.timestep_norm_fwd(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), mask.cuda())
+            ema, hs = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), mask.cuda(), h0.cuda(),
+                                        want_state=True)
+            ema2 = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda())
+        finally:
+            _lib.set_option(0, 0)
+        outs.append((fused, plain, tsn, ema, hs, ema2))
+    (f0, p0, t0, e0, h0s, e20), (f1, p1, t1, e1, h1s, e21) = outs
+    assert rel_l2(f0["y"].float(), f1["y"].float()) < tol and rel_l2(f0["xn"].float(), f1["xn"].float()) < tol
+    assert rel_l2(f0["h"], f1["h"]) < 1e-5 and rel_l2(f0["mean"], f1["mean"]) < 1e-5 and rel_l2(f0["var"], f1["var"]) < 1e-5
+    assert torch.equal(f0["count"], f1["count"])
+    assert rel_l2(p0["y"].float(), p1["y"].float()) < tol
+    assert rel_l2(t0[0].float(), t1[0].float()) < tol and torch.equal(t0[1], t1[1])
+    assert rel_l2(e0.float(), e1.float()) < tol and rel_l2(h0s, h1s) < 1e-5 and rel_l2(e20.float(), e21.float()) < tol
+    # against the oracle
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, mask, acc_dtype=torch.float64)[:4]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, mask, h=h0, return_state=True, silu=True)
+    assert rel_l2(f0["y"].float(), yref.transpose(1, 2)) < tol
+    assert rel_l2(f0["h"], href) < max(tol, 1e-5) * (1 if dtype == torch.float32 else 3)
+    assert torch.equal(f0["count"].cpu(), cnt)
+    assert (f0["xn"].cpu()[mask] == 0).all()
+    eref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, mask, h=h0)
+    assert rel_l2(e0.float(), eref) < tol
+    assert _lib.device_error() == 0
