@@ -148,6 +148,8 @@ extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype,
     sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = a.silu;
+    if (mma_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream))
+      return check_launch("tsn_ema_fwd(mma)");
     if (stream_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, true, sa, (cudaStream_t)stream))
       return check_launch("tsn_ema_fwd(stream)");
   }

@@ -1,0 +1,430 @@
+// Tensor-core variant of the fused TimestepNorm -> causal EMA (and of the EMA alone) for bf16
+// activations with contiguous channels and no padding mask.
+//
+// Work split.  A CTA owns 64 adjacent channels of 8 sequences and walks time in steps of 32
+// positions.  Warp w owns the 16-byte column group w (8 channels).  For one channel the 8
+// sequences x 2 consecutive 16-position chunks of a step form the 16 rows of warp-level MMAs
+// (row g = sequence g, chunk 0; row g + 8 = sequence g, chunk 1), so every carry between
+// chunks stays inside one thread and no cross-lane scan is needed.
+//
+// Math per channel and step (h = pole states, C = 16):
+//   TimestepNorm : prefix sums of x and x^2 inside each chunk are products with 0/1 matrices
+//                  (tf32 MMAs; x is bf16 and x^2 has 16 significant bits, both exact in tf32);
+//                  the running totals enter as the accumulator input.  mean/var follow from
+//                  the sums, xn = (x - mean) * rstd * w + b.
+//   EMA          : y = T xn + G h_start   (T: 16x16 lower-triangular Toeplitz of the kernel
+//                  k[l] = sum_n p g q^l, omega folded into k[0]; G[t][n] = g q^(t+1))
+//                  h_local = P xn          (P[n][t] = p q^(15-t));  h_next = q^16 h + h_local.
+// The per-channel matrices T, P, G are built once per CTA, in MMA fragment order, in shared
+// memory.  Tiles move by TMA (128-byte swizzle), are transformed in place and stored by TMA.
+#include <mutex>
+
+#include "common.cuh"
+#include "stream_cl.cuh"
+#include "tma.cuh"
+
+namespace mega {
+
+namespace {
+
+constexpr int kCh = 64;      // channels per CTA
+constexpr int kSeq = 8;      // sequences per CTA
+constexpr int kStep = 32;    // positions per step (2 chunks of 16)
+constexpr int kStages = 3;
+constexpr int kThreads = 256;
+constexpr int kStageBytes = kSeq * kStep * kCh * 2;  // 32 KiB
+
+// shared memory map (bytes, from a 1024-aligned base)
+constexpr int kOffStages = 0;
+constexpr int kOffT = kOffStages + kStages * kStageBytes;  // [64][2][32] u32
+constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [64][32] uint4
+constexpr int kOffG = kOffP + kCh * 4 * 32 * 4;            // [64][32] uint4
+constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [64][16] f32  (q^16)
+constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [64][2] f32
+constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [64][16] f32 scratch: kernel taps
+constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // [kStages] u64
+constexpr int kSmemBytes = kOffBar + 64 + 1024;            // + alignment slack
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], float a0, float a1, float a2, float a3, float b0,
+                                         float b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)), "r"(__float_as_uint(a2)),
+        "r"(__float_as_uint(a3)), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+}
+// two fp32 -> packed bf16x2 (lo in the low half)
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float rsqrt_fast(float v) {
+  float r;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float rcp_fast(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float qpow(float logq, bool qpos, int l) {
+  return l == 0 ? 1.0f : (qpos ? __expf((float)l * logq) : 0.0f);
+}
+__device__ __forceinline__ uint32_t bf16_bits(float v) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// Byte offset of the 16-byte vector (sequence, position, column group) inside a stage written by
+// TMA with the 128-byte swizzle: chunk index XOR (row mod 8), rows are 128 bytes.
+__device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
+  const int row = seq * kStep + t;
+  return (uint32_t)(row * 128 + ((cg ^ (row & 7)) << 4));
+}
+
+template <bool kNorm>
+__global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx,
+                                                                  const __grid_constant__ CUtensorMap tmy,
+                                                                  StreamArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint32_t* Tc = reinterpret_cast<uint32_t*>(sm + kOffT);
+  uint4* Pc = reinterpret_cast<uint4*>(sm + kOffP);
+  uint4* Gc = reinterpret_cast<uint4*>(sm + kOffG);
+  float* Ac = reinterpret_cast<float*>(sm + kOffA);
+  float* WB = reinterpret_cast<float*>(sm + kOffWB);
+  float* Kp = reinterpret_cast<float*>(sm + kOffKp);
+  uint64_t* full = reinterpret_cast<uint64_t*>(sm + kOffBar);
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, q = lane & 3;
+  const int d0 = blockIdx.x * kCh;
+  const int b0 = blockIdx.y * kSeq;
+  const int L = a.L;
+  const int nsteps = (L + kStep - 1) / kStep;
+
+  if (tid == 0) {
+    prefetch_tensormap(&tmx);
+    prefetch_tensormap(&tmy);
+    for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int s = 0; s < 2 && s < nsteps; ++s) {
+      mbar_expect_tx(&full[s], kStageBytes);
+      tma_load_3d(sm + kOffStages + s * kStageBytes, &tmx, d0, s * kStep, b0, &full[s]);
+    }
+  }
+
+  // ---- per-channel matrices, phase 1: kernel taps k'[l], q^16, affine ---------------------
+  for (int it = tid; it < kCh * 16; it += kThreads) {
+    const int ch = it >> 4, l = it & 15;
+    const int d = d0 + ch;
+    float acc = 0.f, a16 = 0.f;
+    if (d < a.D) {
+      for (int n = 0; n < a.N; ++n) {
+        const float pn = __ldg(a.p + (size_t)d * a.N + n), qn = __ldg(a.q + (size_t)d * a.N + n),
+                    gn = __ldg(a.g + (size_t)d * a.N + n);
+        const bool qpos = qn > 0.f;
+        const float lq = qpos ? __logf(qn) : 0.f;
+        acc = fmaf(pn * gn, qpow(lq, qpos, l), acc);
+        if (n == l) a16 = qpow(lq, qpos, 16);
+      }
+      if (l == 0) acc += __ldg(a.omega + d);
+    }
+    Kp[it] = acc;
+    Ac[it] = a16;  // entry (ch, pole l); poles >= N stay 0
+    if (l < 2) {
+      float v = (l == 0) ? 1.f : 0.f;
+      if (kNorm && d < a.D) v = (l == 0) ? __ldg(a.gamma + d) : __ldg(a.beta + d);
+      WB[ch * 2 + l] = v;
+    }
+  }
+  __syncthreads();
+  // ---- phase 2: fragment-ordered T, P, G --------------------------------------------------
+  for (int it = tid; it < kCh * 32; it += kThreads) {
+    const int ch = it >> 5, ln = it & 31;
+    const int gg = ln >> 2, qq = ln & 3;
+    const int d = d0 + ch;
+    // Toeplitz: B[k = t][n = t'] = k'[t' - t]; R0: t' = gg, t = 2qq, 2qq+1; R1: t' = 8 + gg
+    auto tap = [&](int l) -> float { return (l >= 0 && l < 16) ? Kp[ch * 16 + l] : 0.f; };
+    Tc[(ch * 2 + 0) * 32 + ln] = bf16_bits(tap(gg - 2 * qq)) | (bf16_bits(tap(gg - 2 * qq - 1)) << 16);
+    Tc[(ch * 2 + 1) * 32 + ln] = bf16_bits(tap(8 + gg - 2 * qq)) | (bf16_bits(tap(8 + gg - 2 * qq - 1)) << 16);
+    uint32_t pr[4], gr[4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      // P^T: B[k = t][n = pole 8nb + gg] = p q^(15 - t);  b0: t = 2qq, 2qq+1;  b1: t = 2qq+8, 2qq+9
+      const int n = 8 * nb + gg;
+      float pn = 0.f, lq = 0.f;
+      bool qpos = false;
+      if (d < a.D && n < a.N) {
+        pn = __ldg(a.p + (size_t)d * a.N + n);
+        const float qn = __ldg(a.q + (size_t)d * a.N + n);
+        qpos = qn > 0.f;
+        lq = qpos ? __logf(qn) : 0.f;
+      }
+      pr[nb * 2 + 0] = bf16_bits(pn * qpow(lq, qpos, 15 - 2 * qq)) | (bf16_bits(pn * qpow(lq, qpos, 14 - 2 * qq)) << 16);
+      pr[nb * 2 + 1] = bf16_bits(pn * qpow(lq, qpos, 7 - 2 * qq)) | (bf16_bits(pn * qpow(lq, qpos, 6 - 2 * qq)) << 16);
+      // G^T: B[k = pole][n = t' = 8nb + gg] = g q^(t' + 1);  b0: poles 2qq, 2qq+1;  b1: poles 2qq+8, 2qq+9
+      const int tp = 8 * nb + gg;
+      float gv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int pole = 2 * qq + (k & 1) + ((k >> 1) << 3);
+        float v = 0.f;
+        if (d < a.D && pole < a.N) {
+          const float qn = __ldg(a.q + (size_t)d * a.N + pole);
+          const bool qp = qn > 0.f;
+          v = __ldg(a.g + (size_t)d * a.N + pole) * qpow(qp ? __logf(qn) : 0.f, qp, tp + 1);
+        }
+        gv[k] = v;
+      }
+      gr[nb * 2 + 0] = bf16_bits(gv[0]) | (bf16_bits(gv[1]) << 16);
+      gr[nb * 2 + 1] = bf16_bits(gv[2]) | (bf16_bits(gv[3]) << 16);
+    }
+    Pc[ch * 32 + ln] = make_uint4(pr[0], pr[1], pr[2], pr[3]);
+    Gc[ch * 32 + ln] = make_uint4(gr[0], gr[1], gr[2], gr[3]);
+  }
+
+  // ---- running state of this thread: sequence b0 + g, channels 8*warp + e ----------------------
+  const int bseq = b0 + g;
+  const bool seq_ok = bseq < a.B;
+  float hc[8][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
+  float s1c[8], s2c[8];
+  float nbase = 1.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int d = d0 + warp * 8 + e;
+    const bool ok = seq_ok && d < a.D;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
+      hc[e][k] = (ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+    }
+    s1c[e] = 0.f;
+    s2c[e] = 0.f;
+    if (kNorm && ok) {
+      const float c0 = (float)a.prev_count[bseq];
+      const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
+      s1c[e] = c0 * mu;
+      s2c[e] = c0 * fmaf(mu, mu, vv);
+    }
+  }
+  if (kNorm && seq_ok) nbase = (float)a.prev_count[bseq] + 1.f;
+  const float ut0 = (2 * q <= g) ? 1.f : 0.f, ut1 = (2 * q + 1 <= g) ? 1.f : 0.f;
+  const float eps = a.eps;
+  // position offsets of the 8 vectors this thread touches: j = 0..3 chunk 0, j = 4..7 chunk 1
+  int toff[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) toff[j] = (j >> 2) * 16 + 2 * q + (j & 1) + ((j >> 1) & 1) * 8;
+
+  __syncthreads();  // matrices visible
+
+  for (int i = 0; i < nsteps; ++i) {
+    const int s = i % kStages;
+    const uint32_t ph = (uint32_t)((i / kStages) & 1);
+    unsigned char* stage = sm + kOffStages + s * kStageBytes;
+    const bool ok = mbar_wait(&full[s], ph);
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(stage + vec_off(g, toff[j], warp));
+    float invn[8];
+    if (kNorm) {
+      const float nb_f = nbase + (float)(i * kStep);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(nb_f + (float)toff[j]);
+    }
+#pragma unroll
+    for (int pp = 0; pp < 4; ++pp) {
+      float yv[2][8];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int e = 2 * pp + h2;
+        const int ch = warp * 8 + e;
+        float xf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t w32 = pp == 0 ? v[j].x : pp == 1 ? v[j].y : pp == 2 ? v[j].z : v[j].w;
+          xf[j] = __uint_as_float(h2 == 0 ? (w32 << 16) : (w32 & 0xffff0000u));
+        }
+        float xn[8];
+        if (kNorm) {
+          float S1[8], S2[8];
+          {
+            float F[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tf32(F, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f);
+            mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f);
+            const float c0 = s1c[e], c1 = s1c[e] + F[0];
+            float D0[4] = {c0, c0, c1, c1}, D1[4] = {c0, c0, c1, c1};
+            mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1);
+            mma_tf32(D1, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f);
+            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1);
+            s1c[e] = c1 + F[2];
+            S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
+            S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
+          }
+          {
+            float sq[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sq[j] = xf[j] * xf[j];
+            float F[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_tf32(F, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f);
+            mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f);
+            const float c0 = s2c[e], c1 = s2c[e] + F[0];
+            float D0[4] = {c0, c0, c1, c1}, D1[4] = {c0, c0, c1, c1};
+            mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1);
+            mma_tf32(D1, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f);
+            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1);
+            s2c[e] = c1 + F[2];
+            S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
+            S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
+          }
+          const float2 wb = *reinterpret_cast<const float2*>(WB + ch * 2);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float mean = S1[j] * invn[j];
+            const float ve = fmaxf(fmaf(S2[j], invn[j], eps) - mean * mean, eps);
+            const float sc = rsqrt_fast(ve) * wb.x;
+            xn[j] = fmaf(xf[j] - mean, sc, wb.y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xn[j] = xf[j];
+        }
+        // A fragment of xn: a0 (row g: t = 2q, 2q+1), a1 (row g+8), a2 (row g: t = 2q+8, 2q+9), a3 (row g+8)
+        const uint32_t xa0 = pack_bf16(xn[0], xn[1]), xa2 = pack_bf16(xn[2], xn[3]);
+        const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
+        const uint2 tr = make_uint2(Tc[(ch * 2 + 0) * 32 + lane], Tc[(ch * 2 + 1) * 32 + lane]);
+        const uint4 pr = Pc[ch * 32 + lane];
+        const uint4 gr = Gc[ch * 32 + lane];
+        const float2 aq0 = *reinterpret_cast<const float2*>(Ac + ch * 16 + 2 * q);
+        const float2 aq1 = *reinterpret_cast<const float2*>(Ac + ch * 16 + 8 + 2 * q);
+        // local state contributions of the two chunks
+        float H0[4] = {0.f, 0.f, 0.f, 0.f}, H1[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y);  // poles 2q, 2q+1
+        mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w);  // poles 8+2q, 9+2q
+        // states entering chunk 0 (= carried) and chunk 1, and the new carry
+        const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
+        float hs1[4];
+        hs1[0] = fmaf(aq0.x, hs0[0], H0[0]);
+        hs1[1] = fmaf(aq0.y, hs0[1], H0[1]);
+        hs1[2] = fmaf(aq1.x, hs0[2], H1[0]);
+        hs1[3] = fmaf(aq1.y, hs0[3], H1[1]);
+        hc[e][0] = fmaf(aq0.x, hs1[0], H0[2]);
+        hc[e][1] = fmaf(aq0.y, hs1[1], H0[3]);
+        hc[e][2] = fmaf(aq1.x, hs1[2], H1[2]);
+        hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
+        const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
+        const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
+        float Y0[4] = {0.f, 0.f, 0.f, 0.f}, Y1[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_bf16(Y0, ha0, ha1, ha2, ha3, gr.x, gr.y);
+        mma_bf16(Y1, ha0, ha1, ha2, ha3, gr.z, gr.w);
+        mma_bf16(Y0, xa0, xa1, xa2, xa3, tr.x, 0u);
+        mma_bf16(Y1, xa0, xa1, xa2, xa3, tr.y, tr.x);
+        yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
+        yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
+        if (a.silu) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) yv[h2][j] = siluf_(yv[h2][j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t o = pack_bf16(yv[0][j], yv[1][j]);
+        if (pp == 0) v[j].x = o; else if (pp == 1) v[j].y = o; else if (pp == 2) v[j].z = o; else v[j].w = o;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(stage + vec_off(g, toff[j], warp)) = v[j];
+    fence_proxy_async();
+    if (__syncthreads_or(!ok)) break;
+    if (tid == 0) {
+      tma_store_3d(&tmy, d0, i * kStep, b0, stage);
+      bulk_commit();
+      if (i + 2 < nsteps) {
+        bulk_wait_read<1>();  // the store issued one step ago has drained its stage
+        const int s2 = (i + 2) % kStages;
+        mbar_expect_tx(&full[s2], kStageBytes);
+        tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i + 2) * kStep, b0, &full[s2]);
+      }
+    }
+  }
+  if (tid == 0) bulk_wait<0>();
+
+  // ---- final statistics and states -------------------------------------------------------------
+  if (seq_ok && q == 0) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int d = d0 + warp * 8 + e;
+      if (kNorm && d < a.D) {
+        const float n = (float)a.prev_count[bseq] + (float)L;
+        const float mean = s1c[e] / n;
+        a.mean_out[(size_t)bseq * a.D + d] = mean;
+        a.var_out[(size_t)bseq * a.D + d] = fmaxf(s2c[e] / n - mean * mean, 0.f);
+      }
+    }
+    if (kNorm && blockIdx.x == 0 && warp == 0) a.count_out[bseq] = a.prev_count[bseq] + L;
+  }
+  if (seq_ok && a.h_out) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int d = d0 + warp * 8 + e;
+      if (d < a.D) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
+          if (pole < a.N) a.h_out[((size_t)bseq * a.D + d) * a.N + pole] = hc[e][k];
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// Envelope: bf16, channel stride 1, no padding mask, ndim <= 16, no normalised-copy output,
+// B >= 4 (rows of the MMAs are sequences), L < 2^24, and L a multiple of 32 when a state is
+// exported.  Returns false, launching nothing, outside of it.
+bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
+                long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a_in, cudaStream_t s) {
+  if (g_options[OPT_DISABLE_MMA].load() != 0) return false;
+  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || xn != nullptr || a_in.mask != nullptr) return false;
+  if (a_in.N > 16 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
+  if (a_in.h_out && (a_in.L % kStep) != 0) return false;
+  if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
+  CUtensorMap tx, ty;
+  if (!make_tensor_map_3d(&tx, dtype, x, a_in.D, a_in.L, a_in.B, xsl, xsb, kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B))
+    return false;
+  if (!make_tensor_map_3d(&ty, dtype, y, a_in.D, a_in.L, a_in.B, ysl, ysb, kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B))
+    return false;
+  static std::once_flag once;
+  static bool attr_ok = true;
+  std::call_once(once, [&] {
+    attr_ok = cudaFuncSetAttribute(tsn_ema_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess &&
+              cudaFuncSetAttribute(tsn_ema_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
+  });
+  if (!attr_ok) {
+    cudaGetLastError();
+    return false;
+  }
+  dim3 grid((a_in.D + kCh - 1) / kCh, (a_in.B + kSeq - 1) / kSeq);
+  if (norm)
+    launch(tsn_ema_mma_kernel<true>, grid, dim3(kThreads), (size_t)kSmemBytes, (void*)s, tx, ty, a_in);
+  else
+    launch(tsn_ema_mma_kernel<false>, grid, dim3(kThreads), (size_t)kSmemBytes, (void*)s, tx, ty, a_in);
+  return true;
+}
+
+cudaError_t mma_cl_read_device_error(int* v, bool reset) { return read_device_error(v, reset); }
+
+}  // namespace mega

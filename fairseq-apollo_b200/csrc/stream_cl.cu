@@ -335,7 +335,9 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
 extern "C" MEGA_API int mega_debug_device_error(int* host_value, int reset) {
   if (!host_value) return MEGA_ERR_NULL;
   int v = 0;
+  int v2 = 0;
   if (mega::read_device_error(&v, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
-  *host_value = v;
+  if (mega::mma_cl_read_device_error(&v2, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
+  *host_value = v | v2;
   return MEGA_OK;
 }

@@ -26,4 +26,10 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
                    long long ysb, long long ysl, long long ysd, bool norm, bool ema, const StreamArgs& a,
                    cudaStream_t s);
 
+// Tries the tensor-core path (mma_cl.cu): bf16, channel stride 1, no padding mask, ndim <= 16,
+// no normalised-copy output, at least 4 sequences.  Same contract as stream_cl_try.
+bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
+                long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a, cudaStream_t s);
+cudaError_t mma_cl_read_device_error(int* v, bool reset);
+
 }  // namespace mega

@@ -74,6 +74,7 @@ MEGA_API uint64_t mega_launch_count(void);
  * call to the generic kernels instead of the TMA-streamed ones.
  */
 #define MEGA_OPT_DISABLE_STREAM 0
+#define MEGA_OPT_DISABLE_MMA 1 /* non-zero: skip the tensor-core kernels */
 MEGA_API int mega_set_option(int key, int value);
 /*
  * Debug aid (synchronises the device): reads the device-side error word that a kernel raises

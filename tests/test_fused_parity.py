@@ -145,3 +145,52 @@ def test_streamed_path_matches_generic(dtype, bsz, length, dim):
     eref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, mask, h=h0)
     assert rel_l2(e0.float(), eref) < tol
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("bsz,length,dim,ndim", [(4, 32, 64, 16), (9, 100, 72, 16), (8, 1024, 128, 16),
+                                                  (16, 257, 200, 16), (5, 64, 8, 2), (8, 96, 136, 5)])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_tensor_core_path(bsz, length, dim, ndim, with_state):
+    """bf16, no padding: the tensor-core kernels (fused TimestepNorm -> EMA and EMA alone) against
+    the oracle, and against the streamed SIMT kernels (a test switch disables the MMA path)."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(bsz * 131 + length + dim)
+    prm = make_ema_params(gen, dim, ndim)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.2).to(torch.bfloat16)
+    pc = torch.full((bsz,), 2, dtype=torch.int64)
+    pc[0] = 5
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    h0 = torch.randn(bsz, dim, ndim, generator=gen) * 0.3 if with_state else None
+    want_state = with_state and length % 32 == 0
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    outs = []
+    before = M.launch_count()
+    for disable in (0, 1):
+        _lib.set_option(1, disable)
+        try:
+            fused = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                          p, q, g, prm[4].cuda(), None, h_in=None if h0 is None else h0.cuda(),
+                                          want_state=want_state)
+            ema = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), None,
+                                    None if h0 is None else h0.cuda(), want_state=want_state, silu=True)
+        finally:
+            _lib.set_option(1, 0)
+        outs.append((fused, ema))
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[:4]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, None, h=h0, return_state=True)
+    eref, ehref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, None, h=h0, return_state=True, silu=True)
+    for k, (fused, ema) in enumerate(outs):
+        assert rel_l2(fused["y"].float(), yref.transpose(1, 2)) < 1e-2, k
+        assert torch.equal(fused["count"].cpu(), cnt)
+        assert rel_l2(fused["mean"], mean) < 1e-4 and rel_l2(fused["var"], var) < 1e-3, k
+        e = ema[0] if want_state else ema
+        assert rel_l2(e.float(), eref) < 1e-2, k
+        if want_state:
+            assert rel_l2(fused["h"], href) < 1e-2 and rel_l2(ema[1], ehref) < 1e-2, k
+    # the two implementations agree with each other well inside the bf16 tolerance
+    assert rel_l2(outs[0][0]["y"].float(), outs[1][0]["y"].float()) < 1e-2
+    assert _lib.device_error() == 0
