@@ -386,6 +386,7 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
+    ap.add_argument("--length", type=int, default=0, help="override the sequence length (profiling aid)")
     ap.add_argument("--e2e-slice", type=int, default=8)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -393,6 +394,8 @@ def main():
     B, L, D, dtype_name = WORKLOADS[args.workload]
     if args.batch:
         B = args.batch
+    if args.length:
+        L = args.length
     if args.impl == "reference":
         run_reference(args, B, L, D, dtype_name)
     else:

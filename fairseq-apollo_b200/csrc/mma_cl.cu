@@ -45,20 +45,41 @@ constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [64][16] f32 scrat
 constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // [kStages] u64
 constexpr int kSmemBytes = kOffBar + 64 + 1024;            // + alignment slack
 
+// d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
+                                         uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], float a0, float a1, float a2, float a3, float b0,
-                                         float b1) {
+                                         float b1, float c0, float c1, float c2, float c3) {
   asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)), "r"(__float_as_uint(a2)),
-        "r"(__float_as_uint(a3)), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
+        "r"(__float_as_uint(a3)), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)), "f"(c0), "f"(c1),
+        "f"(c2), "f"(c3));
+}
+// shared-memory accesses by 32-bit shared address (keeps them LDS/STS rather than generic)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 // two fp32 -> packed bf16x2 (lo in the low half)
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -104,6 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
   float* Kp = reinterpret_cast<float*>(sm + kOffKp);
   uint64_t* full = reinterpret_cast<uint64_t*>(sm + kOffBar);
 
+  const uint32_t sm_s = smem_u32(sm);
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, q = lane & 3;
@@ -234,10 +256,11 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
     const int s = i % kStages;
     const uint32_t ph = (uint32_t)((i / kStages) & 1);
     unsigned char* stage = sm + kOffStages + s * kStageBytes;
+    const uint32_t stage_s = sm_s + kOffStages + s * kStageBytes;
     const bool ok = mbar_wait(&full[s], ph);
     uint4 v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const uint4*>(stage + vec_off(g, toff[j], warp));
+    for (int j = 0; j < 8; ++j) v[j] = lds128(stage_s + vec_off(g, toff[j], warp));
     float invn[8];
     if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
@@ -261,14 +284,13 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
         if (kNorm) {
           float S1[8], S2[8];
           {
-            float F[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_tf32(F, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f);
-            mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f);
+            float E[4], F[4], D0[4], D1[4], T[4];
+            mma_tf32(E, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
             const float c0 = s1c[e], c1 = s1c[e] + F[0];
-            float D0[4] = {c0, c0, c1, c1}, D1[4] = {c0, c0, c1, c1};
-            mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1);
-            mma_tf32(D1, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f);
-            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1);
+            mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, c0, c0, c1, c1);
+            mma_tf32(T, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, c0, c0, c1, c1);
+            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, T[0], T[1], T[2], T[3]);
             s1c[e] = c1 + F[2];
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
@@ -277,19 +299,19 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
             float sq[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) sq[j] = xf[j] * xf[j];
-            float F[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_tf32(F, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f);
-            mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f);
+            float E[4], F[4], D0[4], D1[4], T[4];
+            mma_tf32(E, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
             const float c0 = s2c[e], c1 = s2c[e] + F[0];
-            float D0[4] = {c0, c0, c1, c1}, D1[4] = {c0, c0, c1, c1};
-            mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1);
-            mma_tf32(D1, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f);
-            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1);
+            mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, c0, c0, c1, c1);
+            mma_tf32(T, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, c0, c0, c1, c1);
+            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, T[0], T[1], T[2], T[3]);
             s2c[e] = c1 + F[2];
             S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
             S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
           }
-          const float2 wb = *reinterpret_cast<const float2*>(WB + ch * 2);
+          const uint2 wbu = lds64(sm_s + kOffWB + ch * 8);
+          const float2 wb = make_float2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float mean = S1[j] * invn[j];
@@ -304,15 +326,18 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
         // A fragment of xn: a0 (row g: t = 2q, 2q+1), a1 (row g+8), a2 (row g: t = 2q+8, 2q+9), a3 (row g+8)
         const uint32_t xa0 = pack_bf16(xn[0], xn[1]), xa2 = pack_bf16(xn[2], xn[3]);
         const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
-        const uint2 tr = make_uint2(Tc[(ch * 2 + 0) * 32 + lane], Tc[(ch * 2 + 1) * 32 + lane]);
-        const uint4 pr = Pc[ch * 32 + lane];
-        const uint4 gr = Gc[ch * 32 + lane];
-        const float2 aq0 = *reinterpret_cast<const float2*>(Ac + ch * 16 + 2 * q);
-        const float2 aq1 = *reinterpret_cast<const float2*>(Ac + ch * 16 + 8 + 2 * q);
+        const uint2 tr = make_uint2(lds32(sm_s + kOffT + ((ch * 2 + 0) * 32 + lane) * 4),
+                                    lds32(sm_s + kOffT + ((ch * 2 + 1) * 32 + lane) * 4));
+        const uint4 pr = lds128(sm_s + kOffP + (ch * 32 + lane) * 16);
+        const uint4 gr = lds128(sm_s + kOffG + (ch * 32 + lane) * 16);
+        const uint2 aq0u = lds64(sm_s + kOffA + (ch * 16 + 2 * q) * 4);
+        const uint2 aq1u = lds64(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 4);
+        const float2 aq0 = make_float2(__uint_as_float(aq0u.x), __uint_as_float(aq0u.y));
+        const float2 aq1 = make_float2(__uint_as_float(aq1u.x), __uint_as_float(aq1u.y));
         // local state contributions of the two chunks
-        float H0[4] = {0.f, 0.f, 0.f, 0.f}, H1[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y);  // poles 2q, 2q+1
-        mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w);  // poles 8+2q, 9+2q
+        float H0[4], H1[4];
+        mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y, 0.f, 0.f, 0.f, 0.f);  // poles 2q, 2q+1
+        mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
         // states entering chunk 0 (= carried) and chunk 1, and the new carry
         const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
         float hs1[4];
@@ -326,11 +351,11 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
         hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
         const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
         const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
-        float Y0[4] = {0.f, 0.f, 0.f, 0.f}, Y1[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_bf16(Y0, ha0, ha1, ha2, ha3, gr.x, gr.y);
-        mma_bf16(Y1, ha0, ha1, ha2, ha3, gr.z, gr.w);
-        mma_bf16(Y0, xa0, xa1, xa2, xa3, tr.x, 0u);
-        mma_bf16(Y1, xa0, xa1, xa2, xa3, tr.y, tr.x);
+        float Y0[4], Y1[4], Z0[4], Z1[4];
+        mma_bf16(Z0, ha0, ha1, ha2, ha3, gr.x, gr.y, 0.f, 0.f, 0.f, 0.f);
+        mma_bf16(Z1, ha0, ha1, ha2, ha3, gr.z, gr.w, 0.f, 0.f, 0.f, 0.f);
+        mma_bf16(Y0, xa0, xa1, xa2, xa3, tr.x, 0u, Z0[0], Z0[1], Z0[2], Z0[3]);
+        mma_bf16(Y1, xa0, xa1, xa2, xa3, tr.y, tr.x, Z1[0], Z1[1], Z1[2], Z1[3]);
         yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
         if (a.silu) {
@@ -345,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(stage + vec_off(g, toff[j], warp)) = v[j];
+    for (int j = 0; j < 8; ++j) sts128(stage_s + vec_off(g, toff[j], warp), v[j]);
     fence_proxy_async();
     if (__syncthreads_or(!ok)) break;
     if (tid == 0) {
