@@ -16,7 +16,7 @@ namespace mega {
 extern std::atomic<uint64_t> g_launches;
 extern thread_local char g_cuda_err[256];
 extern std::atomic<int> g_options[8];
-enum { OPT_DISABLE_STREAM = 0, OPT_DISABLE_MMA = 1 };
+enum { OPT_DISABLE_STREAM = 0, OPT_DISABLE_MMA = 1, OPT_MMA_TILE = 2 };
 int check_launch(const char* what);
 
 template <typename... KArgs, typename... Args>

@@ -1,15 +1,18 @@
 // Tensor-core variant of the fused TimestepNorm -> causal EMA (and of the EMA alone) for bf16
 // activations with contiguous channels and no padding mask.
 //
-// Work split.  A CTA owns 64 adjacent channels of 8 sequences and walks time in steps of 32
-// positions.  Warp w owns the 16-byte column group w (8 channels).  For one channel the 8
-// sequences x 2 consecutive 16-position chunks of a step form the 16 rows of warp-level MMAs
-// (row g = sequence g, chunk 0; row g + 8 = sequence g, chunk 1), so every carry between
-// chunks stays inside one thread and no cross-lane scan is needed.
+// Work split.  A CTA owns kCg column groups (8 channels = 16 bytes each; kCg = 8 or 7) of 8
+// sequences and walks time in steps of 32 positions.  Warp w owns column group w.  For one
+// channel the 8 sequences x 2 consecutive 16-position chunks of a step form the 16 rows of
+// warp-level MMAs (row g = sequence g, chunk 0; row g + 8 = sequence g, chunk 1), so every carry
+// between chunks stays inside one thread and no cross-lane scan is needed.  The 56-channel tile
+// exists for load balance: one CTA fits per SM, and e.g. 2048 channels x 64 sequences give
+// 37 x 8 = 296 CTAs = exactly two waves over 148 SMs (64-channel tiles leave 40 SMs idle in the
+// second wave).
 //
 // Math per channel and step (h = pole states, C = 16):
 //   TimestepNorm : prefix sums of x and x^2 inside each chunk are products with 0/1 matrices
-//                  (tf32 MMAs; x is bf16 and x^2 has 16 significant bits, both exact in tf32);
+//                  (tf32 MMAs; x is exact in tf32, x^2 is truncated to 11 significant bits);
 //                  the running totals enter as the accumulator input.  mean/var follow from
 //                  the sums, xn = (x - mean) * rstd * w + b.
 //   EMA          : y = T xn + G h_start   (T: 16x16 lower-triangular Toeplitz of the kernel
@@ -27,23 +30,25 @@ namespace mega {
 
 namespace {
 
-constexpr int kCh = 64;      // channels per CTA
-constexpr int kSeq = 8;      // sequences per CTA
-constexpr int kStep = 32;    // positions per step (2 chunks of 16)
+constexpr int kSeq = 8;    // sequences per CTA
+constexpr int kStep = 32;  // positions per step (2 chunks of 16)
 constexpr int kStages = 3;
-constexpr int kThreads = 256;
-constexpr int kStageBytes = kSeq * kStep * kCh * 2;  // 32 KiB
 
-// shared memory map (bytes, from a 1024-aligned base)
-constexpr int kOffStages = 0;
-constexpr int kOffT = kOffStages + kStages * kStageBytes;  // [64][2][32] u32
-constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [64][32] uint4
-constexpr int kOffG = kOffP + kCh * 4 * 32 * 4;            // [64][32] uint4
-constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [64][16] f32  (q^16)
-constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [64][2] f32
-constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [64][16] f32 scratch: kernel taps
-constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // [kStages] u64
-constexpr int kSmemBytes = kOffBar + 64 + 1024;            // + alignment slack
+template <int kCg>
+struct Cfg {
+  static constexpr int kCh = kCg * 8;                       // channels per CTA
+  static constexpr int kRow = kCg * 16;                     // bytes per tile row
+  static constexpr int kStageBytes = kSeq * kStep * kRow;   // 32 KiB (kCg = 8) / 28 KiB (kCg = 7)
+  static constexpr int kOffStages = 0;
+  static constexpr int kOffT = kOffStages + kStages * kStageBytes;  // [kCh][2][32] u32
+  static constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [kCh][32] uint4
+  static constexpr int kOffG = kOffP + kCh * 4 * 32 * 4;            // [kCh][32] uint4
+  static constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [kCh][16] f32  (q^16)
+  static constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [kCh][2] f32
+  static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
+  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages]
+  static constexpr int kSmemBytes = kOffBar + 128 + 1024;           // + alignment slack
+};
 
 // d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -104,17 +109,26 @@ __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
-// Byte offset of the 16-byte vector (sequence, position, column group) inside a stage written by
-// TMA with the 128-byte swizzle: chunk index XOR (row mod 8), rows are 128 bytes.
+// Byte offset of the 16-byte vector (sequence, position, column group) inside a stage.  kCg = 8:
+// rows are 128 bytes and TMA applies its 128-byte swizzle (chunk index XOR row mod 8); kCg = 7:
+// rows are 112 bytes, unswizzled (the odd pitch already staggers the banks).
+template <int kCg>
 __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
   const int row = seq * kStep + t;
-  return (uint32_t)(row * 128 + ((cg ^ (row & 7)) << 4));
+  if (kCg == 8) return (uint32_t)(row * 128 + ((cg ^ (row & 7)) << 4));
+  return (uint32_t)(row * (kCg * 16) + (cg << 4));
 }
 
-template <bool kNorm>
-__global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx,
-                                                                  const __grid_constant__ CUtensorMap tmy,
-                                                                  StreamArgs a) {
+template <bool kNorm, int kCg>
+__global__ void __launch_bounds__(kCg * 32, 1)
+    tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
+                       StreamArgs a) {
+  using C = Cfg<kCg>;
+  constexpr int kCh = C::kCh;
+  constexpr int kThreads = kCg * 32;
+  constexpr int kStageBytes = C::kStageBytes;
+  constexpr int kOffStages = C::kOffStages, kOffT = C::kOffT, kOffP = C::kOffP, kOffG = C::kOffG;
+  constexpr int kOffA = C::kOffA, kOffWB = C::kOffWB, kOffKp = C::kOffKp, kOffBar = C::kOffBar;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint32_t* Tc = reinterpret_cast<uint32_t*>(sm + kOffT);
@@ -260,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
     const bool ok = mbar_wait(&full[s], ph);
     uint4 v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = lds128(stage_s + vec_off(g, toff[j], warp));
+    for (int j = 0; j < 8; ++j) v[j] = lds128(stage_s + vec_off<kCg>(g, toff[j], warp));
     float invn[8];
     if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
@@ -370,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sts128(stage_s + vec_off(g, toff[j], warp), v[j]);
+    for (int j = 0; j < 8; ++j) sts128(stage_s + vec_off<kCg>(g, toff[j], warp), v[j]);
     fence_proxy_async();
     if (__syncthreads_or(!ok)) break;
     if (tid == 0) {
@@ -415,6 +429,29 @@ __global__ void __launch_bounds__(kThreads, 1) tsn_ema_mma_kernel(const __grid_c
   }
 }
 
+template <bool kNorm, int kCg>
+static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
+                           long long ysl, const StreamArgs& a, cudaStream_t s) {
+  using C = Cfg<kCg>;
+  const CUtensorMapSwizzle sw = kCg == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUtensorMap tx, ty;
+  if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
+  if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, sw)) return false;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg>;
+  static std::once_flag once;
+  static bool attr_ok = true;
+  std::call_once(once, [&] {
+    attr_ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) == cudaSuccess;
+  });
+  if (!attr_ok) {
+    cudaGetLastError();
+    return false;
+  }
+  dim3 grid((a.D + C::kCh - 1) / C::kCh, (a.B + kSeq - 1) / kSeq);
+  launch(kern, grid, dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, a);
+  return true;
+}
+
 }  // namespace
 
 // Envelope: bf16, channel stride 1, no padding mask, ndim <= 16, no normalised-copy output,
@@ -427,27 +464,22 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   if (a_in.N > 16 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
   if (a_in.h_out && (a_in.L % kStep) != 0) return false;
   if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
-  CUtensorMap tx, ty;
-  if (!make_tensor_map_3d(&tx, dtype, x, a_in.D, a_in.L, a_in.B, xsl, xsb, kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B))
-    return false;
-  if (!make_tensor_map_3d(&ty, dtype, y, a_in.D, a_in.L, a_in.B, ysl, ysb, kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B))
-    return false;
-  static std::once_flag once;
-  static bool attr_ok = true;
-  std::call_once(once, [&] {
-    attr_ok = cudaFuncSetAttribute(tsn_ema_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess &&
-              cudaFuncSetAttribute(tsn_ema_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
-  });
-  if (!attr_ok) {
-    cudaGetLastError();
-    return false;
+  // Tile width: 64 channels, or 56 when that fills the 148 SMs in fewer or fuller waves
+  // (one CTA per SM; e.g. D = 2048 with 64 sequences: 37 x 8 = 296 CTAs = two full waves).
+  const long long seq_groups = (a_in.B + kSeq - 1) / kSeq;
+  auto waves_cost = [&](int ch) -> double {
+    const long long ctas = ((a_in.D + ch - 1) / ch) * seq_groups;
+    const long long waves = (ctas + 147) / 148;
+    return (double)waves * ch;  // time ~ waves x work per CTA
+  };
+  const int opt = g_options[OPT_MMA_TILE].load();
+  const bool use7 = opt == 7 || (opt != 8 && waves_cost(56) < waves_cost(64));
+  if (norm) {
+    return use7 ? launch_variant<true, 7>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                : launch_variant<true, 8>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
   }
-  dim3 grid((a_in.D + kCh - 1) / kCh, (a_in.B + kSeq - 1) / kSeq);
-  if (norm)
-    launch(tsn_ema_mma_kernel<true>, grid, dim3(kThreads), (size_t)kSmemBytes, (void*)s, tx, ty, a_in);
-  else
-    launch(tsn_ema_mma_kernel<false>, grid, dim3(kThreads), (size_t)kSmemBytes, (void*)s, tx, ty, a_in);
-  return true;
+  return use7 ? launch_variant<false, 7>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+              : launch_variant<false, 8>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
 }
 
 cudaError_t mma_cl_read_device_error(int* v, bool reset) { return read_device_error(v, reset); }
