@@ -11,10 +11,13 @@
 // second wave).
 //
 // Math per channel and step (h = pole states, C = 16):
-//   TimestepNorm : prefix sums of x and x^2 inside each chunk are products with 0/1 matrices
-//                  (tf32 MMAs; x is exact in tf32, x^2 is truncated to 11 significant bits);
-//                  the running totals enter as the accumulator input.  mean/var follow from
-//                  the sums, xn = (x - mean) * rstd * w + b.
+//   TimestepNorm : with c the running mean at the start of the step and d = x - c, the prefix
+//                  sums of d and d^2 inside each chunk are products with 0/1 matrices (tf32
+//                  MMAs); the running second moment enters as the accumulator input.  Centring
+//                  keeps mean^2 small against the variance, so the tf32 truncation of the MMA
+//                  inputs (11 significant bits) only costs ~2^-11 of the variance.  Then
+//                  u = sum(d)/n, mean = c + u, var = (M2 + sum(d^2))/n - u^2,
+//                  xn = (d - u) * rstd * w + b.
 //   EMA          : y = T xn + G h_start   (T: 16x16 lower-triangular Toeplitz of the kernel
 //                  k[l] = sum_n p g q^l, omega folded into k[0]; G[t][n] = g q^(t+1))
 //                  h_local = P xn          (P[n][t] = p q^(15-t));  h_next = q^16 h + h_local.
@@ -53,14 +56,14 @@ struct Cfg {
 // d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
 __device__ __forceinline__ void mma_tf32(float (&d)[4], float a0, float a1, float a2, float a3, float b0,
                                          float b1, float c0, float c1, float c2, float c3) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)), "r"(__float_as_uint(a2)),
@@ -236,7 +239,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   const int bseq = b0 + g;
   const bool seq_ok = bseq < a.B;
   float hc[8][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
-  float s1c[8], s2c[8];
+  float mu_run[8], m2_run[8], s1_run[8];  // running mean, sum of squared deviations, sum of x
   float nbase = 1.f;
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
@@ -247,13 +250,15 @@ __global__ void __launch_bounds__(kCg * 32, 1)
       const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
       hc[e][k] = (ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
     }
-    s1c[e] = 0.f;
-    s2c[e] = 0.f;
+    mu_run[e] = 0.f;
+    m2_run[e] = 0.f;
+    s1_run[e] = 0.f;
     if (kNorm && ok) {
       const float c0 = (float)a.prev_count[bseq];
       const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
-      s1c[e] = c0 * mu;
-      s2c[e] = c0 * fmaf(mu, mu, vv);
+      mu_run[e] = mu;
+      m2_run[e] = c0 * vv;
+      s1_run[e] = c0 * mu;
     }
   }
   if (kNorm && seq_ok) nbase = (float)a.prev_count[bseq] + 1.f;
@@ -276,10 +281,14 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = lds128(stage_s + vec_off<kCg>(g, toff[j], warp));
     float invn[8];
+    float inv_end = 0.f, n_end = 1.f;
+    const bool tail = (i + 1) * kStep > L;
     if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
 #pragma unroll
       for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(nb_f + (float)toff[j]);
+      n_end = nb_f - 1.f + (float)min(kStep, L - i * kStep);  // count after this step
+      inv_end = rcp_fast(n_end);
     }
 #pragma unroll
     for (int pp = 0; pp < 4; ++pp) {
@@ -296,42 +305,60 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         }
         float xn[8];
         if (kNorm) {
+          const float cm = mu_run[e];
           float S1[8], S2[8];
-          {
+          float tot1, tot2;
+          {  // sum of x: exact (bf16 inputs, fp32 accumulation); carry = count * running mean
             float E[4], F[4], D0[4], D1[4], T[4];
             mma_tf32(E, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            const float c0 = s1c[e], c1 = s1c[e] + F[0];
+            const float c0 = s1_run[e], c1 = s1_run[e] + F[0];
             mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, c0, c0, c1, c1);
             mma_tf32(T, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, c0, c0, c1, c1);
             mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, T[0], T[1], T[2], T[3]);
-            s1c[e] = c1 + F[2];
+            tot1 = c1 + F[2];
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
-          {
+          float dv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dv[j] = xf[j] - cm;
+          {  // sum of (x - c)^2 on top of the running sum of squared deviations
             float sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = xf[j] * xf[j];
+            for (int j = 0; j < 8; ++j) sq[j] = dv[j] * dv[j];
             float E[4], F[4], D0[4], D1[4], T[4];
             mma_tf32(E, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            const float c0 = s2c[e], c1 = s2c[e] + F[0];
+            const float c0 = m2_run[e], c1 = m2_run[e] + F[0];
             mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, c0, c0, c1, c1);
             mma_tf32(T, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, c0, c0, c1, c1);
             mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, T[0], T[1], T[2], T[3]);
-            s2c[e] = c1 + F[2];
+            tot2 = F[0] + F[2];
             S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
             S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
           }
+          if (tail) {
+            // positions past the end hold x = 0, i.e. d = -c: take their squares (as the MMA saw
+            // them, truncated to tf32) back out of the step total
+            const float c2 = __uint_as_float(__float_as_uint(cm * cm) & 0xffffe000u);
+            tot2 -= (float)(kStep - (L - i * kStep)) * c2;
+          }
+          // running statistics after this step: the new mean, and the squared deviations moved
+          // from the old centre c to it (sum (x-c)^2 = sum (x-m)^2 + n (m-c)^2)
+          s1_run[e] = tot1;
+          const float mnew = tot1 * inv_end;
+          const float shift = mnew - cm;
+          mu_run[e] = mnew;
+          m2_run[e] = fmaf(-shift * shift, n_end, m2_run[e] + tot2);
           const uint2 wbu = lds64(sm_s + kOffWB + ch * 8);
           const float2 wb = make_float2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float mean = S1[j] * invn[j];
-            const float ve = fmaxf(fmaf(S2[j], invn[j], eps) - mean * mean, eps);
+            const float u = fmaf(S1[j], invn[j], -cm);  // mean - c
+            const float ve = fmaxf(fmaf(S2[j], invn[j], eps) - u * u, eps);
             const float sc = rsqrt_fast(ve) * wb.x;
-            xn[j] = fmaf(xf[j] - mean, sc, wb.y);
+            xn[j] = fmaf(dv[j] - u, sc, wb.y);
           }
         } else {
 #pragma unroll
@@ -407,9 +434,8 @@ __global__ void __launch_bounds__(kCg * 32, 1)
       const int d = d0 + warp * 8 + e;
       if (kNorm && d < a.D) {
         const float n = (float)a.prev_count[bseq] + (float)L;
-        const float mean = s1c[e] / n;
-        a.mean_out[(size_t)bseq * a.D + d] = mean;
-        a.var_out[(size_t)bseq * a.D + d] = fmaxf(s2c[e] / n - mean * mean, 0.f);
+        a.mean_out[(size_t)bseq * a.D + d] = mu_run[e];
+        a.var_out[(size_t)bseq * a.D + d] = fmaxf(m2_run[e] / n, 0.f);
       }
     }
     if (kNorm && blockIdx.x == 0 && warp == 0) a.count_out[bseq] = a.prev_count[bseq] + L;

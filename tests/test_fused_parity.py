@@ -197,3 +197,26 @@ def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
     # the two implementations agree with each other well inside the bf16 tolerance
     assert rel_l2(outs[0][0]["y"].float(), outs[1][0]["y"].float()) < 1e-2
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("offset,scale", [(5.0, 0.3), (-20.0, 2.0), (0.0, 30.0)])
+def test_tensor_core_path_offset_data(offset, scale):
+    """Channels whose mean is large against their spread: the tensor-core TimestepNorm keeps its
+    sums centred on the running mean, so the normalised output and the statistics stay accurate."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(77)
+    bsz, length, dim = 8, 512, 64
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * scale + offset).to(torch.bfloat16)
+    pc = torch.full((bsz,), 2, dtype=torch.int64)
+    pm = torch.full((bsz, dim), offset)
+    pv = torch.full((bsz, dim), scale * scale)
+    gamma, beta = torch.ones(dim), torch.zeros(dim)
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[:4]
+    yref = O.ema_forward_recurrence(xn.transpose(1, 2), *prm).transpose(1, 2)
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    before = M.launch_count()
+    res = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                p, q, g, prm[4].cuda())
+    assert rel_l2(res["y"].float(), yref) < 1e-2
+    assert rel_l2(res["mean"], mean) < 1e-4 and rel_l2(res["var"], var) < 2e-3
