@@ -184,6 +184,24 @@ def run_reference(args, B, L, D, dtype_name):
     print(json.dumps(line), flush=True)
 
 
+def batch_shard(batch, rank, world):
+    """Contiguous [lo, hi) slice of the batch owned by `rank` (strong scaling)."""
+    base, rem = divmod(batch, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def job_throughput(tokens_per_rank, world, steps, total_ms):
+    """Whole-job tokens/s: all ranks' tokens over the slowest rank's time."""
+    return tokens_per_rank * world * steps / (total_ms * 1e-3)
+
+
+# DRAM bytes per token of the tensor-core kernel from its ncu capture (profiles/
+# tsn_ema_mma_kernel__b32_l4096_full.md: 1036.3 MB for 32 x 4096 tokens of 2048 bf16 channels);
+# it scales with the tokens of a launch.
+NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = 1036.28e6 / (32 * 4096)
+
+
 def workload_name(args, B, L, D, dtype_name):
     return "%s: TimestepNorm+MultiHeadEMA causal fwd, B=%d L=%d D=%d %s (per rank)" % (
         args.workload, B, L, D, dtype_name)
@@ -205,8 +223,8 @@ def run_ours(args, B, L, D, dtype_name):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     if args.scaling == "strong":
-        assert B % world == 0
-        Bl = B // world
+        lo, hi = batch_shard(B, rank, world)
+        Bl = hi - lo
     else:
         Bl = B
     dtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
@@ -275,8 +293,7 @@ def run_ours(args, B, L, D, dtype_name):
     if world > 1:
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
     total_ms = float(tm.item())
-    tokens_per_step = Bl * L * world
-    value = tokens_per_step * args.steps / (total_ms * 1e-3)
+    value = job_throughput(Bl * L, world, args.steps, total_ms)
 
     # ---- end-to-end through host buffers: pinned host x -> device -> kernel -> pinned host y
     # The per-rank batch streams through in slices on three streams (H2D, compute, D2H).
@@ -362,12 +379,15 @@ def run_ours(args, B, L, D, dtype_name):
                        "global_batch": Bl * world, "l2": "inputs (%.1f GiB per rank) exceed the 126 MB L2"
                        % (Bl * L * D * es / 2**30), "parallelism": "batch shards, no data-path collective"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak,
+                         "traffic": (NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 * Bl * L
+                                     if (D == 2048 and dtype_name == "bf16") else None),
+                         "peak_kind": peak_kind,
                          "kernel": "tsn_ema fused forward", "algorithmic_bytes_per_launch": alg_bytes,
                          "kernel_ms": kern_ms},
             "cpu_baseline": cpu,
-            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_dir,
-                    "d2h_bytes_per_step": bytes_dir, "steps": e2e_steps,
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_dir * world,
+                    "d2h_bytes_per_step": bytes_dir * world, "steps": e2e_steps,
                     "note": "pinned host slices of %d sequences streamed on 3 streams" % sl},
             "gpu_launches": int(launches),
             "clocks": clocks,
