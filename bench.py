@@ -30,11 +30,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (B, L, D, dtype)
+    # name: (B, L, D, dtype)   fused TimestepNorm -> causal EMA
     "c4": (64, 32768, 2048, "bf16"),
     "c1": (16, 4096, 1024, "bf16"),
     "tiny": (4, 2048, 256, "bf16"),
 }
+# side workloads (BASELINE configs 0, 2 and the decode half of config 4): own JSON line, N=1 only
+AUX_WORKLOADS = ("c0", "c2", "decode")
 NDIM = 16
 FALLBACK_HBM_GBS = 6650.0
 
@@ -397,13 +399,88 @@ def run_ours(args, B, L, D, dtype_name):
         dist.destroy_process_group()
 
 
+def run_aux(args):
+    """Configs 0 and 2 and the 1024-step decode loop: CUDA-event timing of the module calls."""
+    import torch
+    import fairseq_apollo_b200 as M
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(1234)
+    peak, peak_kind = hbm_peak()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, steps, warm):
+        for _ in range(warm):
+            fn()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps)]
+        for i in range(steps):
+            flush.zero_()
+            ev[2 * i].record()
+            fn()
+            ev[2 * i + 1].record()
+        torch.cuda.synchronize()
+        ts = sorted(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(steps))
+        return ts[len(ts) // 2]
+
+    steps, warm = max(args.steps, 5), max(args.warmup, 3)
+    l0 = M.launch_count()
+    with torch.no_grad():
+        if args.workload == "c0":
+            L, B, D = 1024, 8, 512
+            x = torch.randn(L, B, D, generator=gen).to(dev)           # time-major, viewed as (B, D, L)
+            ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+            mask = torch.zeros(B, L, dtype=torch.bool)
+            for b in range(B):
+                n = int(torch.rand((), generator=gen).item() * 0.25 * L)
+                if n:
+                    mask[b, L - n:] = True
+            mask = mask.to(dev)
+            ms = timed(lambda: ema.forward_time_major(x, mask), steps, warm)
+            tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 4, "c0: MultiHeadEMA fwd fp32 L=1024 B=8 D=512, 0-25% padding", "f32"
+        elif args.workload == "c2":
+            L, B, D = 16384, 32, 256
+            x = torch.randn(B, D, L, generator=gen).to(dev)
+            ema = M.MultiHeadEMA(D, ndim=NDIM, bidirectional=True).to(dev).eval()
+            norm = M.SequenceNorm(D).to(dev).eval()
+            mask = torch.zeros(B, L, dtype=torch.bool)
+            for b in range(B):
+                n = int(torch.rand((), generator=gen).item() * 0.5 * L)
+                if n:
+                    mask[b, L - n:] = True
+            mask = mask.to(dev)
+            ms = timed(lambda: ema(norm(x, mask), mask), steps, warm)
+            tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 4, "c2: SequenceNorm + bidirectional MultiHeadEMA fwd fp32 L=16384 B=32 D=256, 0-50% padding", "f32"
+        else:  # decode: 1024 single-token steps, state seeded from a 4096-token prefix
+            B, D, T = 64, 2048, 1024
+            ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+            norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+            st = {}
+            M.timestep_norm_ema(norm, ema, torch.randn(B, 4096, D, generator=gen).to(dev).bfloat16(), None, st)
+            xs = torch.randn(T, B, 1, D, generator=gen).to(dev).bfloat16()
+
+            def loop():
+                for t in range(T):
+                    M.timestep_norm_ema(norm, ema, xs[t], None, st)
+            ms = timed(loop, 3, 1) / T
+            tokens, bytes_alg, name, dt = B, 2.0 * B * D * NDIM * 4 + 2.0 * B * D * 2, "decode: TimestepNorm+EMA single-token step, B=64 D=2048 ndim=16, state fp32", "bf16"
+    launches = M.launch_count() - l0
+    line = {"metric": "mega_ema_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": name, "ndim": NDIM, "l2": "256 MiB scratch written between timed calls"},
+            "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": bytes_alg / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind},
+            "gpu_launches": int(launches)}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
     ap.add_argument("--length", type=int, default=0, help="override the sequence length (profiling aid)")
@@ -411,6 +488,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload in AUX_WORKLOADS:
+        return run_aux(args)
     B, L, D, dtype_name = WORKLOADS[args.workload]
     if args.batch:
         B = args.batch

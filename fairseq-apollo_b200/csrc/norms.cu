@@ -3,6 +3,8 @@
 // TimestepNorm is a causal cumulative normalisation: the statistics at step t are the Welford
 // moments of the unmasked prefix (plus a prior that acts as prev_count pseudo-samples).
 // SequenceNorm normalises with the masked moments of the whole sequence.
+#include <mutex>
+
 #include "common.cuh"
 #include "stream_cl.cuh"
 
@@ -348,7 +350,16 @@ extern "C" int mega_sequence_norm_fwd(const void* x, void* y, int dtype, int B, 
   } else {
     if ((long long)B * G > 0x7fffffffLL) return MEGA_ERR_SHAPE;
     const long long n = (long long)(D / G) * L;
-    const int cap = 40 * 1024 / 4;  // fits the default dynamic shared-memory limit
+    // cache the segment in shared memory when it fits (opt-in limit, leaves room for 1 KB of statics)
+    static bool attr_ok = false;
+    static std::once_flag once;
+    std::call_once(once, [] {
+      attr_ok = cudaFuncSetAttribute(sqn_segment_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+                cudaFuncSetAttribute(sqn_segment_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess &&
+                cudaFuncSetAttribute(sqn_segment_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess;
+      cudaGetLastError();
+    });
+    const int cap = (attr_ok ? 200 : 40) * 1024 / 4;
     const int cache_elems = n <= cap ? (int)n : 0;
     MEGA_DISPATCH_DTYPE(dtype, launch(sqn_segment_kernel<T>, (unsigned)(B * G), 256,
                                       (size_t)cache_elems * sizeof(float), stream, a, cache_elems));
