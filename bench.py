@@ -461,10 +461,24 @@ def run_aux(args):
             def loop():
                 for t in range(T):
                     M.timestep_norm_ema(norm, ema, xs[t], None, st)
-            ms = timed(loop, 3, 1) / T
+            ms_module = timed(loop, 3, 1) / T
+            # the same step captured once in a CUDA graph and replayed (device-side cost of a step)
+            sx = xs[0].clone()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                M.timestep_norm_ema(norm, ema, sx, None, st)
+
+            def replay():
+                for _ in range(T):
+                    gr.replay()
+            ms = timed(replay, 3, 1) / T
+            extra = {"module_call_us_per_step": ms_module * 1e3, "graph_replay_us_per_step": ms * 1e3}
             tokens, bytes_alg, name, dt = B, 2.0 * B * D * NDIM * 4 + 2.0 * B * D * 2, "decode: TimestepNorm+EMA single-token step, B=64 D=2048 ndim=16, state fp32", "bf16"
     launches = M.launch_count() - l0
-    line = {"metric": "mega_ema_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+    if args.workload != "decode":
+        extra = None
+    line = {"extra": extra, "metric": "mega_ema_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
             "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dt, "data": "synthetic",
             "config": {"workload": name, "ndim": NDIM, "l2": "256 MiB scratch written between timed calls"},

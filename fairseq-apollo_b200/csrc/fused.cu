@@ -112,9 +112,100 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
   }
 }
 
+// Single-token decode step of the fused pair: one thread per (sequence, channel) updates the
+// TimestepNorm statistics and the pole states in place and emits one output element.
+template <typename T, int NP>
+__global__ void __launch_bounds__(128) tsn_ema_step_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                           T* __restrict__ xn_out, int B, int D, int N,
+                                                           long long* count, float* mean, float* var,
+                                                           const float* __restrict__ gamma,
+                                                           const float* __restrict__ beta, float eps,
+                                                           const float* __restrict__ p, const float* __restrict__ q,
+                                                           const float* __restrict__ g,
+                                                           const float* __restrict__ omega, float* h, int silu,
+                                                           int use_norm) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)B * D) return;
+  const int d = (int)(gid % D);
+  const int b = (int)(gid / D);
+  float xv = Elem<T>::ld(x + gid);
+  if (use_norm) {
+    const long long c = count[b];
+    float m1, m2;
+    const float coef = __frcp_rn((float)(c + 1));
+    const float d1 = xv - mean[gid];
+    m1 = fmaf(coef, d1, mean[gid]);
+    const float d2 = fmaf(d1, xv - m1, -var[gid]);
+    m2 = fmaf(coef, d2, var[gid]);
+    xv = fmaf((xv - m1) * rsqrtf(m2 + eps), __ldg(gamma + d), __ldg(beta + d));
+    mean[gid] = m1;
+    var[gid] = m2;
+    if (xn_out) Elem<T>::st(xn_out + gid, xv);
+  }
+  float acc = 0.f;
+  float4* hp = reinterpret_cast<float4*>(h + gid * N);
+  if (NP >= 4 && (N & 3) == 0) {
+#pragma unroll
+    for (int n4 = 0; n4 < NP / 4; ++n4) {
+      if (n4 * 4 < N) {
+        float4 hv = hp[n4];
+        const float4 qv = __ldg(reinterpret_cast<const float4*>(q + (size_t)d * N) + n4);
+        const float4 pv = __ldg(reinterpret_cast<const float4*>(p + (size_t)d * N) + n4);
+        const float4 gv = __ldg(reinterpret_cast<const float4*>(g + (size_t)d * N) + n4);
+        hv.x = fmaf(qv.x, hv.x, pv.x * xv); hv.y = fmaf(qv.y, hv.y, pv.y * xv);
+        hv.z = fmaf(qv.z, hv.z, pv.z * xv); hv.w = fmaf(qv.w, hv.w, pv.w * xv);
+        acc = fmaf(gv.x, hv.x, acc); acc = fmaf(gv.y, hv.y, acc);
+        acc = fmaf(gv.z, hv.z, acc); acc = fmaf(gv.w, hv.w, acc);
+        hp[n4] = hv;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < NP; ++n) {
+      if (n < N) {
+        const float hn = fmaf(__ldg(q + (size_t)d * N + n), h[gid * N + n], __ldg(p + (size_t)d * N + n) * xv);
+        h[gid * N + n] = hn;
+        acc = fmaf(__ldg(g + (size_t)d * N + n), hn, acc);
+      }
+    }
+  }
+  float v = fmaf(__ldg(omega + d), xv, acc);
+  if (silu) v = siluf_(v);
+  Elem<T>::st(y + gid, v);
+}
+
+// One thread per sequence bumps the counts after the element kernel has read them.
+__global__ void tsn_count_step_kernel(long long* count, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) count[b] += 1;
+}
+
 }  // namespace mega
 
 using namespace mega;
+
+extern "C" MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D,
+                                          int64_t* count, float* mean, float* var, const float* gamma,
+                                          const float* beta, double eps, const float* p, const float* q,
+                                          const float* gamma_hat, const float* omega, int N, float* h,
+                                          unsigned flags, mega_stream_t stream) {
+  if (!x || !y || !p || !q || !gamma_hat || !omega || !h) return MEGA_ERR_NULL;
+  const int use_norm = count != nullptr;
+  if (use_norm && (!mean || !var || !gamma || !beta)) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (!aligned_to(h, 16) && (N & 3) == 0) return MEGA_ERR_ALIGN;
+  const int np = next_pow2_ndim(N);
+  const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+  const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, launch(tsn_ema_step_kernel<T, NP>, grid, 128, 0, stream,
+                                                         (const T*)x, (T*)y, (T*)xn_out, B, D, N,
+                                                         (long long*)count, mean, var, gamma, beta, (float)eps,
+                                                         p, q, gamma_hat, omega, h, silu, use_norm)));
+  if (use_norm) launch(tsn_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
+  return check_launch("tsn_ema_step");
+}
 
 extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D,
                                 int64_t xsb, int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,

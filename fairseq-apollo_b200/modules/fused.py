@@ -30,6 +30,8 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
         xn = norm(x, padding_mask, incremental_state)
         mx = move(xn.transpose(1, 2), padding_mask, incremental_state, activation).transpose(1, 2)
         return (mx, xn) if return_normed else mx
+    if (incremental_state is not None and x.size(1) == 1 and padding_mask is None and x.is_contiguous()):
+        return _decode_step(norm, move, x, incremental_state, activation, return_normed)
     prev_count, prev_mean, prev_var, nstate = norm.initial_statistics(x.size(0), incremental_state)
     p, q, g = move.coeffs()
     h_in = None
@@ -46,3 +48,46 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
         estate['prev_state'] = res["h"]
         move._set_input_buffer(incremental_state, estate)
     return (res["y"], res["xn"]) if return_normed else res["y"]
+
+
+def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):
+    """fp32, contiguous copies of everything the decode kernel reads, cached until a parameter
+    is modified (checked through the tensors' version counters)."""
+    tensors = (norm.weight, norm.bias, move.alpha, move.delta, move.beta, move.gamma, move.omega)
+    key = tuple((t.data_ptr(), t._version) for t in tensors)
+    cache = getattr(move, "_decode_cache", None)
+    if cache is None or cache[0] != key:
+        p, q, g = ops.ema_coeffs(move.alpha, move.delta, move.beta, move.gamma)
+        cache = (key, (norm.weight.detach().float() + 1.0).contiguous(), norm.bias.detach().float().contiguous(),
+                 p, q, g, move.omega.detach().float().contiguous())
+        move._decode_cache = cache
+    return cache[1:]
+
+
+def _decode_step(norm, move, x, incremental_state, activation, return_normed):
+    """Single-token step (x: (B, 1, D)): one fused kernel, running state updated in place."""
+    bsz, _, dim = x.shape
+    gamma, beta, p, q, g, omega = _fp32_params(norm, move)
+    nstate = norm._get_input_buffer(incremental_state)
+    if 'prev_mean' not in nstate:
+        count, mean, var, nstate = norm.initial_statistics(bsz, incremental_state)
+        nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'] = count.clone(), mean, var
+        norm._set_input_buffer(incremental_state, nstate)
+    for k in ('prev_mean', 'prev_var'):
+        t = nstate[k]
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            nstate[k] = t.float().contiguous()
+    estate = move._get_input_buffer(incremental_state)
+    h = estate.get('prev_state')
+    if h is None:
+        h = torch.zeros(bsz, dim, move.ndim, device=x.device, dtype=torch.float32)
+    elif h.dtype != torch.float32 or not h.is_contiguous():
+        h = h.float().contiguous()
+    estate['prev_state'] = h
+    move._set_input_buffer(incremental_state, estate)
+    y = torch.empty_like(x)
+    xn = torch.empty_like(x) if return_normed else None
+    ops.tsn_ema_step_(x.view(bsz, dim), y.view(bsz, dim), nstate['prev_count'], nstate['prev_mean'],
+                      nstate['prev_var'], gamma, beta, norm.eps, p, q, g, omega, h,
+                      silu=activation == 'silu', xn_out=None if xn is None else xn.view(bsz, dim))
+    return (y, xn) if return_normed else y

@@ -248,6 +248,19 @@ def tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma, beta, eps, p, q, 
     return res
 
 
+def tsn_ema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None):
+    """In-place decode step: x, y (B, D) contiguous; count (B) int64, mean/var (B, D) fp32 and
+    h (B, D, N) fp32 are UPDATED IN PLACE (pass count=None to skip the norm).  All parameter
+    tensors must already be fp32 and contiguous: nothing is converted or allocated here."""
+    bsz, dim = x.shape
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_tsn_ema_step(
+            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, _ptr(count), _ptr(mean), _ptr(var),
+            _ptr(gamma), _ptr(beta), float(eps), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(),
+            p.shape[1], h.data_ptr(), EMA_SILU if silu else 0, _stream()), "tsn_ema_step")
+    return y
+
+
 # --------------------------------------------------------------------------- gates
 def _rows(t):
     """View t (..., cols) as `rows` rows of `cols` elements with one row pitch; copies only

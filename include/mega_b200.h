@@ -190,6 +190,20 @@ MEGA_API int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, i
                      unsigned flags, mega_stream_t stream);
 
 /*
+ * Single-token decode step of the fused pair, all running state updated IN PLACE:
+ * count (B) int64, mean/var (B,D) fp32 (pass count = NULL to skip the TimestepNorm),
+ * h (B,D,N) fp32 pole states (16-byte aligned when N is a multiple of 4).  x, y, xn_out (B,D)
+ * contiguous activations; xn_out may be NULL.  Queues two launches (elements, then counts).
+ * Replaces: the L == 1 case of TimestepNorm.forward + BaseMovingLayer.forward with an
+ * incremental state (norm_layer/timestep_norm.py:100-139, base_moving_average.py:144-160).
+ */
+MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D,
+                               int64_t* count, float* mean, float* var,
+                               const float* gamma, const float* beta, double eps,
+                               const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                               float* h, unsigned flags, mega_stream_t stream);
+
+/*
  * Mega gate elementwise ops on (rows, D) contiguous activations.
  *   mega_gate_silu:    y = silu(a [+ b])            (b may be NULL)
  *   mega_gate_mul_silu y = a * silu(r)              (attn * silu(r) with r pre-activation)
