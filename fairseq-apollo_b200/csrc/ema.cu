@@ -6,6 +6,7 @@
 // O(L) work per row, no length cap, one pass over x.
 #include "common.cuh"
 #include "stream_cl.cuh"
+#include "rowres.cuh"
 
 namespace mega {
 
@@ -401,6 +402,15 @@ extern "C" int mega_ema_fwd(const void* x, void* y, int dtype, int B, int D, int
   a.x = x; a.y = y; a.B = B; a.D = D; a.L = L; a.N = N;
   a.xsb = xsb; a.xsd = xsd; a.xsl = xsl; a.ysb = ysb; a.ysd = ysd; a.ysl = ysl;
   a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask; a.h_in = h_in; a.h_out = h_out;
+  if (!h_in && !h_out && !(truncation > 0 && truncation < L) && xsl == 1 && ysl == 1 && xsd != 1) {
+    RowArgs ra{};
+    ra.x = x; ra.y = y; ra.B = B; ra.D = D; ra.L = L; ra.N = N;
+    ra.xsb = xsb; ra.xsd = xsd; ra.ysb = ysb; ra.ysd = ysd;
+    ra.p = p; ra.q = q; ra.g = gamma_hat; ra.omega = omega; ra.mask = pad_mask;
+    ra.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
+    ra.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+    if (rowres_try(dtype, ra, xsl, ysl, bidir, false, (cudaStream_t)stream)) return check_launch("ema_fwd(rowres)");
+  }
   if (!bidir && x != y) {
     StreamArgs sa{};
     sa.B = B; sa.L = L; sa.D = D; sa.N = N;

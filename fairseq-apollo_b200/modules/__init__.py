@@ -1,6 +1,6 @@
 from .exponential_moving_average import MultiHeadEMA
 from .timestep_norm import TimestepNorm
 from .sequence_norm import SequenceNorm
-from .fused import timestep_norm_ema
+from .fused import sequence_norm_ema, timestep_norm_ema
 
-__all__ = ["MultiHeadEMA", "TimestepNorm", "SequenceNorm", "timestep_norm_ema"]
+__all__ = ["MultiHeadEMA", "TimestepNorm", "SequenceNorm", "timestep_norm_ema", "sequence_norm_ema"]

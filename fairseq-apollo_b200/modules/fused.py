@@ -10,6 +10,7 @@ from torch import Tensor
 from .. import ops
 from ..incremental_state import require_no_grad
 from .exponential_moving_average import MultiHeadEMA
+from .sequence_norm import SequenceNorm
 from .timestep_norm import TimestepNorm
 
 
@@ -48,6 +49,23 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
         estate['prev_state'] = res["h"]
         move._set_input_buffer(incremental_state, estate)
     return (res["y"], res["xn"]) if return_normed else res["y"]
+
+
+def sequence_norm_ema(norm: SequenceNorm, move: MultiHeadEMA, x: Tensor, padding_mask: Optional[Tensor] = None,
+                      activation: Optional[str] = None):
+    """x (B, D, L) -> EMA(SequenceNorm(x)) (B, D, L): the bidirectional branch of the Mega block
+    (moving_average_gated_attention.py:298-303, 313).  One kernel, one pass over x, when the norm
+    is per channel and the rows fit the row-resident kernel; otherwise the two modules in turn."""
+    require_no_grad(x, norm.weight, move.alpha)
+    assert activation in (None, 'silu')
+    if norm.num_groups is None and move.truncation is None:
+        p, q, g = move.coeffs()
+        y = ops.sqn_ema_forward(x, norm.weight.detach().float() + 1.0, norm.bias, norm.eps, p.squeeze(-1),
+                                q.squeeze(-1), g, move.omega, padding_mask, move.bidirectional, move.shift,
+                                silu=activation == 'silu')
+        if y is not None:
+            return y
+    return move(norm(x, padding_mask), padding_mask, None, activation)
 
 
 def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):

@@ -248,6 +248,29 @@ def tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma, beta, eps, p, q, 
     return res
 
 
+def sqn_ema_forward(x, gamma, beta, eps, p, q, g, omega, padding_mask=None, bidirectional=False, shift=True,
+                    silu=False):
+    """Fused per-channel SequenceNorm -> EMA on x (B, D, L) with contiguous length.  Returns y, or
+    None when the call is outside the fused kernel's envelope (the caller then runs the two ops)."""
+    _cuda(x, gamma, beta, p, q, g, omega, padding_mask)
+    bsz, dim, length = x.shape
+    if x.stride(2) != 1:
+        return None
+    gamma, beta, p, q, g, omega = _f32c(gamma), _f32c(beta), _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
+    mask = _mask_u8(padding_mask, bsz, length)
+    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+    flags = (EMA_BIDIRECTIONAL if bidirectional else 0) | (0 if shift else EMA_NO_SHIFT) | (EMA_SILU if silu else 0)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().mega_sqn_ema_fwd(x.data_ptr(), y.data_ptr(), _dt(x), bsz, dim, length, *x.stride(), *y.stride(),
+                                         gamma.data_ptr(), beta.data_ptr(), float(eps), None, None, None,
+                                         p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), p.shape[1],
+                                         _ptr(mask), flags, _stream())
+    if rc == 7:  # MEGA_ERR_UNSUPPORTED: outside the envelope
+        return None
+    _lib.check(rc, "sqn_ema_fwd")
+    return y
+
+
 def tsn_ema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None):
     """In-place decode step: x, y (B, D) contiguous; count (B) int64, mean/var (B, D) fp32 and
     h (B, D, N) fp32 are UPDATED IN PLACE (pass count=None to skip the norm).  All parameter

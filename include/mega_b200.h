@@ -190,6 +190,24 @@ MEGA_API int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, i
                      unsigned flags, mega_stream_t stream);
 
 /*
+ * Fused per-channel SequenceNorm -> EMA (causal or bidirectional) on length-contiguous rows:
+ * x, y (B,D,L) with stride_l == 1.  norm_gamma is the EFFECTIVE scale (module weight + 1).
+ * count_out (B), mean_out / rstd_out (B,D) may be NULL.  flags as in mega_ema_fwd.  Returns
+ * MEGA_ERR_UNSUPPORTED when the row does not fit the shared-memory resident kernel (L < 512, L
+ * beyond ~27k positions bidirectional / ~54k causal, ndim > 16, stride_l != 1): callers then run
+ * mega_sequence_norm_fwd followed by mega_ema_fwd.
+ * Replaces: x = self.norm(x, padding_mask); mx = self.move(x, padding_mask) of the bidirectional
+ * branch of MovingAverageGatedAttention.forward (moving_average_gated_attention.py:298-303,313).
+ */
+MEGA_API int mega_sqn_ema_fwd(const void* x, void* y, int dtype, int B, int D, int L,
+                              int64_t x_stride_b, int64_t x_stride_d, int64_t x_stride_l,
+                              int64_t y_stride_b, int64_t y_stride_d, int64_t y_stride_l,
+                              const float* norm_gamma, const float* norm_beta, double eps,
+                              int64_t* count_out, float* mean_out, float* rstd_out,
+                              const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                              const uint8_t* pad_mask, unsigned flags, mega_stream_t stream);
+
+/*
  * Single-token decode step of the fused pair, all running state updated IN PLACE:
  * count (B) int64, mean/var (B,D) fp32 (pass count = NULL to skip the TimestepNorm),
  * h (B,D,N) fp32 pole states (16-byte aligned when N is a multiple of 4).  x, y, xn_out (B,D)

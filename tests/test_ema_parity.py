@@ -208,3 +208,55 @@ def test_module_dropin():
         assert b is None and k.shape == (12, 45)
         out, h = m.step(x, 45)
         assert rel_l2(out + x * m.omega.view(-1, 1), full) < 1e-5
+
+
+@pytest.mark.parametrize("bsz,dim,length", [(2, 5, 512), (3, 8, 1000), (1, 4, 16384), (2, 3, 4097)])
+@pytest.mark.parametrize("bidir,shift", [(False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_row_resident_length_contiguous(bsz, dim, length, bidir, shift, dtype):
+    """Length-contiguous (B, D, L) rows of >= 512 positions take the row-resident kernel (each row in
+    shared memory, segment-parallel scan); check it against the oracle and against the generic
+    kernels (a test switch disables the fast paths)."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(length + dim)
+    prm = make_ema_params(gen, dim, 16, bidirectional=bidir)
+    x = torch.randn(bsz, dim, length, generator=gen).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.4)
+    mask[0, 7] = True
+    ref = O.ema_forward_recurrence(x.float(), *prm, mask, bidirectional=bidir, shift=shift)
+    p, q, gam = _coeffs(M, prm)
+    y = M.ops.ema_forward(x.cuda(), p, q, gam, prm[4].cuda(), mask.cuda(), bidirectional=bidir, shift=shift)
+    _lib.set_option(0, 1)
+    try:
+        y_gen = M.ops.ema_forward(x.cuda(), p, q, gam, prm[4].cuda(), mask.cuda(), bidirectional=bidir, shift=shift)
+    finally:
+        _lib.set_option(0, 0)
+    assert rel_l2(y.float(), ref) < TOL[dtype]
+    assert rel_l2(y.float(), y_gen.float()) < TOL[dtype]
+
+
+@pytest.mark.parametrize("bidir", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_sequence_norm_ema(bidir, dtype):
+    """SequenceNorm -> EMA in one kernel against the oracle and the two modules run in turn;
+    short rows fall back to the two modules."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(31)
+    bsz, dim = 3, 6
+    for length in (2048, 100):
+        norm = M.SequenceNorm(dim).cuda().eval()
+        move = M.MultiHeadEMA(dim, ndim=16, bidirectional=bidir).cuda().eval()
+        x = (torch.randn(bsz, dim, length, generator=gen) * 2 - 0.5).to(dtype)
+        mask = right_pad_mask(gen, bsz, length, 0.5)
+        mask[bsz - 1] = True
+        with torch.no_grad():
+            norm.weight.normal_(0, 0.1)
+            norm.bias.normal_(0, 0.1)
+            y = M.sequence_norm_ema(norm, move, x.cuda(), mask.cuda())
+            y2 = move(norm(x.cuda(), mask.cuda()), mask.cuda())
+        prm = [t.detach().cpu() for t in (move.alpha, move.delta, move.beta, move.gamma, move.omega)]
+        xn = O.sequence_norm(x.float(), norm.weight.detach().cpu() + 1.0, norm.bias.detach().cpu(), mask)[0]
+        ref = O.ema_forward_recurrence(xn, *prm, mask, bidirectional=bidir)
+        assert rel_l2(y.float(), ref) < TOL[dtype]
+        assert rel_l2(y.float(), y2.float()) < TOL[dtype] * 2
