@@ -448,7 +448,7 @@ def run_aux(args):
                 if n:
                     mask[b, L - n:] = True
             mask = mask.to(dev)
-            ms = timed(lambda: ema(norm(x, mask), mask), steps, warm)
+            ms = timed(lambda: M.sequence_norm_ema(norm, ema, x, mask), steps, warm)
             tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 4, "c2: SequenceNorm + bidirectional MultiHeadEMA fwd fp32 L=16384 B=32 D=256, 0-50% padding", "f32"
         else:  # decode: 1024 single-token steps, state seeded from a 4096-token prefix
             B, D, T = 64, 2048, 1024

@@ -15,12 +15,19 @@
 namespace mega {
 
 
-constexpr int kRowThreads = 256;
 constexpr int kRowNP = 16;
 
-__device__ __forceinline__ int padded(int i, int seg) { return i + i / seg; }
+constexpr int kSegPad = 4;  // pad words after every segment: keeps segments 16-byte aligned and
+                            // staggers them over the banks (segment pitch = seg + 4 words)
 
-__device__ __forceinline__ float block_sum256(float v, float* red) {
+// index of element i in the padded row buffer; i / seg by multiplication with
+// magic = ceil(2^32 / seg) (exact for i < 2^16, seg <= 256)
+__device__ __forceinline__ int padded(int i, unsigned magic) {
+  return i + kSegPad * (int)__umulhi((unsigned)i, magic);
+}
+
+template <int kT>
+__device__ __forceinline__ float block_sum(float v, float* red) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -29,74 +36,113 @@ __device__ __forceinline__ float block_sum256(float v, float* red) {
   __syncthreads();
   float r = 0.f;
 #pragma unroll
-  for (int i = 0; i < kRowThreads / 32; ++i) r += red[i];
+  for (int i = 0; i < kT / 32; ++i) r += red[i];
   return r;
 }
 
-// Exclusive scan across the 256 segments of the affine maps s -> a s + loc (a = q^seg, the same
-// for every segment).  On return st[n] holds the state entering this thread's segment.
-// `reverse` scans right to left (for the anti-causal half).
-__device__ __forceinline__ void carry_scan(float (&st)[kRowNP], const float (&aseg)[kRowNP], float* wtot,
-                                           bool reverse) {
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int vl = reverse ? 31 - lane : lane;  // position of this lane in scan order
-  float apow[kRowNP];
+// Exclusive scan, across the 256 segments of a row, of the affine maps s -> a s + loc (a = q^seg,
+// one per pole).  The 256 x 16 local states go through a shared table; thread j then owns pole
+// j / (T/16) and a block of 16 consecutive segments, scans them sequentially, the 16 block totals are
+// folded the same way, and every thread reads back the state entering its own segment.
+// `vseg` is the position of this thread's segment in scan order (tid, or 255 - tid right-to-left).
+template <int kT>
+__device__ __forceinline__ void carry_scan(float (&st)[kRowNP], const float* qrow, int nq, int seg, int vseg,
+                                           float* tab, float* tot) {
+  constexpr int kBlocks = kT / 16;       // blocks of 16 segments per pole (= threads per pole)
+  constexpr int kPitch = kBlocks * 17;   // table words per pole
+  const int tid = threadIdx.x;
+  // table entry of (pole n, segment position v): n * kPitch + (v / 16) * 17 + v % 16
+  const int wslot = (vseg >> 4) * 17 + (vseg & 15);
 #pragma unroll
-  for (int n = 0; n < kRowNP; ++n) apow[n] = aseg[n];
-  // inclusive Hillis-Steele within the warp
-#pragma unroll
-  for (int dlt = 1; dlt < 32; dlt <<= 1) {
-#pragma unroll
-    for (int n = 0; n < kRowNP; ++n) {
-      const float o = reverse ? __shfl_down_sync(0xffffffffu, st[n], dlt) : __shfl_up_sync(0xffffffffu, st[n], dlt);
-      if (vl >= dlt) st[n] = fmaf(apow[n], o, st[n]);
-      apow[n] *= apow[n];
-    }
-  }
-  // apow now holds a^32.  Warp totals -> shared, then each warp folds in the warps before it.
-  const int vw = reverse ? (kRowThreads / 32 - 1 - w) : w;
-  if (vl == 31) {
-#pragma unroll
-    for (int n = 0; n < kRowNP; ++n) wtot[w * kRowNP + n] = st[n];
+  for (int n = 0; n < kRowNP; ++n) tab[n * kPitch + wslot] = st[n];
+  const int n = tid / kBlocks, sb = tid % kBlocks;
+  float a1 = 0.f;
+  if (n < nq) {
+    const float qn = __ldg(qrow + n);
+    a1 = qn > 0.f ? __expf((float)seg * __logf(qn)) : 0.f;
   }
   __syncthreads();
-  float pre[kRowNP];  // state entering this warp
+  float* col = tab + n * kPitch + sb * 17;
+  float run = 0.f;
 #pragma unroll
-  for (int n = 0; n < kRowNP; ++n) pre[n] = 0.f;
-  for (int k = 0; k < vw; ++k) {
-    const int src = reverse ? (kRowThreads / 32 - 1 - k) : k;
-#pragma unroll
-    for (int n = 0; n < kRowNP; ++n) pre[n] = fmaf(apow[n], pre[n], wtot[src * kRowNP + n]);
+  for (int s = 0; s < 16; ++s) {
+    const float v = col[s];
+    col[s] = run;
+    run = fmaf(a1, run, v);
   }
-  // exclusive value for this lane: inclusive of the previous lane, plus a^(vl) * pre
+  tot[n * (kBlocks + 1) + sb] = run;
+  __syncthreads();
+  float a16 = a1 * a1;
+  a16 *= a16; a16 *= a16; a16 *= a16;
+  float pre = 0.f;
+  for (int k = 0; k < sb; ++k) pre = fmaf(a16, pre, tot[n * (kBlocks + 1) + k]);
 #pragma unroll
-  for (int n = 0; n < kRowNP; ++n) {
-    float prev = reverse ? __shfl_down_sync(0xffffffffu, st[n], 1) : __shfl_up_sync(0xffffffffu, st[n], 1);
-    if (vl == 0) prev = 0.f;
-    // a^vl by binary powers of aseg
-    float av = 1.f, b = aseg[n];
-    int e = vl;
-#pragma unroll
-    for (int k = 0; k < 5; ++k) {
-      if (e & 1) av *= b;
-      b *= b;
-      e >>= 1;
-    }
-    st[n] = fmaf(av, pre[n], prev);
+  for (int s = 0; s < 16; ++s) {
+    col[s] += pre;
+    pre *= a1;
   }
+  __syncthreads();
+#pragma unroll
+  for (int n2 = 0; n2 < kRowNP; ++n2) st[n2] = tab[n2 * kPitch + wslot];
   __syncthreads();
 }
 
-template <typename T, bool kBidir, bool kNorm>
-__global__ void __launch_bounds__(kRowThreads) rowres_kernel(RowArgs a) {
-  extern __shared__ float smf[];
+template <int kDir, bool kEmit, bool kAccum, bool kPreEmit>
+__device__ __forceinline__ void walk_segment(float* src, float* dst, int base, int seg, const float (&q)[kRowNP],
+                                             const float (&c)[kRowNP], float (&st)[kRowNP], float om) {
+  // kDir = +1 left to right, -1 right to left; four positions per shared-memory access
+  const int nq4 = seg >> 2;
+  for (int k4 = 0; k4 < nq4; ++k4) {
+    const int off = base + 4 * (kDir > 0 ? k4 : nq4 - 1 - k4);
+    const float4 xv4 = *reinterpret_cast<const float4*>(src + off);
+    float xs[4] = {xv4.x, xv4.y, xv4.z, xv4.w};
+    float ys[4];
+    if (kAccum) {
+      const float4 y4 = *reinterpret_cast<const float4*>(dst + off);
+      ys[0] = y4.x; ys[1] = y4.y; ys[2] = y4.z; ys[3] = y4.w;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = kDir > 0 ? u : 3 - u;
+      const float xv = xs[e];
+      if (!kEmit) {
+#pragma unroll
+        for (int n = 0; n < kRowNP; ++n) st[n] = fmaf(q[n], st[n], xv);
+      } else {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < kRowNP; n += 2) {
+          if (kPreEmit) {
+            a0 = fmaf(c[n], st[n], a0);
+            a1 = fmaf(c[n + 1], st[n + 1], a1);
+          }
+          st[n] = fmaf(q[n], st[n], xv);
+          st[n + 1] = fmaf(q[n + 1], st[n + 1], xv);
+          if (!kPreEmit) {
+            a0 = fmaf(c[n], st[n], a0);
+            a1 = fmaf(c[n + 1], st[n + 1], a1);
+          }
+        }
+        ys[e] = kAccum ? ys[e] + (a0 + a1) : fmaf(om, xv, a0 + a1);
+      }
+    }
+    if (kEmit) *reinterpret_cast<float4*>(dst + off) = make_float4(ys[0], ys[1], ys[2], ys[3]);
+  }
+}
+
+template <typename T, bool kBidir, bool kNorm, int kT>
+__global__ void __launch_bounds__(kT) rowres_kernel(RowArgs a) {
+  constexpr int kRowThreads = kT;
+  extern __shared__ __align__(16) float smf[];
   const int L = a.L, seg = a.seg;
-  const int Lp = padded(kRowThreads * seg, seg) + 4;
-  float* bx = smf;                       // row (raw or normalised x), padded per segment
-  float* by = smf + Lp;                  // second buffer (bidirectional only)
-  float* red = smf + (kBidir ? 2 : 1) * Lp;        // [8]
-  float* wtot = red + 8;                           // [8][16]
-  unsigned char* mk = reinterpret_cast<unsigned char*>(wtot + 8 * kRowNP);  // [256*seg]
+  const unsigned magic = a.magic;
+  const int Lp = kRowThreads * (seg + kSegPad);
+  float* bx = smf;                                   // row (x zeroed at pads, or normalised x)
+  float* by = smf + Lp;                              // second buffer (bidirectional only)
+  float* tab = smf + (kBidir ? 2 : 1) * Lp;          // [16][272] carry table
+  float* tot = tab + kRowNP * (kT / 16) * 17;        // [16][kT/16 + 1]
+  float* red = tot + kRowNP * (kT / 16 + 1);         // [kT/32]
+  unsigned char* mk = reinterpret_cast<unsigned char*>(red + kT / 32);  // [kT * seg]
 
   const int tid = threadIdx.x;
   const int row = blockIdx.x;
@@ -106,132 +152,124 @@ __global__ void __launch_bounds__(kRowThreads) rowres_kernel(RowArgs a) {
   const unsigned char* mg = a.mask ? a.mask + (size_t)b * L : nullptr;
   const int Ltot = kRowThreads * seg;
 
-  for (int i = tid; i < Ltot; i += kRowThreads) {
-    const bool in = i < L;
-    bx[padded(i, seg)] = in ? Elem<T>::ld(xg + i) : 0.f;
-    mk[i] = in ? (mg ? mg[i] : 0) : 1;
+  // the row buffer holds x zeroed at padded positions (and beyond L); the residual of padded
+  // positions, which uses the unmasked x, is added when the row is stored
+  for (int i0 = tid; i0 < Ltot; i0 += 8 * kRowThreads) {
+    float xv[8];
+    unsigned char mv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {  // eight independent loads in flight per thread
+      const int i = i0 + u * kRowThreads;
+      const bool in = i < L;
+      mv[u] = in ? (mg ? mg[i] : 0) : 1;
+      xv[u] = in ? Elem<T>::ld(xg + i) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * kRowThreads;
+      if (i < Ltot) {
+        mk[i] = mv[u];
+        bx[padded(i, magic)] = mv[u] ? 0.f : xv[u];
+      }
+    }
   }
   __syncthreads();
 
+  const int t0 = tid * seg;
+  const int base = tid * (seg + kSegPad);  // this thread's segment, contiguous and 16-byte aligned
   if (kNorm) {
     float s = 0.f, c = 0.f;
-    for (int i = tid; i < L; i += kRowThreads)
-      if (!mk[i]) { s += bx[padded(i, seg)]; c += 1.f; }
-    const float cnt = block_sum256(c, red);
-    const float mean = cnt > 0.f ? block_sum256(s, red) / cnt : 0.f;
+    for (int k = 0; k < seg; k += 4) {
+      const float4 v4 = *reinterpret_cast<const float4*>(bx + base + k);  // padded positions hold 0
+      s += (v4.x + v4.y) + (v4.z + v4.w);
+      const uchar4 m4 = *reinterpret_cast<const uchar4*>(mk + t0 + k);
+      c += (m4.x ? 0.f : 1.f) + (m4.y ? 0.f : 1.f) + (m4.z ? 0.f : 1.f) + (m4.w ? 0.f : 1.f);
+    }
+    const float cnt = block_sum<kT>(c, red);
+    const float mean = cnt > 0.f ? block_sum<kT>(s, red) / cnt : 0.f;
     float v = 0.f;
-    for (int i = tid; i < L; i += kRowThreads)
-      if (!mk[i]) { const float dl = bx[padded(i, seg)] - mean; v = fmaf(dl, dl, v); }
-    const float var = cnt > 0.f ? block_sum256(v, red) / cnt : 0.f;
+    for (int k = 0; k < seg; k += 4) {
+      const float4 v4 = *reinterpret_cast<const float4*>(bx + base + k);
+      const uchar4 m4 = *reinterpret_cast<const uchar4*>(mk + t0 + k);
+      const float d0 = m4.x ? 0.f : v4.x - mean, d1 = m4.y ? 0.f : v4.y - mean;
+      const float d2 = m4.z ? 0.f : v4.z - mean, d3 = m4.w ? 0.f : v4.w - mean;
+      v = fmaf(d0, d0, v); v = fmaf(d1, d1, v); v = fmaf(d2, d2, v); v = fmaf(d3, d3, v);
+    }
+    const float var = cnt > 0.f ? block_sum<kT>(v, red) / cnt : 0.f;
     const float rstd = rsqrtf(var + a.eps);
     const float w = __ldg(a.ngamma + d), bb = __ldg(a.nbeta + d);
-    for (int i = tid; i < L; i += kRowThreads) {
-      const int pi = padded(i, seg);
-      bx[pi] = mk[i] ? 0.f : fmaf((bx[pi] - mean) * rstd, w, bb);
+    const float sc = rstd * w, sh = fmaf(-mean, sc, bb);
+    for (int k = 0; k < seg; k += 4) {
+      float4 v4 = *reinterpret_cast<const float4*>(bx + base + k);
+      const uchar4 m4 = *reinterpret_cast<const uchar4*>(mk + t0 + k);
+      v4.x = m4.x ? 0.f : fmaf(v4.x, sc, sh);
+      v4.y = m4.y ? 0.f : fmaf(v4.y, sc, sh);
+      v4.z = m4.z ? 0.f : fmaf(v4.z, sc, sh);
+      v4.w = m4.w ? 0.f : fmaf(v4.w, sc, sh);
+      *reinterpret_cast<float4*>(bx + base + k) = v4;
     }
     if (tid == 0) {
       if (a.mean_out) a.mean_out[row] = mean;
       if (a.rstd_out) a.rstd_out[row] = rstd;
       if (a.count_out && d == 0) a.count_out[b] = (long long)(cnt + 0.5f);
     }
-    __syncthreads();
   }
 
-  const int t0 = tid * seg;
-  const int base = padded(t0, seg);  // this thread's segment is contiguous from here
   const float om = __ldg(a.omega + d);
 
   // ------------------------------ causal half ----------------------------------------------
   {
-    float q[kRowNP], c[kRowNP], st[kRowNP], aseg[kRowNP];
+    float q[kRowNP], c[kRowNP], st[kRowNP];
+    const float* qrow = a.q + (size_t)d * a.N;
 #pragma unroll
     for (int n = 0; n < kRowNP; ++n) {
       float pn = 0.f, qn = 0.f, gn = 0.f;
       if (n < a.N) {
         pn = __ldg(a.p + (size_t)d * a.N + n);
-        qn = __ldg(a.q + (size_t)d * a.N + n);
+        qn = __ldg(qrow + n);
         gn = __ldg(a.g + (size_t)d * a.N + n);
       }
       q[n] = qn; c[n] = pn * gn; st[n] = 0.f;
-      aseg[n] = qn > 0.f ? __expf((float)seg * __logf(qn)) : 0.f;
     }
-    for (int k = 0; k < seg; ++k) {
-      const float xv = mk[t0 + k] ? 0.f : bx[base + k];
-#pragma unroll
-      for (int n = 0; n < kRowNP; ++n) st[n] = fmaf(q[n], st[n], xv);
-    }
-    carry_scan(st, aseg, wtot, false);
-    float* out = kBidir ? by : bx;
-    for (int k = 0; k < seg; ++k) {
-      const float xr = bx[base + k];
-      const float xv = mk[t0 + k] ? 0.f : xr;
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int n = 0; n < kRowNP; n += 2) {
-        st[n] = fmaf(q[n], st[n], xv);
-        st[n + 1] = fmaf(q[n + 1], st[n + 1], xv);
-        a0 = fmaf(c[n], st[n], a0);
-        a1 = fmaf(c[n + 1], st[n + 1], a1);
-      }
-      out[base + k] = fmaf(om, xr, a0 + a1);
-    }
+    walk_segment<1, false, false, false>(bx, bx, base, seg, q, c, st, om);
+    carry_scan<kT>(st, qrow, a.N, seg, tid, tab, tot);
+    walk_segment<1, true, false, false>(bx, kBidir ? by : bx, base, seg, q, c, st, om);
   }
   // ------------------------------ anti-causal half ------------------------------------------
   if (kBidir) {
-    float q[kRowNP], c[kRowNP], st[kRowNP], aseg[kRowNP];
+    float q[kRowNP], c[kRowNP], st[kRowNP];
     const int r2 = d + a.D;
+    const float* qrow = a.q + (size_t)r2 * a.N;
 #pragma unroll
     for (int n = 0; n < kRowNP; ++n) {
       float pn = 0.f, qn = 0.f, gn = 0.f;
       if (n < a.N) {
         pn = __ldg(a.p + (size_t)r2 * a.N + n);
-        qn = __ldg(a.q + (size_t)r2 * a.N + n);
+        qn = __ldg(qrow + n);
         gn = __ldg(a.g + (size_t)r2 * a.N + n);
       }
       q[n] = qn; c[n] = pn * gn; st[n] = 0.f;
-      aseg[n] = qn > 0.f ? __expf((float)seg * __logf(qn)) : 0.f;
     }
-    for (int k = seg - 1; k >= 0; --k) {
-      const float xv = mk[t0 + k] ? 0.f : bx[base + k];
-#pragma unroll
-      for (int n = 0; n < kRowNP; ++n) st[n] = fmaf(q[n], st[n], xv);
-    }
-    carry_scan(st, aseg, wtot, true);
-    for (int k = seg - 1; k >= 0; --k) {
-      const float xv = mk[t0 + k] ? 0.f : bx[base + k];
-      float a0 = 0.f, a1 = 0.f;
-      if (a.shift) {  // taps start at lag 1: emit from the state before this position enters
-#pragma unroll
-        for (int n = 0; n < kRowNP; n += 2) {
-          a0 = fmaf(c[n], st[n], a0);
-          a1 = fmaf(c[n + 1], st[n + 1], a1);
-          st[n] = fmaf(q[n], st[n], xv);
-          st[n + 1] = fmaf(q[n + 1], st[n + 1], xv);
-        }
-      } else {
-#pragma unroll
-        for (int n = 0; n < kRowNP; n += 2) {
-          st[n] = fmaf(q[n], st[n], xv);
-          st[n + 1] = fmaf(q[n + 1], st[n + 1], xv);
-          a0 = fmaf(c[n], st[n], a0);
-          a1 = fmaf(c[n + 1], st[n + 1], a1);
-        }
-      }
-      by[base + k] += a0 + a1;
-    }
+    walk_segment<-1, false, false, false>(bx, bx, base, seg, q, c, st, om);
+    carry_scan<kT>(st, qrow, a.N, seg, kRowThreads - 1 - tid, tab, tot);
+    if (a.shift)  // taps start at lag 1: emit from the state before the position enters
+      walk_segment<-1, true, true, true>(bx, by, base, seg, q, c, st, om);
+    else
+      walk_segment<-1, true, true, false>(bx, by, base, seg, q, c, st, om);
   }
   __syncthreads();
   const float* out = kBidir ? by : bx;
   for (int i = tid; i < L; i += kRowThreads) {
-    float v = out[padded(i, seg)];
+    float v = out[padded(i, magic)];
+    if (!kNorm && mk[i]) v = fmaf(om, Elem<T>::ld(xg + i), v);  // residual of the unmasked x at a pad
     if (a.silu) v = siluf_(v);
     Elem<T>::st(yg + i, v);
   }
 }
 
-template <typename T, bool kBidir, bool kNorm>
+template <typename T, bool kBidir, bool kNorm, int kT>
 static bool launch_rowres(const RowArgs& a, size_t smem, cudaStream_t s) {
-  auto kern = rowres_kernel<T, kBidir, kNorm>;
+  auto kern = rowres_kernel<T, kBidir, kNorm, kT>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -239,8 +277,14 @@ static bool launch_rowres(const RowArgs& a, size_t smem, cudaStream_t s) {
     cudaGetLastError();
   });
   if (!attr_ok) return false;
-  launch(kern, dim3((unsigned)((long long)a.B * a.D)), dim3(kRowThreads), smem, (void*)s, a);
+  launch(kern, dim3((unsigned)((long long)a.B * a.D)), dim3(kT), smem, (void*)s, a);
   return true;
+}
+
+static size_t rowres_smem(int threads, int seg, bool bidir) {
+  const size_t lp = (size_t)threads * (seg + kSegPad);
+  return ((bidir ? 2 : 1) * lp + kRowNP * (threads / 16) * 17 + kRowNP * (threads / 16 + 1) + threads / 32) * sizeof(float) +
+         (size_t)threads * seg + 16;
 }
 
 // Tries the row-resident path: length stride 1 on both tensors, ndim <= 16, no carried state, no
@@ -248,26 +292,33 @@ static bool launch_rowres(const RowArgs& a, size_t smem, cudaStream_t s) {
 bool rowres_try(int dtype, const RowArgs& a_in, long long xsl, long long ysl, bool bidir, bool norm,
                 cudaStream_t s) {
   if (g_options[OPT_DISABLE_STREAM].load() != 0) return false;
-  if (xsl != 1 || ysl != 1 || a_in.N > kRowNP || a_in.L < 512) return false;
+  if (xsl != 1 || ysl != 1 || a_in.N > kRowNP || a_in.L < 512 || a_in.L > 65535) return false;
   if ((long long)a_in.B * a_in.D > 0x7fffffffLL) return false;
   RowArgs a = a_in;
-  int seg = (a.L + kRowThreads - 1) / kRowThreads;
-  seg += seg & 1;
+  // 512 threads per row (16 warps per SM at one row per SM) once segments stay >= 16 positions
+  int threads = a.L >= 8192 ? 512 : 256;
+  int seg = (((a.L + threads - 1) / threads) + 3) & ~3;
+  if (threads == 512 && rowres_smem(512, seg, bidir) > 220 * 1024) {
+    threads = 256;
+    seg = (((a.L + threads - 1) / threads) + 3) & ~3;
+  }
   a.seg = seg;
-  const size_t lp = (size_t)kRowThreads * seg + kRowThreads + 4;
-  const size_t smem = ((bidir ? 2 : 1) * lp + 8 + 8 * kRowNP) * sizeof(float) + (size_t)kRowThreads * seg + 16;
+  a.magic = (unsigned)((0x100000000ULL + seg - 1) / seg);
+  const size_t smem = rowres_smem(threads, seg, bidir);
   if (smem > 220 * 1024) return false;
   bool ok = false;
   switch (dtype) {
+#define MEGA_ROW_LAUNCH(TY, BI, NO) (threads == 512 ? launch_rowres<TY, BI, NO, 512>(a, smem, s) : launch_rowres<TY, BI, NO, 256>(a, smem, s))
 #define MEGA_ROW_CASE(DT, TY)                                                                    \
   case DT:                                                                                       \
-    if (bidir) ok = norm ? launch_rowres<TY, true, true>(a, smem, s) : launch_rowres<TY, true, false>(a, smem, s);   \
-    else ok = norm ? launch_rowres<TY, false, true>(a, smem, s) : launch_rowres<TY, false, false>(a, smem, s);      \
+    if (bidir) ok = norm ? MEGA_ROW_LAUNCH(TY, true, true) : MEGA_ROW_LAUNCH(TY, true, false);   \
+    else ok = norm ? MEGA_ROW_LAUNCH(TY, false, true) : MEGA_ROW_LAUNCH(TY, false, false);       \
     break;
     MEGA_ROW_CASE(MEGA_F32, float)
     MEGA_ROW_CASE(MEGA_BF16, __nv_bfloat16)
     MEGA_ROW_CASE(MEGA_F16, __half)
 #undef MEGA_ROW_CASE
+#undef MEGA_ROW_LAUNCH
     default: return false;
   }
   return ok;

@@ -16,7 +16,8 @@ struct RowArgs {
   long long* count_out;                  // SequenceNorm outputs (optional)
   float *mean_out, *rstd_out;
   int shift, silu;
-  int seg;                               // elements per thread (even)
+  int seg;                               // elements per thread (multiple of 4)
+  unsigned magic;                        // ceil(2^32 / seg)
 };
 
 // Tries the row-resident path: length stride 1 on both tensors, ndim <= 16, the row (two copies
