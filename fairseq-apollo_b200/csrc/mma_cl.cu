@@ -49,7 +49,7 @@ struct Cfg {
   static constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [kCh][16] f32  (q^16)
   static constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [kCh][2] f32
   static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
-  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages]
+  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages]
   static constexpr int kSmemBytes = kOffBar + 128 + 1024;           // + alignment slack
 };
 
@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   float* WB = reinterpret_cast<float*>(sm + kOffWB);
   float* Kp = reinterpret_cast<float*>(sm + kOffKp);
   uint64_t* full = reinterpret_cast<uint64_t*>(sm + kOffBar);
+  uint64_t* done = full + kStages;  // one arrival per warp once its slice of the stage is written
 
   const uint32_t sm_s = smem_u32(sm);
   const int tid = threadIdx.x;
@@ -154,7 +155,10 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   if (tid == 0) {
     prefetch_tensormap(&tmx);
     prefetch_tensormap(&tmy);
-    for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&done[s], kCg);
+    }
     mbar_fence_init();
   }
   __syncthreads();
@@ -413,8 +417,12 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
     for (int j = 0; j < 8; ++j) sts128(stage_s + vec_off<kCg>(g, toff[j], warp), v[j]);
     fence_proxy_async();
-    if (__syncthreads_or(!ok)) break;
+    __syncwarp();
+    if (!ok) break;
+    if (lane == 0) mbar_arrive(&done[s]);
+    // warps run on to the next stage on their own; only the issuing thread waits for the whole tile
     if (tid == 0) {
+      if (!mbar_wait(&done[s], ph)) break;
       tma_store_3d(&tmy, d0, i * kStep, b0, stage);
       bulk_commit();
       if (i + 2 < nsteps) {
