@@ -36,6 +36,7 @@ SIGNATURES = {
     "mega_gate_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
+    "mega_gate_qk": [c_p, c_l, c_p, c_p, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_d, c_p],
     "mega_set_option": [c_i, c_i],
     "mega_debug_device_error": [ctypes.POINTER(c_i), c_i],
 }

@@ -35,7 +35,7 @@ namespace {
 
 constexpr int kSeq = 8;    // sequences per CTA
 constexpr int kStep = 32;  // positions per step (2 chunks of 16)
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 
 template <int kCg>
 struct Cfg {
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   }
   __syncthreads();
   if (tid == 0) {
-    for (int s = 0; s < 2 && s < nsteps; ++s) {
+    for (int s = 0; s < kStages - 1 && s < nsteps; ++s) {
       mbar_expect_tx(&full[s], kStageBytes);
       tma_load_3d(sm + kOffStages + s * kStageBytes, &tmx, d0, s * kStep, b0, &full[s]);
     }
@@ -425,11 +425,11 @@ __global__ void __launch_bounds__(kCg * 32, 1)
       if (!mbar_wait(&done[s], ph)) break;
       tma_store_3d(&tmy, d0, i * kStep, b0, stage);
       bulk_commit();
-      if (i + 2 < nsteps) {
+      if (i + kStages - 1 < nsteps) {
         bulk_wait_read<1>();  // the store issued one step ago has drained its stage
-        const int s2 = (i + 2) % kStages;
+        const int s2 = (i + kStages - 1) % kStages;
         mbar_expect_tx(&full[s2], kStageBytes);
-        tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i + 2) * kStep, b0, &full[s2]);
+        tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i + kStages - 1) * kStep, b0, &full[s2]);
       }
     }
   }

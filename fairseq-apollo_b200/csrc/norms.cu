@@ -284,6 +284,30 @@ __global__ void gate_kernel(const T* a, long long lda, const T* b, long long ldb
   }
 }
 
+// One warp per row: z / max(||z||_2, eps), then the two affine rows (query, key).
+template <typename T>
+__global__ void gate_qk_kernel(const T* z, long long ldz, const float* gamma, const float* beta, T* qo,
+                               long long ldq, T* ko, long long ldk, long long rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+    const T* zr = z + r * ldz;
+    float ss = 0.f;
+    for (int c = lane; c < cols; c += 32) {
+      const float v = Elem<T>::ld(zr + c);
+      ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.f / fmaxf(sqrtf(ss), eps);
+    for (int c = lane; c < cols; c += 32) {
+      const float v = Elem<T>::ld(zr + c) * inv;
+      Elem<T>::st(qo + r * ldq + c, fmaf(v, gamma[c] + 1.f, beta[c]));
+      Elem<T>::st(ko + r * ldk + c, fmaf(v, gamma[cols + c] + 1.f, beta[cols + c]));
+    }
+  }
+}
+
 }  // namespace mega
 
 using namespace mega;
@@ -406,4 +430,19 @@ extern "C" int mega_gate_output(const void* residual, int64_t ld_res, const void
   if (!residual || !u || !hx || !h_lin || !out) return MEGA_ERR_NULL;
   return gate_common(2, residual, ld_res, u, ld_u, hx, ld_hx, h_lin, ld_h, out, ld_out, dtype, rows, cols,
                      stream);
+}
+
+extern "C" int mega_gate_qk(const void* z, int64_t ld_z, const float* gamma, const float* beta, void* q,
+                            int64_t ld_q, void* k, int64_t ld_k, int dtype, int64_t rows, int cols, double eps,
+                            mega_stream_t stream) {
+  if (!z || !gamma || !beta || !q || !k) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (rows <= 0 || cols <= 0) return MEGA_ERR_SHAPE;
+  if (ld_z < cols || ld_q < cols || ld_k < cols) return MEGA_ERR_STRIDE;
+  const long long blocks = (rows + 7) / 8;  // 8 warps per block, one row per warp and pass
+  const unsigned grid = (unsigned)(blocks > 148 * 8 ? 148 * 8 : blocks);
+  MEGA_DISPATCH_DTYPE(dtype, launch(gate_qk_kernel<T>, grid, 256, 0, stream, (const T*)z, (long long)ld_z, gamma,
+                                    beta, (T*)q, (long long)ld_q, (T*)k, (long long)ld_k, (long long)rows, cols,
+                                    (float)eps));
+  return check_launch("gate_qk");
 }

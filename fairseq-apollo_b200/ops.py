@@ -343,3 +343,23 @@ def gate_output(residual, u, hx, h_lin):
                                                h_.data_ptr(), ldh, y.data_ptr(), cols, _dt(residual), rows, cols,
                                                _stream()), "gate_output")
     return y
+
+
+def gate_qk(z, gamma, beta, eps=1e-5):
+    """Query and key of the Mega block from the shared representation z (..., S):
+    zn = z / max(||z||_2, eps); returns (zn * (gamma[0] + 1) + beta[0], zn * (gamma[1] + 1) + beta[1]).
+    gamma, beta are (2, S); z may be a column slice of the mx_proj output.
+    Mirrors fairseq/modules/moving_average_gated_attention.py:324-328."""
+    _cuda(z, gamma, beta)
+    z_, rows, cols, ldz = _rows(z)
+    g = gamma.detach().to(torch.float32).contiguous()
+    b = beta.detach().to(torch.float32).contiguous()
+    if g.shape != (2, cols) or b.shape != (2, cols):
+        raise ValueError("gate_qk: gamma and beta must be (2, %d)" % cols)
+    q = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    k = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    with torch.cuda.device(z.device):
+        _lib.check(_lib.lib().mega_gate_qk(z_.data_ptr(), ldz, g.data_ptr(), b.data_ptr(), q.data_ptr(), cols,
+                                           k.data_ptr(), cols, _dt(z), rows, cols, float(eps), _stream()),
+                   "gate_qk")
+    return q, k

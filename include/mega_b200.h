@@ -226,8 +226,11 @@ MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, int dtype, 
  *   mega_gate_silu:    y = silu(a [+ b])            (b may be NULL)
  *   mega_gate_mul_silu y = a * silu(r)              (attn * silu(r) with r pre-activation)
  *   mega_gate_output:  out = residual + sigmoid(u) * (silu(hx + h_lin) - residual)
- * u, hx may be column slices of a wider matrix: `ld_*` are their row pitches in elements.
- * Replaces: moving_average_gated_attention.py:308,316,322,330,407-412 (sigmoid / silu / addcmul chain).
+ *   mega_gate_qk:      zn = z / max(||z||_2, eps) per row; q = zn * (gamma[0] + 1) + beta[0],
+ *                      k = zn * (gamma[1] + 1) + beta[1]; gamma, beta are (2, cols) fp32
+ * u, hx, z may be column slices of a wider matrix: `ld_*` are their row pitches in elements.
+ * Replaces: moving_average_gated_attention.py:308,316,322,324-328,330,407-412
+ * (sigmoid / silu / addcmul chain; F.normalize + the (2, S) affine that makes query and key).
  */
 MEGA_API int mega_gate_silu(const void* a, int64_t ld_a, const void* b, int64_t ld_b, void* y, int64_t ld_y,
                    int dtype, int64_t rows, int cols, mega_stream_t stream);
@@ -237,6 +240,9 @@ MEGA_API int mega_gate_output(const void* residual, int64_t ld_res, const void* 
                      const void* hx, int64_t ld_hx, const void* h_lin, int64_t ld_h,
                      void* out, int64_t ld_out, int dtype, int64_t rows, int cols,
                      mega_stream_t stream);
+MEGA_API int mega_gate_qk(const void* z, int64_t ld_z, const float* gamma, const float* beta, void* q,
+                 int64_t ld_q, void* k, int64_t ld_k, int dtype, int64_t rows, int cols, double eps,
+                 mega_stream_t stream);
 
 #ifdef __cplusplus
 }
