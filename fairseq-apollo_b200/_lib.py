@@ -37,6 +37,13 @@ SIGNATURES = {
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_qk": [c_p, c_l, c_p, c_p, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_d, c_p],
+    "mega_timestep_norm_fwd_train": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                                     c_p, c_p, c_p, c_i, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p],
+    "mega_timestep_norm_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 9 + [c_i] + [c_p] * 5,
+    "mega_sequence_norm_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 5 + [c_i] + [c_p] * 3,
+    "mega_ema_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 4 + [c_i] + [c_p] * 3 + [c_u, c_i]
+                    + [c_p] * 6,
+    "mega_ema_coeffs_bwd": [c_p] * 6 + [c_i, c_i] + [c_p] * 5,
     "mega_set_option": [c_i, c_i],
     "mega_debug_device_error": [ctypes.POINTER(c_i), c_i],
 }

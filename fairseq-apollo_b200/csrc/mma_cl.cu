@@ -405,7 +405,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
         if (a.silu) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) yv[h2][j] = siluf_(yv[h2][j]);
+          for (int j = 0; j < 8; ++j) yv[h2][j] = silu_tanh(yv[h2][j]);
         }
       }
 #pragma unroll

@@ -21,6 +21,9 @@ struct TsnArgs {
   float eps;
   long long* count_out;
   float *mean_out, *var_out;
+  // training-mode saves (all NULL in inference): per-step statistics, fp32, contiguous (B, L, G);
+  // group_mean only for the grouped form
+  float *cummean, *cumrstd, *group_mean;
 };
 
 // Welford step with the update rule of the reference (fairseq/csrc/utils.h:56-65).
@@ -69,6 +72,11 @@ __global__ void __launch_bounds__(128) tsn_plain_kernel(TsnArgs a) {
         const float out = mk[u] ? 0.f : fmaf((xv[u] - m1) * rstd, w, bb);
         Elem<T>::st(yp + t * a.ysl, out);
         if (!mk[u]) { mean = m1; var = m2; ++cnt; }
+        if (a.cummean) {  // the running mean AFTER step t (unchanged by a padded step)
+          const size_t o = ((size_t)b * a.L + t) * a.D + d;
+          a.cummean[o] = mean;
+          a.cumrstd[o] = rstd;
+        }
       }
     }
   }
@@ -124,6 +132,12 @@ __global__ void __launch_bounds__(128) tsn_group_kernel(TsnArgs a) {
       Elem<T>::st(yr + k * a.ysd, out);
     }
     if (!mk) { mean = m1; var = m2; ++cnt; }
+    if (a.cummean && lane == 0) {
+      const size_t o = ((size_t)b * a.L + t) * a.G + g;
+      a.cummean[o] = mean;
+      a.cumrstd[o] = rstd;
+      a.group_mean[o] = gm;
+    }
   }
   if (lane == 0) {
     a.mean_out[wid] = mean;
@@ -312,13 +326,12 @@ __global__ void gate_qk_kernel(const T* z, long long ldz, const float* gamma, co
 
 using namespace mega;
 
-extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb,
-                                      int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
-                                      const int64_t* prev_count, const float* prev_mean,
-                                      const float* prev_var, const float* gamma, const float* beta,
-                                      const uint8_t* pad_mask, int num_groups, double eps,
-                                      int64_t* count_out, float* mean_out, float* var_out,
-                                      mega_stream_t stream) {
+static int tsn_fwd_common(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb, int64_t xsl,
+                          int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd, const int64_t* prev_count,
+                          const float* prev_mean, const float* prev_var, const float* gamma, const float* beta,
+                          const uint8_t* pad_mask, int num_groups, double eps, int64_t* count_out,
+                          float* mean_out, float* var_out, float* cummean, float* cumrstd, float* group_mean,
+                          mega_stream_t stream) {
   if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
       !var_out)
     return MEGA_ERR_NULL;
@@ -333,8 +346,9 @@ extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, 
   a.prev_count = (const long long*)prev_count; a.prev_mean = prev_mean; a.prev_var = prev_var;
   a.gamma = gamma; a.beta = beta; a.mask = pad_mask; a.eps = (float)eps;
   a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
+  a.cummean = cummean; a.cumrstd = cumrstd; a.group_mean = group_mean;
   if (G == D) {
-    if (x != y) {
+    if (x != y && !cummean) {
       StreamArgs sa{};
       sa.B = B; sa.L = L; sa.D = D; sa.N = 0;
       sa.prev_count = a.prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var; sa.gamma = gamma;
@@ -350,6 +364,33 @@ extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, 
     MEGA_DISPATCH_DTYPE(dtype, launch(tsn_group_kernel<T>, grid, 128, 0, stream, a));
   }
   return check_launch("timestep_norm_fwd");
+}
+
+extern "C" int mega_timestep_norm_fwd(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb,
+                                      int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                      const int64_t* prev_count, const float* prev_mean,
+                                      const float* prev_var, const float* gamma, const float* beta,
+                                      const uint8_t* pad_mask, int num_groups, double eps,
+                                      int64_t* count_out, float* mean_out, float* var_out,
+                                      mega_stream_t stream) {
+  return tsn_fwd_common(x, y, dtype, B, L, D, xsb, xsl, xsd, ysb, ysl, ysd, prev_count, prev_mean, prev_var,
+                        gamma, beta, pad_mask, num_groups, eps, count_out, mean_out, var_out, nullptr, nullptr,
+                        nullptr, stream);
+}
+
+extern "C" int mega_timestep_norm_fwd_train(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb,
+                                            int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                            const int64_t* prev_count, const float* prev_mean,
+                                            const float* prev_var, const float* gamma, const float* beta,
+                                            const uint8_t* pad_mask, int num_groups, double eps,
+                                            int64_t* count_out, float* mean_out, float* var_out, float* cummean,
+                                            float* cumrstd, float* group_mean, mega_stream_t stream) {
+  if (!cummean || !cumrstd) return MEGA_ERR_NULL;
+  const bool grouped = num_groups > 0 && num_groups != D;
+  if (grouped && !group_mean) return MEGA_ERR_NULL;
+  return tsn_fwd_common(x, y, dtype, B, L, D, xsb, xsl, xsd, ysb, ysl, ysd, prev_count, prev_mean, prev_var,
+                        gamma, beta, pad_mask, num_groups, eps, count_out, mean_out, var_out, cummean, cumrstd,
+                        grouped ? group_mean : nullptr, stream);
 }
 
 extern "C" int mega_sequence_norm_fwd(const void* x, void* y, int dtype, int B, int D, int L, int64_t xsb,

@@ -20,6 +20,7 @@ import torch
 from torch import Tensor, nn
 
 from .. import ops
+from ..functions import EMAFunction, needs_grad
 from ..incremental_state import IncrementalStateMixin, require_no_grad
 
 
@@ -133,12 +134,13 @@ class MultiHeadEMA(IncrementalStateMixin, nn.Module):
                 activation: Optional[str] = None) -> Tensor:
         """x: (B, D, L) (any strides).  padding_mask: (B, L), non-zero = pad.
         ``activation='silu'`` fuses the caller's move_act into the epilogue."""
-        require_no_grad(x, self.alpha)
         bsz, embed_dim, seq_len = x.size()
         assert embed_dim == self.embed_dim
         assert activation in (None, 'silu')
         assert not self.bidirectional or incremental_state is None, \
             'Bidirectional EMA does not support incremental state'
+        if needs_grad(x, self.alpha, self.delta, self.beta, self.gamma, self.omega):
+            return self._forward_train(x, padding_mask, incremental_state, activation)
         p, q, g = self.coeffs()
         p, q = p.squeeze(-1), q.squeeze(-1)
         silu = activation == 'silu'
@@ -155,6 +157,17 @@ class MultiHeadEMA(IncrementalStateMixin, nn.Module):
         return ops.ema_forward(x, p, q, g, self.omega, padding_mask, None, False,
                                bidirectional=self.bidirectional, shift=self.shift,
                                truncation=self.truncation, silu=silu)
+
+    def _forward_train(self, x, padding_mask, incremental_state, activation):
+        """Differentiable path: forward and backward kernels behind an autograd Function; the
+        activation is applied by torch on the result, as the reference's caller does."""
+        if incremental_state is not None:
+            raise NotImplementedError("the incremental state is an inference feature: use torch.no_grad()")
+        if self.truncation is not None and self.truncation >= 1:
+            raise NotImplementedError("the backward kernel does not implement a truncated kernel")
+        y = EMAFunction.apply(x, self.alpha, self.delta, self.beta, self.gamma, self.omega, padding_mask,
+                              self.bidirectional, self.shift)
+        return torch.nn.functional.silu(y) if activation == 'silu' else y
 
     def forward_time_major(self, x, padding_mask=None, incremental_state=None, activation=None):
         """x: (L, B, D) time-major; returns (L, B, D).  A strided view, no copy."""

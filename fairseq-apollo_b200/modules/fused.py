@@ -8,7 +8,7 @@ import torch
 from torch import Tensor
 
 from .. import ops
-from ..incremental_state import require_no_grad
+from ..functions import needs_grad
 from .exponential_moving_average import MultiHeadEMA
 from .sequence_norm import SequenceNorm
 from .timestep_norm import TimestepNorm
@@ -24,10 +24,10 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     otherwise the two modules run back to back.  Both modules' incremental buffers are read
     and updated exactly as their own ``forward`` would.
     """
-    require_no_grad(x, norm.weight, move.alpha)
     assert activation in (None, 'silu')
     per_feature = norm.num_groups is None or norm.num_groups == norm.num_features
-    if not per_feature or move.bidirectional:
+    train = needs_grad(x, *norm.parameters(), *move.parameters())
+    if train or not per_feature or move.bidirectional:  # training: the two differentiable modules in turn
         xn = norm(x, padding_mask, incremental_state)
         mx = move(xn.transpose(1, 2), padding_mask, incremental_state, activation).transpose(1, 2)
         return (mx, xn) if return_normed else mx
@@ -56,9 +56,9 @@ def sequence_norm_ema(norm: SequenceNorm, move: MultiHeadEMA, x: Tensor, padding
     """x (B, D, L) -> EMA(SequenceNorm(x)) (B, D, L): the bidirectional branch of the Mega block
     (moving_average_gated_attention.py:298-303, 313).  One kernel, one pass over x, when the norm
     is per channel and the rows fit the row-resident kernel; otherwise the two modules in turn."""
-    require_no_grad(x, norm.weight, move.alpha)
     assert activation in (None, 'silu')
-    if norm.num_groups is None and move.truncation is None:
+    train = needs_grad(x, *norm.parameters(), *move.parameters())
+    if not train and norm.num_groups is None and move.truncation is None:
         p, q, g = move.coeffs()
         y = ops.sqn_ema_forward(x, norm.weight.detach().float() + 1.0, norm.bias, norm.eps, p.squeeze(-1),
                                 q.squeeze(-1), g, move.omega, padding_mask, move.bidirectional, move.shift,

@@ -18,7 +18,8 @@ from torch import Tensor
 from torch.nn.parameter import Parameter
 
 from .. import ops
-from ..incremental_state import IncrementalStateMixin, require_no_grad
+from ..functions import TimestepNormFunction, needs_grad
+from ..incremental_state import IncrementalStateMixin
 
 
 class TimestepNorm(IncrementalStateMixin, nn.Module):
@@ -73,9 +74,18 @@ class TimestepNorm(IncrementalStateMixin, nn.Module):
 
     def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None,
                 incremental_state: Optional[Dict[str, Dict[str, Optional[Tensor]]]] = None) -> torch.Tensor:
-        require_no_grad(x, self.weight)
-        prev_count, prev_mean, prev_var, saved_state = self.initial_statistics(x.size(0), incremental_state)
         groups = None if (self.num_groups is None or self.num_groups == self.num_features) else self.num_groups
+        if needs_grad(x, self.weight, self.bias, self.prior_mean, self.prior_logv):
+            # differentiable path (norm_layer/timestep_norm.py:100-139 with the autograd Function)
+            if incremental_state is not None:
+                raise NotImplementedError("the incremental state is an inference feature: use torch.no_grad()")
+            bsz = x.size(0)
+            out, _, _, _ = TimestepNormFunction.apply(
+                x, self.prior_count.expand(bsz).contiguous(), self.prior_mean.float().expand(bsz, -1),
+                torch.exp(self.prior_logv.float()).expand(bsz, -1), self.weight.float() + 1.0, self.bias.float(),
+                padding_mask, groups, self.eps)
+            return out
+        prev_count, prev_mean, prev_var, saved_state = self.initial_statistics(x.size(0), incremental_state)
         out, count, mean, var = ops.timestep_norm_fwd(x, prev_count, prev_mean, prev_var,
                                                       self.weight.detach().float() + 1.0, self.bias,
                                                       padding_mask, self.eps, groups)

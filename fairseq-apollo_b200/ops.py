@@ -363,3 +363,129 @@ def gate_qk(z, gamma, beta, eps=1e-5):
                                            k.data_ptr(), cols, _dt(z), rows, cols, float(eps), _stream()),
                    "gate_qk")
     return q, k
+
+
+# ------------------------------------------------------------------------ training
+def _like(x):
+    return torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
+        if _dense(x) else torch.empty_like(x, memory_format=torch.contiguous_format)
+
+
+def timestep_norm_fwd_train(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=None, eps=1e-5,
+                            num_groups=None):
+    """timestep_norm_fwd that also returns what the backward needs, like the reference op:
+    (y, count, mean, var, cummean, cumrstd, group_mean); the saves are (B, L, G) fp32 and
+    group_mean is None for the per-feature form."""
+    _cuda(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask)
+    bsz, length, dim = x.shape
+    groups = dim if num_groups is None else int(num_groups)
+    prev_count = prev_count.detach().to(torch.int64).contiguous()
+    prev_mean, prev_var, gamma, beta = _f32c(prev_mean), _f32c(prev_var), _f32c(gamma), _f32c(beta)
+    if prev_mean.shape != (bsz, groups) or prev_var.shape != (bsz, groups):
+        raise ValueError("prev_mean/prev_var must be (batch, groups) = (%d, %d)" % (bsz, groups))
+    mask = _mask_u8(padding_mask, bsz, length)
+    out = _like(x)
+    count = torch.empty(bsz, device=x.device, dtype=torch.int64)
+    mean = torch.empty(bsz, groups, device=x.device, dtype=torch.float32)
+    var = torch.empty_like(mean)
+    cummean = torch.empty(bsz, length, groups, device=x.device, dtype=torch.float32)
+    cumrstd = torch.empty_like(cummean)
+    group_mean = torch.empty_like(cummean) if groups != dim else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_timestep_norm_fwd_train(
+            x.data_ptr(), out.data_ptr(), _dt(x), bsz, length, dim, *x.stride(), *out.stride(),
+            prev_count.data_ptr(), prev_mean.data_ptr(), prev_var.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+            _ptr(mask), groups, float(eps), count.data_ptr(), mean.data_ptr(), var.data_ptr(),
+            cummean.data_ptr(), cumrstd.data_ptr(), _ptr(group_mean), _stream()), "timestep_norm_fwd_train")
+    return out, count, mean, var, cummean, cumrstd, group_mean
+
+
+def timestep_norm_bwd(dy, dmean, dvar, x, prev_mean, count, cummean, cumrstd, group_mean, gamma,
+                      padding_mask=None, num_groups=None):
+    """Gradients of TimestepNorm: (dx, dprev_mean, dprev_var, dgamma, dbeta); the argument order
+    follows the reference's timestep_norm_bwd / group_timestep_norm_bwd."""
+    _cuda(dy, dmean, dvar, x, prev_mean, count, cummean, cumrstd, group_mean, gamma, padding_mask)
+    bsz, length, dim = x.shape
+    groups = dim if num_groups is None else int(num_groups)
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    dmean, dvar, prev_mean, gamma = _f32c(dmean), _f32c(dvar), _f32c(prev_mean), _f32c(gamma)
+    mask = _mask_u8(padding_mask, bsz, length)
+    dx = _like(x)
+    dpm = torch.empty(bsz, groups, device=x.device, dtype=torch.float32)
+    dpv = torch.empty_like(dpm)
+    dgamma = torch.empty(dim, device=x.device, dtype=torch.float32)
+    dbeta = torch.empty_like(dgamma)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_timestep_norm_bwd(
+            dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, length, dim, *dy.stride(), *x.stride(),
+            *dx.stride(), _ptr(dmean), _ptr(dvar), prev_mean.data_ptr(), count.data_ptr(), cummean.data_ptr(),
+            cumrstd.data_ptr(), _ptr(group_mean), gamma.data_ptr(), _ptr(mask), groups, dpm.data_ptr(),
+            dpv.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), _stream()), "timestep_norm_bwd")
+    return dx, dpm, dpv, dgamma, dbeta
+
+
+def sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask=None, length_last=True):
+    """Gradients of the per-channel SequenceNorm: (dx, dgamma, dbeta)."""
+    _cuda(dy, x, count, mean, rstd, gamma, padding_mask)
+    if length_last:
+        bsz, dim, length = x.shape
+    else:
+        bsz, length, dim = x.shape
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    mean, rstd, gamma = _f32c(mean), _f32c(rstd), _f32c(gamma)
+    mask = _mask_u8(padding_mask, bsz, length)
+    dx = _like(x)
+    gs, xs, ds = dy.stride(), x.stride(), dx.stride()
+    if not length_last:
+        gs, xs, ds = (gs[0], gs[2], gs[1]), (xs[0], xs[2], xs[1]), (ds[0], ds[2], ds[1])
+    dgamma = torch.empty(dim, device=x.device, dtype=torch.float32)
+    dbeta = torch.empty_like(dgamma)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_sequence_norm_bwd(
+            dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *gs, *xs, *ds,
+            count.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gamma.data_ptr(), _ptr(mask), dim,
+            dgamma.data_ptr(), dbeta.data_ptr(), _stream()), "sequence_norm_bwd")
+    return dx, dgamma, dbeta
+
+
+def ema_backward(dy, x, p, q, g, omega, padding_mask=None, h_in=None, dh_out=None, bidirectional=False,
+                 shift=True, want_dh_in=False):
+    """Gradients of ema_forward (no activation, no truncation) on (B, D, L) tensors with any
+    strides: (dx, dp, dq, dgamma_hat, domega, dh_in or None)."""
+    _cuda(dy, x, p, q, g, omega, padding_mask, h_in, dh_out)
+    bsz, dim, length = x.shape
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    p, q, g, omega, h_in, dh_out = _f32c(p), _f32c(q), _f32c(g), _f32c(omega), _f32c(h_in), _f32c(dh_out)
+    n = p.shape[1]
+    mask = _mask_u8(padding_mask, bsz, length)
+    dx = _like(x)
+    dp = torch.empty_like(p)
+    dq = torch.empty_like(p)
+    dg = torch.empty_like(p)
+    dom = torch.empty(dim, device=x.device, dtype=torch.float32)
+    dh_in = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32) if want_dh_in else None
+    flags = (EMA_BIDIRECTIONAL if bidirectional else 0) | (0 if shift else EMA_NO_SHIFT)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_ema_bwd(
+            dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *dy.stride(), *x.stride(),
+            *dx.stride(), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), _ptr(h_in),
+            _ptr(dh_out), flags, 0, dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(), _ptr(dh_in),
+            _stream()), "ema_bwd")
+    return dx, dp, dq, dg, dom, dh_in
+
+
+def ema_coeffs_bwd(alpha, delta, beta, dp, dq, dg):
+    """(dalpha, ddelta, dbeta (K, N, 1), dgamma (K, N)) from the coefficient gradients."""
+    _cuda(alpha, delta, beta, dp, dq, dg)
+    k, n = alpha.shape[0], alpha.shape[1]
+    a, d, b = _f32c(alpha).view(k, n), _f32c(delta).view(k, n), _f32c(beta).view(k, n)
+    dp, dq, dg = _f32c(dp), _f32c(dq), _f32c(dg)
+    outs = [torch.empty(k, n, device=alpha.device, dtype=torch.float32) for _ in range(4)]
+    with torch.cuda.device(alpha.device):
+        _lib.check(_lib.lib().mega_ema_coeffs_bwd(a.data_ptr(), d.data_ptr(), b.data_ptr(), dp.data_ptr(),
+                                                  dq.data_ptr(), dg.data_ptr(), k, n,
+                                                  *[o.data_ptr() for o in outs], _stream()), "ema_coeffs_bwd")
+    return outs[0].unsqueeze(-1), outs[1].unsqueeze(-1), outs[2].unsqueeze(-1), outs[3]

@@ -244,6 +244,83 @@ MEGA_API int mega_gate_qk(const void* z, int64_t ld_z, const float* gamma, const
                  int64_t ld_q, void* k, int64_t ld_k, int dtype, int64_t rows, int cols, double eps,
                  mega_stream_t stream);
 
+/*
+ * ---- Training: forward with saved statistics, and backward ---------------------------------
+ *
+ * mega_timestep_norm_fwd_train: mega_timestep_norm_fwd that also writes the per-step statistics
+ * the backward needs: cummean, cumrstd (B, L, G) fp32 contiguous, and group_mean (B, L, G) for
+ * the grouped form (NULL otherwise); G = D for the per-feature form.  At a padded step cummean
+ * holds the unchanged running mean.
+ * Replaces: timestep_norm_fwd / group_timestep_norm_fwd as called by TimestepNormFunc.forward
+ * (norm_layer/timestep_norm.py:29-41), which return (Y, count, mean, var, [group_mean,] cummean,
+ * cumrstd).
+ */
+MEGA_API int mega_timestep_norm_fwd_train(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb,
+                                 int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                 const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                                 const float* gamma, const float* beta, const uint8_t* pad_mask,
+                                 int num_groups, double eps, int64_t* count_out, float* mean_out,
+                                 float* var_out, float* cummean, float* cumrstd, float* group_mean,
+                                 mega_stream_t stream);
+
+/*
+ * mega_timestep_norm_bwd: gradients of TimestepNorm.  dy, x, dx are (B, L, D) with strides in
+ * elements; dmean, dvar (B, G) are the gradients flowing into the returned statistics (NULL = 0);
+ * count is the FINAL count returned by the forward; cummean / cumrstd / group_mean are the
+ * forward's saves.  Outputs: dx, dprev_mean, dprev_var (B, G), dgamma, dbeta (D); the last two
+ * are zeroed on the stream and accumulated with atomic adds over the batch.
+ * Grouped form: at most 256 features per group (MEGA_ERR_UNSUPPORTED beyond).
+ * Replaces: timestep_norm_bwd / group_timestep_norm_bwd (fairseq/csrc/ops/timestep_norm.cc:105-216,
+ * 318-446).
+ */
+MEGA_API int mega_timestep_norm_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int L, int D,
+                           int64_t gsb, int64_t gsl, int64_t gsd, int64_t xsb, int64_t xsl, int64_t xsd,
+                           int64_t dsb, int64_t dsl, int64_t dsd, const float* dmean, const float* dvar,
+                           const float* prev_mean, const int64_t* count, const float* cummean,
+                           const float* cumrstd, const float* group_mean, const float* gamma,
+                           const uint8_t* pad_mask, int num_groups, float* dprev_mean, float* dprev_var,
+                           float* dgamma, float* dbeta, mega_stream_t stream);
+
+/*
+ * mega_sequence_norm_bwd: gradients of SequenceNorm (per-channel form).  dy, x, dx are (B, D, L)
+ * with strides in elements (the length-major order of a (B, L, D) tensor is a stride pattern);
+ * count (B), mean, rstd (B, D) are the forward's outputs.  dgamma, dbeta (D) are zeroed on the
+ * stream and accumulated over the batch.  num_groups other than 0 / D: MEGA_ERR_UNSUPPORTED.
+ * Replaces: sequence_norm_bwd (fairseq/csrc/ops/sequence_norm.cc:374-529).
+ */
+MEGA_API int mega_sequence_norm_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int D, int L,
+                           int64_t gsb, int64_t gsd, int64_t gsl, int64_t xsb, int64_t xsd, int64_t xsl,
+                           int64_t dsb, int64_t dsd, int64_t dsl, const int64_t* count, const float* mean,
+                           const float* rstd, const float* gamma, const uint8_t* pad_mask, int num_groups,
+                           float* dgamma, float* dbeta, mega_stream_t stream);
+
+/*
+ * mega_ema_bwd: gradients of mega_ema_fwd (without the SiLU flag and without truncation).
+ * dy, x, dx are (B, D, L) with strides in elements; p, q, gamma_hat are (K, N) with K = D or 2D
+ * (bidirectional).  h_in (B, D, N) is the state the forward started from, dh_out the gradient
+ * flowing into the state it returned (either may be NULL; causal form only).  Outputs: dx;
+ * dp, dq, dgamma_hat (K, N) and domega (D), zeroed on the stream and accumulated over the batch
+ * with atomic adds; dh_in (B, D, N) or NULL.
+ * Replaces: the backward chain FFTConvFunc.backward -> ema_parameters_bwd -> ema_hidden_bwd
+ * (fused_ops/fftconv.py:29-38,65-82; fairseq/csrc/ops/ema_parameters.cc, ema_hidden.cc) and the
+ * autograd of the mask / omega elementwise ops in base_moving_average.py:137-172.
+ */
+MEGA_API int mega_ema_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int D, int L, int64_t gsb,
+                 int64_t gsd, int64_t gsl, int64_t xsb, int64_t xsd, int64_t xsl, int64_t dsb, int64_t dsd,
+                 int64_t dsl, const float* p, const float* q, const float* gamma_hat, const float* omega,
+                 int N, const uint8_t* pad_mask, const float* h_in, const float* dh_out, unsigned flags,
+                 int truncation, float* dp, float* dq, float* dgamma_hat, float* domega, float* dh_in,
+                 mega_stream_t stream);
+
+/*
+ * mega_ema_coeffs_bwd: chain rule from (dp, dq, dgamma_hat), each (K, N), to the raw parameters
+ * alpha, delta, beta (K, N[, 1]) and gamma (K, N).
+ * Replaces: autograd through _calc_coeffs (exponential_moving_average.py:71-80).
+ */
+MEGA_API int mega_ema_coeffs_bwd(const float* alpha, const float* delta, const float* beta, const float* dp,
+                        const float* dq, const float* dgamma_hat, int K, int N, float* dalpha, float* ddelta,
+                        float* dbeta, float* dgamma, mega_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

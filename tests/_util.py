@@ -21,8 +21,8 @@ def opt_mask(t):
 
 
 def rel_l2(a, b):
-    a = a.double().cpu()
-    b = b.double().cpu()
+    a = a.detach().double().cpu()
+    b = b.detach().double().cpu()
     d = (a - b).norm()
     n = b.norm()
     return float(d / n) if n > 0 else float(d)

@@ -5,6 +5,8 @@ Run in a container where the reference checkout is mounted (default
 ``oracle/_ref/mega_ref_cpu.so`` (python oracle/build_ref.py).  The fixtures are
 committed; nothing at test time reads the reference checkout.
 
+Usage: python tests/golden/make_golden.py [all|forward|backward].
+
 What runs:
   * the reference's CPU C++ ops (timestep_norm_fwd, group_timestep_norm_fwd,
     sequence_norm_fwd, group_sequence_norm_fwd, ema_parameters_fwd,
@@ -247,5 +249,81 @@ def main():
     print("cema state_dict:", {k: tuple(v.shape) for k, v in m.state_dict().items()})
 
 
+def backward_fixtures():
+    """Gradients produced by the reference: its CPU backward ops for the norms, and autograd
+    through MultiHeadComplexEMA (ema_parameters_bwd C++ op + the Python FFT convolution) for the
+    EMA.  Real-EMA parameter gradients follow from the rotation-off mapping: the kernel depends
+    on gamma * beta only, so dgamma = dgamma'[..., 0] * beta and dbeta = dgamma'[..., 0] * gamma."""
+    ops, cema, tsn, sqn = import_reference()
+    gen = torch.Generator().manual_seed(20251126)
+
+    for tag, (bsz, dim, length, ndim, bidir, shift, pad) in {
+        "ema_bwd_uni": (3, 6, 45, 16, False, True, 0.3),
+        "ema_bwd_uni_n3": (2, 5, 40, 3, False, True, 0.0),
+        "ema_bwd_bidir_shift": (2, 5, 37, 16, True, True, 0.4),
+        "ema_bwd_bidir_noshift": (2, 4, 32, 16, True, False, 0.3),
+    }.items():
+        params = ema_params(gen, dim, ndim, bidir)
+        x = torch.randn(bsz, dim, length, generator=gen).requires_grad_(True)
+        dy = torch.randn(bsz, dim, length, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None
+        m = cema_from_real(cema, dim, ndim, params, bidirectional=bidir, truncation=None, shift=shift).train()
+        y = m(x, mask, None)
+        (y * dy).sum().backward()
+        g0 = m.gamma.grad[:, :, 0]
+        alpha, delta, beta, gamma, omega = params
+        npz(tag, x=x, dy=dy, alpha=alpha, delta=delta, beta=beta, gamma=gamma, omega=omega,
+            mask=(mask if mask is not None else np.zeros((0,), bool)), bidirectional=bidir, shift=shift, y=y,
+            dx=x.grad, dalpha=m.alpha.grad, ddelta=m.delta.grad, dbeta=(g0 * gamma).unsqueeze(-1),
+            dgamma=g0 * beta.squeeze(-1), domega=m.omega.grad.view(dim))
+
+    for tag, (bsz, length, feat, groups, pad, prior) in {
+        "tsn_bwd_plain": (3, 33, 9, None, 0.4, 2),
+        "tsn_bwd_plain_nomask": (2, 40, 6, None, 0.0, 3),
+        "tsn_bwd_group": (3, 27, 12, 3, 0.4, 0),
+        "tsn_bwd_group_prior": (2, 18, 70, 2, 0.0, 2),
+    }.items():
+        x = torch.randn(bsz, length, feat, generator=gen) * 1.5 + 0.2
+        dy = torch.randn(bsz, length, feat, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None   # right padding only
+        ng = feat if groups is None else groups
+        prev_count = torch.full((bsz,), prior, dtype=torch.int64)
+        prev_mean = torch.randn(bsz, ng, generator=gen) * 0.1 if prior else torch.zeros(bsz, ng)
+        prev_var = torch.rand(bsz, ng, generator=gen) + 0.5 if prior else torch.ones(bsz, ng)
+        gamma = torch.randn(feat, generator=gen) * 0.1 + 1.0
+        beta = torch.randn(feat, generator=gen) * 0.1
+        dmean = torch.randn(bsz, ng, generator=gen)
+        dvar = torch.randn(bsz, ng, generator=gen)
+        if groups is None:
+            y, cnt, mean, var, cm, cr = ops.timestep_norm_fwd(x, prev_count, prev_mean, prev_var, gamma, beta, mask, 1e-5)
+            dx, dpm, dpv, dg, db = ops.timestep_norm_bwd(dy, dmean, dvar, x, prev_mean, cnt, cm, cr, gamma, mask)
+        else:
+            y, cnt, mean, var, gm, cm, cr = ops.group_timestep_norm_fwd(x, prev_count, prev_mean, prev_var, gamma,
+                                                                        beta, mask, groups, 1e-5)
+            dx, dpm, dpv, dg, db = ops.group_timestep_norm_bwd(dy, dmean, dvar, x, prev_mean, cnt, gm, cm, cr,
+                                                               gamma, mask, groups)
+        npz(tag, x=x, dy=dy, mask=(mask if mask is not None else np.zeros((0,), bool)), prev_count=prev_count,
+            prev_mean=prev_mean, prev_var=prev_var, gamma=gamma, beta=beta, dmean=dmean, dvar=dvar,
+            groups=(-1 if groups is None else groups), dx=dx, dprev_mean=dpm, dprev_var=dpv, dgamma=dg, dbeta=db)
+
+    for tag, (bsz, feat, length, length_last, pad) in {
+        "sqn_bwd_bhl": (3, 6, 41, True, 0.5),
+        "sqn_bwd_blh": (3, 7, 38, False, 0.5),
+    }.items():
+        shape = (bsz, feat, length) if length_last else (bsz, length, feat)
+        x = torch.randn(*shape, generator=gen) * 2.0 - 0.5
+        dy = torch.randn(*shape, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad)
+        gamma = torch.randn(feat, generator=gen) * 0.1 + 1.0
+        beta = torch.randn(feat, generator=gen) * 0.1
+        y, cnt, mean, rstd = ops.sequence_norm_fwd(x, gamma, beta, mask, 1e-5, length_last)
+        dx, dg, db = ops.sequence_norm_bwd(dy, x, cnt, mean, rstd, gamma, mask, length_last)
+        npz(tag, x=x, dy=dy, mask=mask, gamma=gamma, beta=beta, length_last=length_last, dx=dx, dgamma=dg, dbeta=db)
+
+
 if __name__ == "__main__":
-    main()
+    which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "forward"):
+        main()
+    if which in ("all", "backward"):
+        backward_fixtures()
