@@ -44,6 +44,11 @@ SIGNATURES = {
     "mega_ema_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 4 + [c_i] + [c_p] * 3 + [c_u, c_i]
                     + [c_p] * 6,
     "mega_ema_coeffs_bwd": [c_p] * 6 + [c_i, c_i] + [c_p] * 5,
+    "mega_cema_coeffs": [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p],
+    "mega_cema_kernel": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p],
+    "mega_cema_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p, c_p, c_i,
+                      c_p, c_p, c_p, c_u, c_i, c_p],
+    "mega_cema_step": [c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_u, c_p],
     "mega_set_option": [c_i, c_i],
     "mega_debug_device_error": [ctypes.POINTER(c_i), c_i],
 }

@@ -1,0 +1,291 @@
+// Complex EMA layer (MultiHeadComplexEMA): poles q_n = r_n e^{i theta_n}, real input gain p_n,
+// complex output weights gamma_n.  h_t = q h_{t-1} + p x_t (complex state), y_t = Re(sum_n gamma_n
+// h_{n,t}) + omega x_t.  Evaluated as the recurrence itself: O(L) per row, one pass over x, no
+// length cap.  Four lanes share a (batch, channel) row and split its poles; the per-step output is
+// a two-shuffle reduction.
+#include "common.cuh"
+
+namespace mega {
+
+// theta_n = (n + 1) sigmoid(theta) 2 pi / N ; r = 1 - sigmoid(alpha) sigmoid(delta) ;
+// p = sigmoid(alpha) ; gamma_hat = gamma / sqrt(N)
+template <typename T>
+__global__ void cema_coeffs_kernel(const T* __restrict__ alpha, const T* __restrict__ delta,
+                                   const T* __restrict__ theta, const T* __restrict__ gamma, int K, int N,
+                                   float scale, float* __restrict__ p, float* __restrict__ q,
+                                   float* __restrict__ g) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= K * N) return;
+  const int k = i / N, n = i % N;
+  const float a = 1.0f / (1.0f + expf(-Elem<T>::ld(alpha + i)));
+  const float d = 1.0f / (1.0f + expf(-Elem<T>::ld(delta + i)));
+  const float th = 1.0f / (1.0f + expf(-Elem<T>::ld(theta + k))) * (6.283185307179586f / (float)N) * (float)(n + 1);
+  const float r = 1.0f - a * d;
+  float sn, cs;
+  sincosf(th, &sn, &cs);
+  p[i] = a;
+  q[2 * i] = r * cs;
+  q[2 * i + 1] = r * sn;
+  g[2 * i] = Elem<T>::ld(gamma + 2 * i) * scale;
+  g[2 * i + 1] = Elem<T>::ld(gamma + 2 * i + 1) * scale;
+}
+
+// k[row, l] = Re(sum_n p gamma q^l), through the polar form of q
+__global__ void cema_kernel_kernel(const float* __restrict__ p, const float* __restrict__ q,
+                                   const float* __restrict__ g, int N, int L, float* __restrict__ out) {
+  extern __shared__ float sm[];  // [N] x {p*gr, p*gi, log r, arg}
+  const int r = blockIdx.y;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    const float qr = q[2 * (r * N + n)], qi = q[2 * (r * N + n) + 1];
+    const float pn = p[r * N + n];
+    sm[4 * n + 0] = pn * g[2 * (r * N + n)];
+    sm[4 * n + 1] = pn * g[2 * (r * N + n) + 1];
+    const float mag = sqrtf(qr * qr + qi * qi);
+    sm[4 * n + 2] = mag > 0.f ? logf(mag) : -1e30f;
+    sm[4 * n + 3] = atan2f(qi, qr);
+  }
+  __syncthreads();
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  float acc = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const float m = l == 0 ? 1.f : expf((float)l * sm[4 * n + 2]);
+    float sn, cs;
+    sincosf((float)l * sm[4 * n + 3], &sn, &cs);
+    acc += m * (sm[4 * n + 0] * cs - sm[4 * n + 1] * sn);
+  }
+  out[(size_t)r * L + l] = acc;
+}
+
+struct CemaArgs {
+  const void* x;
+  void* y;
+  int B, D, L, N;
+  long long xsb, xsd, xsl, ysb, ysd, ysl;
+  const float *p, *q, *g, *omega;  // q, g interleaved (re, im)
+  const unsigned char* mask;
+  const float* h_in;  // (B, D, N, 2) or NULL
+  float* h_out;
+  int ksize;  // kernel support; >= L when not truncated
+  int bidir, shift, silu;
+};
+
+// q^k for a complex q by repeated squaring
+__device__ __forceinline__ void cpow(float qr, float qi, int k, float& outr, float& outi) {
+  float rr = 1.f, ri = 0.f;
+  while (k > 0) {
+    if (k & 1) {
+      const float t = rr * qr - ri * qi;
+      ri = rr * qi + ri * qr;
+      rr = t;
+    }
+    const float t = qr * qr - qi * qi;
+    qi = 2.f * qr * qi;
+    qr = t;
+    k >>= 1;
+  }
+  outr = rr;
+  outi = ri;
+}
+
+template <typename T, int NP, bool kTrunc>
+__global__ void __launch_bounds__(128) cema_scan_kernel(CemaArgs a) {
+  constexpr int U = 4;
+  const int sub = threadIdx.x & 3;
+  const long long row = (long long)blockIdx.x * 32 + (threadIdx.x >> 2);
+  const bool live = row < (long long)a.B * a.D;  // dead rows keep running for the shuffles
+  const int d = live ? (int)(row % a.D) : 0;
+  const int b = live ? (int)(row / a.D) : 0;
+  const int L = a.L;
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * L : nullptr;
+  const float om = __ldg(a.omega + d);
+  const size_t srow = ((size_t)b * a.D + d) * a.N;
+
+  for (int half = 0; half < (a.bidir ? 2 : 1); ++half) {
+    const bool rev = half == 1;
+    const bool pre_output = rev && a.shift;  // anti-causal half starting at lag 1: emit, then update
+    const bool last = half == (a.bidir ? 1 : 0);
+    const size_t prow = (size_t)(d + half * a.D) * a.N;
+    float pp[NP], qr[NP], qi[NP], gr[NP], gi[NP], hr[NP], hi[NP], wr[kTrunc ? NP : 1], wi[kTrunc ? NP : 1];
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+      const int n = k * 4 + sub;
+      const bool ok = n < a.N;
+      pp[k] = ok ? __ldg(a.p + prow + n) : 0.f;
+      qr[k] = ok ? __ldg(a.q + 2 * (prow + n)) : 0.f;
+      qi[k] = ok ? __ldg(a.q + 2 * (prow + n) + 1) : 0.f;
+      gr[k] = ok ? __ldg(a.g + 2 * (prow + n)) : 0.f;
+      gi[k] = ok ? __ldg(a.g + 2 * (prow + n) + 1) : 0.f;
+      const bool hin = ok && live && a.h_in != nullptr;
+      hr[k] = hin ? __ldg(a.h_in + 2 * (srow + n)) : 0.f;
+      hi[k] = hin ? __ldg(a.h_in + 2 * (srow + n) + 1) : 0.f;
+      if (kTrunc) {  // p q^ksize: what a sample leaving the window still contributes
+        cpow(qr[k], qi[k], a.ksize, wr[k], wi[k]);
+        wr[k] *= pp[k];
+        wi[k] *= pp[k];
+      }
+    }
+    for (int u0 = 0; u0 < L; u0 += U) {
+      float xv[U], xm[U], xd[U], old[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int u = u0 + j;
+        xv[j] = xm[j] = xd[j] = old[j] = 0.f;
+        if (u < L && live) {
+          const int t = rev ? L - 1 - u : u;
+          xv[j] = Elem<T>::ld(xp + t * a.xsl);
+          xm[j] = (mp && mp[t]) ? 0.f : xv[j];
+          if (kTrunc) {
+            const int td = rev ? t + a.ksize : t - a.ksize;
+            if (td >= 0 && td < L && !(mp && mp[td])) xd[j] = Elem<T>::ld(xp + td * a.xsl);
+          }
+          if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(yp + t * a.ysl);  // written by the first half
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int u = u0 + j;
+        if (u < L) {
+          float part = 0.f;
+#pragma unroll
+          for (int k = 0; k < NP; ++k) {
+            if (pre_output) part += gr[k] * hr[k] - gi[k] * hi[k];
+            float nr = fmaf(qr[k], hr[k], fmaf(-qi[k], hi[k], pp[k] * xm[j]));
+            float ni = fmaf(qi[k], hr[k], qr[k] * hi[k]);
+            if (kTrunc) {
+              nr = fmaf(-wr[k], xd[j], nr);
+              ni = fmaf(-wi[k], xd[j], ni);
+            }
+            hr[k] = nr;
+            hi[k] = ni;
+            if (!pre_output) part += gr[k] * nr - gi[k] * ni;
+          }
+          part += __shfl_xor_sync(0xffffffffu, part, 1);
+          part += __shfl_xor_sync(0xffffffffu, part, 2);
+          if (live && sub == 0) {
+            const int t = rev ? L - 1 - u : u;
+            float v = half == 0 ? fmaf(om, xv[j], part) : old[j] + part;
+            if (last && a.silu) v = siluf_(v);
+            Elem<T>::st(yp + t * a.ysl, v);
+          }
+        }
+      }
+    }
+    if (half == 0 && a.h_out && live) {
+#pragma unroll
+      for (int k = 0; k < NP; ++k) {
+        const int n = k * 4 + sub;
+        if (n < a.N) {
+          a.h_out[2 * (srow + n)] = hr[k];
+          a.h_out[2 * (srow + n) + 1] = hi[k];
+        }
+      }
+    }
+  }
+}
+
+// Decode step: one thread per (batch, channel); state read and written once.
+template <typename T>
+__global__ void __launch_bounds__(128) cema_step_kernel(const T* x, T* y, int B, int D, int N, const float* p,
+                                                        const float* q, const float* g, const float* omega,
+                                                        const float* h_in, float* h_out, int silu) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)B * D) return;
+  const int d = (int)(gid % D);
+  const float xv = Elem<T>::ld(x + gid);
+  float acc = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const size_t c = (size_t)d * N + n, s = (size_t)gid * N + n;
+    const float qr = __ldg(q + 2 * c), qi = __ldg(q + 2 * c + 1);
+    const float hr = h_in ? h_in[2 * s] : 0.f, hi = h_in ? h_in[2 * s + 1] : 0.f;
+    const float nr = fmaf(qr, hr, fmaf(-qi, hi, __ldg(p + c) * xv));
+    const float ni = fmaf(qi, hr, qr * hi);
+    h_out[2 * s] = nr;
+    h_out[2 * s + 1] = ni;
+    acc += __ldg(g + 2 * c) * nr - __ldg(g + 2 * c + 1) * ni;
+  }
+  float v = fmaf(__ldg(omega + d), xv, acc);
+  if (silu) v = siluf_(v);
+  Elem<T>::st(y + gid, v);
+}
+
+}  // namespace mega
+
+using namespace mega;
+
+extern "C" int mega_cema_coeffs(const void* alpha, const void* delta, const void* theta, const void* gamma,
+                                int param_dtype, int K, int N, float* p, float* q, float* gamma_hat,
+                                mega_stream_t stream) {
+  if (!alpha || !delta || !theta || !gamma || !p || !q || !gamma_hat) return MEGA_ERR_NULL;
+  if (!valid_dtype(param_dtype)) return MEGA_ERR_DTYPE;
+  if (K <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  const unsigned grid = (unsigned)((K * N + 255) / 256);
+  MEGA_DISPATCH_DTYPE(param_dtype, launch(cema_coeffs_kernel<T>, grid, 256, 0, stream, (const T*)alpha,
+                                          (const T*)delta, (const T*)theta, (const T*)gamma, K, N,
+                                          sqrtf(1.0f / (float)N), p, q, gamma_hat));
+  return check_launch("cema_coeffs");
+}
+
+extern "C" int mega_cema_kernel(const float* p, const float* q, const float* gamma_hat, int K, int N, int L,
+                                float* kernel_out, mega_stream_t stream) {
+  if (!p || !q || !gamma_hat || !kernel_out) return MEGA_ERR_NULL;
+  if (K <= 0 || L <= 0 || K > 65535) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  dim3 grid((L + 255) / 256, K);
+  launch(cema_kernel_kernel, grid, 256, 4 * N * sizeof(float), stream, p, q, gamma_hat, N, L, kernel_out);
+  return check_launch("cema_kernel");
+}
+
+extern "C" int mega_cema_fwd(const void* x, void* y, int dtype, int B, int D, int L, int64_t xsb, int64_t xsd,
+                             int64_t xsl, int64_t ysb, int64_t ysd, int64_t ysl, const float* p, const float* q,
+                             const float* gamma_hat, const float* omega, int N, const uint8_t* pad_mask,
+                             const float* h_in, float* h_out, unsigned flags, int truncation,
+                             mega_stream_t stream) {
+  if (!x || !y || !p || !q || !gamma_hat || !omega) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || D <= 0 || L <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (!aligned_to(x, elem_size(dtype)) || !aligned_to(y, elem_size(dtype))) return MEGA_ERR_ALIGN;
+  const bool bidir = flags & MEGA_EMA_BIDIRECTIONAL;
+  const bool trunc = truncation > 0 && truncation < L;
+  if (bidir && (h_in || h_out)) return MEGA_ERR_UNSUPPORTED;
+  if (!bidir && trunc) return MEGA_ERR_UNSUPPORTED;
+  if (x == y && (bidir || trunc || xsb != ysb || xsd != ysd || xsl != ysl)) return MEGA_ERR_STRIDE;
+  CemaArgs a{};
+  a.x = x; a.y = y; a.B = B; a.D = D; a.L = L; a.N = N;
+  a.xsb = xsb; a.xsd = xsd; a.xsl = xsl; a.ysb = ysb; a.ysd = ysd; a.ysl = ysl;
+  a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask; a.h_in = h_in; a.h_out = h_out;
+  a.ksize = trunc ? truncation : L;
+  a.bidir = bidir ? 1 : 0;
+  a.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
+  a.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
+  const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
+#define MEGA_CEMA_LAUNCH(NPV)                                                                   \
+  if (trunc) launch(cema_scan_kernel<T, NPV, true>, grid, 128, 0, stream, a);                   \
+  else launch(cema_scan_kernel<T, NPV, false>, grid, 128, 0, stream, a)
+  MEGA_DISPATCH_DTYPE(dtype, {
+    if (np == 1) { MEGA_CEMA_LAUNCH(1); }
+    else if (np == 2) { MEGA_CEMA_LAUNCH(2); }
+    else if (np == 4) { MEGA_CEMA_LAUNCH(4); }
+    else { MEGA_CEMA_LAUNCH(8); }
+  });
+#undef MEGA_CEMA_LAUNCH
+  return check_launch("cema_fwd");
+}
+
+extern "C" int mega_cema_step(const void* x, void* y, int dtype, int B, int D, const float* p, const float* q,
+                              const float* gamma_hat, const float* omega, int N, const float* h_in,
+                              float* h_out, unsigned flags, mega_stream_t stream) {
+  if (!x || !y || !p || !q || !gamma_hat || !omega || !h_out) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+  MEGA_DISPATCH_DTYPE(dtype, launch(cema_step_kernel<T>, grid, 128, 0, stream, (const T*)x, (T*)y, B, D, N, p, q,
+                                    gamma_hat, omega, h_in, h_out, (flags & MEGA_EMA_SILU) ? 1 : 0));
+  return check_launch("cema_step");
+}

@@ -1,6 +1,7 @@
 from .exponential_moving_average import MultiHeadEMA
+from .complex_exponential_moving_average import MultiHeadComplexEMA
 from .timestep_norm import TimestepNorm
 from .sequence_norm import SequenceNorm
 from .fused import sequence_norm_ema, timestep_norm_ema
 
-__all__ = ["MultiHeadEMA", "TimestepNorm", "SequenceNorm", "timestep_norm_ema", "sequence_norm_ema"]
+__all__ = ["MultiHeadEMA", "MultiHeadComplexEMA", "TimestepNorm", "SequenceNorm", "timestep_norm_ema", "sequence_norm_ema"]

@@ -27,7 +27,8 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     assert activation in (None, 'silu')
     per_feature = norm.num_groups is None or norm.num_groups == norm.num_features
     train = needs_grad(x, *norm.parameters(), *move.parameters())
-    if train or not per_feature or move.bidirectional:  # training: the two differentiable modules in turn
+    if train or not per_feature or move.bidirectional or move.complex:
+        # training, grouped statistics, bidirectional or complex poles: the two modules in turn
         xn = norm(x, padding_mask, incremental_state)
         mx = move(xn.transpose(1, 2), padding_mask, incremental_state, activation).transpose(1, 2)
         return (mx, xn) if return_normed else mx
@@ -58,7 +59,7 @@ def sequence_norm_ema(norm: SequenceNorm, move: MultiHeadEMA, x: Tensor, padding
     is per channel and the rows fit the row-resident kernel; otherwise the two modules in turn."""
     assert activation in (None, 'silu')
     train = needs_grad(x, *norm.parameters(), *move.parameters())
-    if not train and norm.num_groups is None and move.truncation is None:
+    if not train and not move.complex and norm.num_groups is None and move.truncation is None:
         p, q, g = move.coeffs()
         y = ops.sqn_ema_forward(x, norm.weight.detach().float() + 1.0, norm.bias, norm.eps, p.squeeze(-1),
                                 q.squeeze(-1), g, move.omega, padding_mask, move.bidirectional, move.shift,

@@ -489,3 +489,85 @@ def ema_coeffs_bwd(alpha, delta, beta, dp, dq, dg):
                                                   dq.data_ptr(), dg.data_ptr(), k, n,
                                                   *[o.data_ptr() for o in outs], _stream()), "ema_coeffs_bwd")
     return outs[0].unsqueeze(-1), outs[1].unsqueeze(-1), outs[2].unsqueeze(-1), outs[3]
+
+
+# --------------------------------------------------------------------- complex EMA
+def cema_coeffs(alpha, delta, theta, gamma):
+    """(p (K, N) fp32, q (K, N) complex64, gamma_hat (K, N) complex64) of the complex EMA."""
+    _cuda(alpha, delta, theta, gamma)
+    k, n = alpha.shape[0], alpha.shape[1]
+    dt = alpha.dtype
+    args = [t.detach().to(dt).contiguous() for t in (alpha, delta, theta, gamma)]
+    p = torch.empty(k, n, device=alpha.device, dtype=torch.float32)
+    q = torch.empty(k, n, 2, device=alpha.device, dtype=torch.float32)
+    g = torch.empty_like(q)
+    with torch.cuda.device(alpha.device):
+        _lib.check(_lib.lib().mega_cema_coeffs(*[a.data_ptr() for a in args], _dt(args[0]), k, n,
+                                               p.data_ptr(), q.data_ptr(), g.data_ptr(), _stream()), "cema_coeffs")
+    return p, torch.view_as_complex(q), torch.view_as_complex(g)
+
+
+def _c64(t):
+    """complex64 contiguous tensor -> its interleaved float view (no copy when already so)."""
+    if t is None:
+        return None
+    t = t.detach()
+    if not t.is_complex():
+        t = t.to(torch.complex64)
+    elif t.dtype != torch.complex64:
+        t = t.to(torch.complex64)
+    return torch.view_as_real(t.contiguous())
+
+
+def cema_kernel(p, q, g, length):
+    """k (K, L) fp32 = Re(sum_n p gamma_hat q^l)."""
+    _cuda(p, q, g)
+    p, q, g = _f32c(p), _c64(q), _c64(g)
+    k, n = p.shape
+    out = torch.empty(k, length, device=p.device, dtype=torch.float32)
+    with torch.cuda.device(p.device):
+        _lib.check(_lib.lib().mega_cema_kernel(p.data_ptr(), q.data_ptr(), g.data_ptr(), k, n, length,
+                                               out.data_ptr(), _stream()), "cema_kernel")
+    return out
+
+
+def cema_forward(x, p, q, g, omega, padding_mask=None, h_in=None, want_state=False, bidirectional=False,
+                 shift=True, truncation=None, silu=False):
+    """Complex EMA layer forward on x (B, D, L) with any strides; q, g complex64 (K, N); the state
+    is complex64 (B, D, N).  Returns y like x, and the new state when ``want_state``."""
+    _cuda(x, p, q, g, omega, padding_mask, h_in)
+    bsz, dim, length = x.shape
+    p, q, g, omega = _f32c(p), _c64(q), _c64(g), _f32c(omega).reshape(-1)
+    n = p.shape[1]
+    if p.shape[0] != (2 * dim if bidirectional else dim):
+        raise ValueError("coefficient rows %d do not match embed_dim %d" % (p.shape[0], dim))
+    mask = _mask_u8(padding_mask, bsz, length)
+    out = _like(x)
+    h_in = _c64(h_in)
+    h_out = torch.empty(bsz, dim, n, 2, device=x.device, dtype=torch.float32) if want_state else None
+    flags = (EMA_BIDIRECTIONAL if bidirectional else 0) | (0 if shift else EMA_NO_SHIFT) | (EMA_SILU if silu else 0)
+    trunc = 0 if truncation is None or truncation < 1 else int(truncation)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_cema_fwd(
+            x.data_ptr(), out.data_ptr(), _dt(x), bsz, dim, length, *x.stride(), *out.stride(),
+            p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n,
+            _ptr(mask), _ptr(h_in), _ptr(h_out), flags, trunc, _stream()), "cema_fwd")
+    return (out, torch.view_as_complex(h_out)) if want_state else out
+
+
+def cema_step(x, p, q, g, omega, h=None, silu=False):
+    """One decode step.  x (B, D) or (B, D, 1); returns (y like x, h' (B, D, N) complex64)."""
+    _cuda(x, p, q, g, omega, h)
+    shape = x.shape
+    x2 = x.reshape(shape[0], shape[1]).contiguous()
+    bsz, dim = x2.shape
+    p, q, g, omega = _f32c(p), _c64(q), _c64(g), _f32c(omega).reshape(-1)
+    n = p.shape[1]
+    h = _c64(h)
+    h_out = torch.empty(bsz, dim, n, 2, device=x.device, dtype=torch.float32)
+    y = torch.empty_like(x2)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_cema_step(x2.data_ptr(), y.data_ptr(), _dt(x2), bsz, dim, p.data_ptr(),
+                                             q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(h),
+                                             h_out.data_ptr(), EMA_SILU if silu else 0, _stream()), "cema_step")
+    return y.view(shape), torch.view_as_complex(h_out)

@@ -321,6 +321,38 @@ MEGA_API int mega_ema_coeffs_bwd(const float* alpha, const float* delta, const f
                         const float* dq, const float* dgamma_hat, int K, int N, float* dalpha, float* ddelta,
                         float* dbeta, float* dgamma, mega_stream_t stream);
 
+/*
+ * ---- Complex EMA (MultiHeadComplexEMA) ----------------------------------------------------
+ * Poles q_n = (1 - sigmoid(alpha) sigmoid(delta)) e^{i theta_n}, theta_n = (n + 1) sigmoid(theta)
+ * 2 pi / N; input gain p = sigmoid(alpha); gamma_hat = (gamma_re + i gamma_im) / sqrt(N).
+ * Complex arrays are interleaved (re, im) fp32: q, gamma_hat are (K, N, 2); states are (B, D, N, 2)
+ * — the memory of a complex64 tensor.
+ *
+ * mega_cema_coeffs: alpha, delta (K, N[, 1]), theta (K[, 1, 1]), gamma (K, N, 2) in param_dtype
+ *   -> p (K, N), q (K, N, 2), gamma_hat (K, N, 2).
+ *   Replaces: MultiHeadComplexEMA._calc_coeffs (complex_exponential_moving_average.py:79-96).
+ * mega_cema_kernel: k[row, l] = Re(sum_n p gamma_hat q^l), (K, L) fp32.
+ *   Replaces: _compute_kernel (:98-109) / the weight half of ema_parameters_fwd.
+ * mega_cema_fwd: same contract as mega_ema_fwd (strides, mask, flags, truncation for the
+ *   bidirectional form, carried state in / out for the causal form) with complex poles.
+ *   Replaces: BaseMovingLayer.forward (base_moving_average.py:120-172) for the complex layer:
+ *   ema_parameters_fwd + fftconv / bidirectional_fftconv + bias + ema_hidden_fwd + residual.
+ * mega_cema_step: single-token update, x, y (B, D) contiguous; h_in may be NULL or equal h_out.
+ *   Replaces: BaseMovingLayer.one_step (:105-118) + the omega residual.
+ */
+MEGA_API int mega_cema_coeffs(const void* alpha, const void* delta, const void* theta, const void* gamma,
+                     int param_dtype, int K, int N, float* p, float* q, float* gamma_hat,
+                     mega_stream_t stream);
+MEGA_API int mega_cema_kernel(const float* p, const float* q, const float* gamma_hat, int K, int N, int L,
+                     float* kernel_out, mega_stream_t stream);
+MEGA_API int mega_cema_fwd(const void* x, void* y, int dtype, int B, int D, int L, int64_t xsb, int64_t xsd,
+                  int64_t xsl, int64_t ysb, int64_t ysd, int64_t ysl, const float* p, const float* q,
+                  const float* gamma_hat, const float* omega, int N, const uint8_t* pad_mask,
+                  const float* h_in, float* h_out, unsigned flags, int truncation, mega_stream_t stream);
+MEGA_API int mega_cema_step(const void* x, void* y, int dtype, int B, int D, const float* p, const float* q,
+                   const float* gamma_hat, const float* omega, int N, const float* h_in, float* h_out,
+                   unsigned flags, mega_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

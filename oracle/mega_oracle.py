@@ -229,6 +229,79 @@ def ema_one_step(x, p, q, g, h):
 
 
 # --------------------------------------------------------------------------
+# Complex EMA (MultiHeadComplexEMA)
+# --------------------------------------------------------------------------
+def cema_coeffs(alpha, delta, theta, gamma, dtype=torch.float32):
+    """p (K, N) real, q (K, N) complex, gamma_hat (K, N) complex.
+
+    fairseq/modules/complex_exponential_moving_average.py:79-96:
+      theta_n = n * sigmoid(theta) * 2 pi / N for n = 1..N ;
+      p = sigmoid(alpha) ; q = polar(1 - sigmoid(alpha) sigmoid(delta), theta_n) ;
+      gamma_hat = (gamma[..., 0] + i gamma[..., 1]) * sqrt(1 / N).
+    """
+    n = alpha.shape[1]
+    th = torch.sigmoid(theta.to(dtype)) * (2 * math.pi / n)          # K 1 1
+    wave = torch.arange(1, n + 1, dtype=dtype).view(1, n, 1)
+    th = wave * th                                                    # K N 1
+    a = torch.sigmoid(alpha.to(dtype))
+    d = torch.sigmoid(delta.to(dtype))
+    q = torch.polar(1.0 - a * d, th)
+    g = torch.view_as_complex(gamma.to(dtype).contiguous()) * math.sqrt(1.0 / n)
+    return a.squeeze(-1), q.squeeze(-1), g
+
+
+def cema_forward_recurrence(x, alpha, delta, theta, gamma, omega, padding_mask=None,
+                            bidirectional=False, shift=True, truncation=None,
+                            h=None, return_state=False, silu=False):
+    """Complex EMA layer in float64 as the recurrence itself.
+
+    h_t = q h_{t-1} + p x~_t (complex), y_t = Re(sum_n gamma_hat_n h_{n,t}) + omega x_t:
+    base_moving_average.py:105-118 (``one_step``) applied L times with the complex
+    coefficients; mask, residual, bidirectional halves, shift and truncation as in
+    ``ema_forward_recurrence``.  omega is (D, 1) or (D,).
+    """
+    x64 = x.double()
+    bsz, dim, length = x64.shape
+    p, q, g = cema_coeffs(alpha, delta, theta, gamma, dtype=torch.float64)
+    xm = x64
+    if padding_mask is not None:
+        xm = x64 * (1.0 - padding_mask.unsqueeze(1).double())
+    ksize = length if truncation is None or truncation < 1 else min(truncation, length)
+
+    def scan(xs, pp, qq, gg, h0):
+        st = torch.zeros(bsz, dim, pp.shape[1], dtype=torch.complex128) if h0 is None else h0.to(torch.complex128)
+        ys = torch.empty_like(xs)
+        hist = []
+        qk = qq ** ksize
+        for t in range(length):
+            st = qq * st + pp * xs[:, :, t:t + 1]
+            if ksize < length:
+                hist.append(st)
+                eff = st - (qk * hist[t - ksize] if t >= ksize else 0.0)
+            else:
+                eff = st
+            ys[:, :, t] = (eff * gg).sum(-1).real
+        return ys, st
+
+    if not bidirectional:
+        y, st = scan(xm, p, q, g, h)
+    else:
+        assert h is None and not return_state
+        y, _ = scan(xm, p[:dim], q[:dim], g[:dim], None)
+        xr = xm.flip(-1)
+        if shift:
+            xr = torch.nn.functional.pad(xr, (1, 0))[..., :length]
+        yb, _ = scan(xr, p[dim:], q[dim:], g[dim:], None)
+        y = y + yb.flip(-1)
+    y = y + x64 * omega.double().view(dim, 1)
+    if silu:
+        y = y * torch.sigmoid(y)
+    if return_state:
+        return y, st
+    return y
+
+
+# --------------------------------------------------------------------------
 # Welford helpers (fairseq/csrc/utils.h:56-76)
 # --------------------------------------------------------------------------
 def _welford_update(m0, m1, m2, x):

@@ -5,7 +5,7 @@ Run in a container where the reference checkout is mounted (default
 ``oracle/_ref/mega_ref_cpu.so`` (python oracle/build_ref.py).  The fixtures are
 committed; nothing at test time reads the reference checkout.
 
-Usage: python tests/golden/make_golden.py [all|forward|backward].
+Usage: python tests/golden/make_golden.py [all|forward|backward|cema].
 
 What runs:
   * the reference's CPU C++ ops (timestep_norm_fwd, group_timestep_norm_fwd,
@@ -321,8 +321,61 @@ def backward_fixtures():
         npz(tag, x=x, dy=dy, mask=mask, gamma=gamma, beta=beta, length_last=length_last, dx=dx, dgamma=dg, dbeta=db)
 
 
+def cema_fixtures():
+    """MultiHeadComplexEMA as the reference ships it (rotation on, default init)."""
+    ops, cema, tsn, sqn = import_reference()
+    gen = torch.Generator().manual_seed(20251127)
+    torch.manual_seed(20251127)   # reset_parameters draws from the global generator
+
+    def params_of(m):
+        return dict(alpha=m.alpha, delta=m.delta, theta=m.theta, gamma=m.gamma, omega=m.omega)
+
+    for tag, (bsz, dim, length, ndim, bidir, shift, trunc, pad) in {
+        "cema_uni_n16": (3, 8, 50, 16, False, True, None, 0.25),
+        "cema_uni_n3": (2, 5, 33, 3, False, True, None, 0.0),
+        "cema_bidir_shift": (3, 6, 41, 16, True, True, None, 0.5),
+        "cema_bidir_noshift": (2, 6, 32, 16, True, False, None, 0.3),
+        "cema_bidir_trunc": (2, 4, 40, 16, True, True, 7, 0.3),
+    }.items():
+        m = cema.MultiHeadComplexEMA(dim, ndim=ndim, bidirectional=bidir, truncation=trunc, shift=shift).eval()
+        with torch.no_grad():
+            m.gamma[:, :, 1].normal_(0, 1, generator=gen)   # exercise the imaginary output weights too
+            x = torch.randn(bsz, dim, length, generator=gen)
+            mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None
+            y = m(x, mask, None)
+            k, _ = m.kernel(length, None)
+        npz(tag, x=x, mask=(mask if mask is not None else np.zeros((0,), bool)), y=y, kernel=k,
+            bidirectional=bidir, shift=shift, truncation=(-1 if trunc is None else trunc), **params_of(m))
+
+    # incremental: chunks through the reference CPU ops, then the closed-form single step
+    bsz, dim, length, ndim, chunk = 3, 6, 48, 16, 16
+    m = cema.MultiHeadComplexEMA(dim, ndim=ndim).eval()
+    fftconv = sys.modules["fairseq.modules.fused_ops.fftconv"]._fftconv_fwd
+    with torch.no_grad():
+        m.gamma[:, :, 1].normal_(0, 1, generator=gen)
+        x = torch.randn(bsz, dim, length, generator=gen)
+        pc, qc, gc = m._calc_coeffs()
+        hh, ys, hs = None, [], []
+        for i in range(0, length, chunk):
+            xc = x[..., i:i + chunk].contiguous()
+            w, b, _ = ops.ema_parameters_fwd(pc, qc.log(), gc, hh, chunk)
+            yy = fftconv(xc, w)[0]
+            if b is not None:
+                yy = yy + b
+            hh, _ = ops.ema_hidden_fwd(xc, pc, qc.log(), hh)
+            ys.append(yy + xc * m.omega)
+            hs.append(torch.view_as_real(hh).clone())
+        y1, h1 = m.one_step(x[..., :1], hx=None)
+        y2, h2 = m.one_step(x[..., 1:2], hx=h1)
+        y_full = m(x, None, None)
+    npz("cema_incremental", x=x, chunk=chunk, y=torch.cat(ys, -1), y_full=y_full, states=torch.stack(hs),
+        step_y1=y1, step_h1=torch.view_as_real(h1), step_y2=y2, step_h2=torch.view_as_real(h2), **params_of(m))
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "cema"):
+        cema_fixtures()
     if which in ("all", "forward"):
         main()
     if which in ("all", "backward"):
