@@ -122,7 +122,7 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
   return (uint32_t)(row * (kCg * 16) + (cg << 4));
 }
 
-template <bool kNorm, int kCg>
+template <bool kNorm, int kCg, bool kSilu>
 __global__ void __launch_bounds__(kCg * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        StreamArgs a) {
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         mma_bf16(Y1, xa0, xa1, xa2, xa3, tr.y, tr.x, Z1[0], Z1[1], Z1[2], Z1[3]);
         yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
-        if (a.silu) {
+        if (kSilu) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) yv[h2][j] = silu_tanh(yv[h2][j]);
         }
@@ -463,7 +463,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   }
 }
 
-template <bool kNorm, int kCg>
+template <bool kNorm, int kCg, bool kSilu>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s) {
   using C = Cfg<kCg>;
@@ -471,7 +471,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   CUtensorMap tx, ty;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
   if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, sw)) return false;
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -508,12 +508,12 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   };
   const int opt = g_options[OPT_MMA_TILE].load();
   const bool use7 = opt == 7 || (opt != 8 && waves_cost(56) < waves_cost(64));
-  if (norm) {
-    return use7 ? launch_variant<true, 7>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-                : launch_variant<true, 8>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
-  }
-  return use7 ? launch_variant<false, 7>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-              : launch_variant<false, 8>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
+#define MEGA_MMA_VARIANT(NORM, SILU)                                                          \
+  (use7 ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)              \
+        : launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
+  if (norm) return a_in.silu ? MEGA_MMA_VARIANT(true, true) : MEGA_MMA_VARIANT(true, false);
+  return a_in.silu ? MEGA_MMA_VARIANT(false, true) : MEGA_MMA_VARIANT(false, false);
+#undef MEGA_MMA_VARIANT
 }
 
 cudaError_t mma_cl_read_device_error(int* v, bool reset) { return read_device_error(v, reset); }
