@@ -199,7 +199,7 @@ def job_throughput(tokens_per_rank, world, steps, total_ms):
 
 
 # DRAM bytes per token of the tensor-core kernel from its ncu capture (profiles/
-# tsn_ema_mma_kernel__b32_l4096_full.md: 1036.3 MB for 32 x 4096 tokens of 2048 bf16 channels);
+# tsn_ema_mma_kernel__b32_l4096.md: 1036.3 MB for 32 x 4096 tokens of 2048 bf16 channels);
 # it scales with the tokens of a launch.
 NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = 1036.28e6 / (32 * 4096)
 
