@@ -324,13 +324,22 @@ __global__ void __launch_bounds__(kCg * 32, 1)
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
-          float dv[8];
+          // deviations from the centre, two positions (t, t + 1 of one row) per packed operation
+          f32x2 dv2[4];
+          {
+            const f32x2 ncm2 = pack2(-cm, -cm);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dv[j] = xf[j] - cm;
+            for (int jp = 0; jp < 4; ++jp) dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
+          }
           {  // sum of (x - c)^2 on top of the running sum of squared deviations
             float sq[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sq[j] = dv[j] * dv[j];
+            for (int jp = 0; jp < 4; ++jp) {
+              float lo, hi;
+              unpack2(dv2[jp], lo, hi);
+              sq[2 * jp] = lo * lo;
+              sq[2 * jp + 1] = hi * hi;
+            }
             float E[4], F[4], D0[4], D1[4], T[4];
             mma_tf32(E, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
@@ -357,12 +366,19 @@ __global__ void __launch_bounds__(kCg * 32, 1)
           m2_run[e] = fmaf(-shift * shift, n_end, m2_run[e] + tot2);
           const uint2 wbu = lds64(sm_s + kOffWB + ch * 8);
           const float2 wb = make_float2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
+          {
+            const f32x2 ncm2 = pack2(-cm, -cm), eps2 = pack2(eps, eps);
+            const f32x2 w2 = pack2(wb.x, wb.x), b2 = pack2(wb.y, wb.y);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float u = fmaf(S1[j], invn[j], -cm);  // mean - c
-            const float ve = fmaxf(fmaf(S2[j], invn[j], eps) - u * u, eps);
-            const float sc = rsqrt_fast(ve) * wb.x;
-            xn[j] = fmaf(dv[j] - u, sc, wb.y);
+            for (int jp = 0; jp < 4; ++jp) {
+              const f32x2 in2 = pack2(invn[2 * jp], invn[2 * jp + 1]);
+              const f32x2 u2 = fma2(pack2(S1[2 * jp], S1[2 * jp + 1]), in2, ncm2);  // mean - c
+              const f32x2 e2 = fma2(pack2(S2[2 * jp], S2[2 * jp + 1]), in2, eps2);
+              float va, vb;
+              unpack2(sub2(e2, mul2(u2, u2)), va, vb);
+              const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(va, eps)), rsqrt_fast(fmaxf(vb, eps))), w2);
+              unpack2(fma2(sub2(dv2[jp], u2), sc2, b2), xn[2 * jp], xn[2 * jp + 1]);
+            }
           }
         } else {
 #pragma unroll

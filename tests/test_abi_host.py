@@ -53,6 +53,45 @@ def test_argument_rejection_without_gpu():
     assert lib.mega_ema_step(one, one, 0, 1, 1, one, one, one, one, 16, None, None, 0, None) == 1
 
 
+def test_argument_rejection_training_and_complex_entry_points():
+    lib, _ = _lib()
+    one = ctypes.c_void_p(16)
+    st9 = [1] * 9
+    # mega_ema_bwd: null, SiLU flag, truncation, state with bidirectional, ndim
+    ema = lambda dy, N, flags, trunc, h: lib.mega_ema_bwd(dy, one, one, 0, 1, 1, 8, *st9, one, one, one, one, N, None, h,
+                                                          None, flags, trunc, one, one, one, one, None, None)
+    assert ema(None, 16, 0, 0, None) == 1
+    assert ema(one, 16, 4, 0, None) == 7
+    assert ema(one, 16, 0, 3, None) == 7
+    assert ema(one, 16, 1, 0, one) == 7
+    assert ema(one, 40, 0, 0, None) == 6
+    # mega_timestep_norm_bwd: grouped form needs group_mean; groups must divide features; group size cap
+    tsn = lambda D, G, gm: lib.mega_timestep_norm_bwd(one, one, one, 0, 1, 1, D, *st9, None, None, one, one, one, one, gm,
+                                                      one, None, G, one, one, one, one, None)
+    assert tsn(12, 3, None) == 1
+    assert tsn(10, 3, one) == 3
+    assert tsn(1024, 2, one) == 7
+    # mega_timestep_norm_fwd_train: the saves are required
+    assert lib.mega_timestep_norm_fwd_train(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 8,
+                                            1e-5, one, one, one, None, None, None, None) == 1
+    assert lib.mega_timestep_norm_fwd_train(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 2,
+                                            1e-5, one, one, one, one, one, None, None) == 1
+    # mega_sequence_norm_bwd: the grouped form is not built
+    assert lib.mega_sequence_norm_bwd(one, one, one, 0, 1, 8, 4, *st9, one, one, one, one, None, 2, one, one, None) == 7
+    assert lib.mega_sequence_norm_bwd(one, one, one, 5, 1, 8, 4, *st9, one, one, one, one, None, 8, one, one, None) == 2
+    # complex EMA: same envelope rules as the real layer
+    cema = lambda x, N, flags, trunc, h: lib.mega_cema_fwd(x, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, N,
+                                                           None, h, None, flags, trunc, None)
+    assert cema(None, 16, 0, 0, None) == 1
+    assert cema(one, 0, 0, 0, None) == 6
+    assert cema(one, 16, 1, 0, one) == 7
+    assert cema(one, 16, 0, 4, None) == 7
+    assert lib.mega_cema_step(one, one, 0, 1, 1, one, one, one, one, 16, None, None, 0, None) == 1
+    assert lib.mega_cema_coeffs(one, one, one, one, 7, 4, 16, one, one, one, None) == 2
+    assert lib.mega_gate_qk(one, 4, one, one, one, 8, one, 8, 0, 2, 8, 1e-5, None) == 4  # pitch below the row length
+    assert lib.mega_ema_coeffs_bwd(one, one, one, one, one, one, 0, 16, one, one, one, one, None) == 3
+
+
 def test_ops_refuse_cpu_tensors():
     import fairseq_apollo_b200 as M
     m = M.MultiHeadEMA(4, ndim=16).eval()
