@@ -114,7 +114,8 @@ __device__ __forceinline__ uint32_t bf16_bits(float v) {
 
 // Byte offset of the 16-byte vector (sequence, position, column group) inside a stage.  kCg = 8:
 // rows are 128 bytes and TMA applies its 128-byte swizzle (chunk index XOR row mod 8); kCg = 7:
-// rows are 112 bytes, unswizzled (the odd pitch already staggers the banks).
+// rows are 112 bytes, unswizzled (the odd pitch already staggers the banks); kCg = 4, 2 (the
+// narrow tiles of small problems): 64- and 32-byte rows, unswizzled.
 template <int kCg>
 __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
   const int row = seq * kStep + t;
@@ -312,15 +313,20 @@ __global__ void __launch_bounds__(kCg * 32, 1)
           const float cm = mu_run[e];
           float S1[8], S2[8];
           float tot1, tot2;
-          {  // sum of x: exact (bf16 inputs, fp32 accumulation); carry = count * running mean
-            float E[4], F[4], D0[4], D1[4], T[4];
+          // Prefix sums inside the two chunks as tf32 MMAs against 0/1 matrices, two MMAs deep
+          // (first half of the chunk, then second half on top of the first half's total); the
+          // carries (running total; plus chunk 0's total for chunk 1) are added afterwards, which
+          // costs a few fp32 adds but keeps the dependent MMA chain short.
+          float c1a, c1b;  // carries of rows g / g + 8 for the sum of x
+          {  // sum of x: exact (bf16 inputs, fp32 accumulation)
+            float E[4], F[4], D0[4], D1[4];
+            mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(E, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, E[0], E[1], E[2], E[3]);
             mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            const float c0 = s1_run[e], c1 = s1_run[e] + F[0];
-            mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, c0, c0, c1, c1);
-            mma_tf32(T, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, c0, c0, c1, c1);
-            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, T[0], T[1], T[2], T[3]);
-            tot1 = c1 + F[2];
+            c1a = s1_run[e];
+            c1b = c1a + F[0];
+            tot1 = c1b + F[2];
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
@@ -331,7 +337,8 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
           }
-          {  // sum of (x - c)^2 on top of the running sum of squared deviations
+          float c2a, c2b;  // carries of rows g / g + 8 for the sum of squared deviations
+          {  // sum of (x - c)^2
             float sq[8];
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
@@ -340,13 +347,13 @@ __global__ void __launch_bounds__(kCg * 32, 1)
               sq[2 * jp] = lo * lo;
               sq[2 * jp + 1] = hi * hi;
             }
-            float E[4], F[4], D0[4], D1[4], T[4];
+            float E[4], F[4], D0[4], D1[4];
+            mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(E, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, E[0], E[1], E[2], E[3]);
             mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            const float c0 = m2_run[e], c1 = m2_run[e] + F[0];
-            mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, c0, c0, c1, c1);
-            mma_tf32(T, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, c0, c0, c1, c1);
-            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, T[0], T[1], T[2], T[3]);
+            c2a = m2_run[e];
+            c2b = c2a + F[0];
             tot2 = F[0] + F[2];
             S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
             S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
@@ -372,8 +379,9 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
               const f32x2 in2 = pack2(invn[2 * jp], invn[2 * jp + 1]);
-              const f32x2 u2 = fma2(pack2(S1[2 * jp], S1[2 * jp + 1]), in2, ncm2);  // mean - c
-              const f32x2 e2 = fma2(pack2(S2[2 * jp], S2[2 * jp + 1]), in2, eps2);
+              const float k1 = jp < 2 ? c1a : c1b, k2 = jp < 2 ? c2a : c2b;
+              const f32x2 u2 = fma2(add2(pack2(S1[2 * jp], S1[2 * jp + 1]), pack2(k1, k1)), in2, ncm2);  // mean - c
+              const f32x2 e2 = fma2(add2(pack2(S2[2 * jp], S2[2 * jp + 1]), pack2(k2, k2)), in2, eps2);
               float va, vb;
               unpack2(sub2(e2, mul2(u2, u2)), va, vb);
               const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(va, eps)), rsqrt_fast(fmaxf(vb, eps))), w2);
@@ -399,6 +407,9 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         float H0[4], H1[4];
         mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y, 0.f, 0.f, 0.f, 0.f);  // poles 2q, 2q+1
         mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
+        float W0[4], W1[4];  // Toeplitz term of the outputs (positions 0..7 and 8..15 of each chunk)
+        mma_bf16(W0, xa0, xa1, xa2, xa3, tr.x, 0u, 0.f, 0.f, 0.f, 0.f);
+        mma_bf16(W1, xa0, xa1, xa2, xa3, tr.y, tr.x, 0.f, 0.f, 0.f, 0.f);
         // states entering chunk 0 (= carried) and chunk 1, and the new carry
         const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
         float hs1[4];
@@ -412,11 +423,11 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
         const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
         const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
-        float Y0[4], Y1[4], Z0[4], Z1[4];
-        mma_bf16(Z0, ha0, ha1, ha2, ha3, gr.x, gr.y, 0.f, 0.f, 0.f, 0.f);
-        mma_bf16(Z1, ha0, ha1, ha2, ha3, gr.z, gr.w, 0.f, 0.f, 0.f, 0.f);
-        mma_bf16(Y0, xa0, xa1, xa2, xa3, tr.x, 0u, Z0[0], Z0[1], Z0[2], Z0[3]);
-        mma_bf16(Y1, xa0, xa1, xa2, xa3, tr.y, tr.x, Z1[0], Z1[1], Z1[2], Z1[3]);
+        // outputs: the carried-state term accumulates onto the Toeplitz term, which does not
+        // wait for the states (W0, W1 are issued alongside H0, H1 above)
+        float Y0[4], Y1[4];
+        mma_bf16(Y0, ha0, ha1, ha2, ha3, gr.x, gr.y, W0[0], W0[1], W0[2], W0[3]);
+        mma_bf16(Y1, ha0, ha1, ha2, ha3, gr.z, gr.w, W1[0], W1[1], W1[2], W1[3]);
         yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
         if (kSilu) {
@@ -514,19 +525,27 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   if (a_in.N > 16 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
   if (a_in.h_out && (a_in.L % kStep) != 0) return false;
   if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
-  // Tile width: 64 channels, or 56 when that fills the 148 SMs in fewer or fuller waves
-  // (one CTA per SM; e.g. D = 2048 with 64 sequences: 37 x 8 = 296 CTAs = two full waves).
+  // Tile width.  Large problems: 64 channels, or 56 when that fills the 148 SMs in fewer or
+  // fuller waves (one CTA per SM; e.g. D = 2048 with 64 sequences: 37 x 8 = 296 CTAs = two full
+  // waves).  Problems too small to give every SM a wide tile: 32 or 16 channels per CTA, so
+  // that the few (8 sequences x 8 channels) strips there are spread over the SMs; a strip is
+  // a serial chain along the sequence, so its speed depends on how few warps share its SM.
   const long long seq_groups = (a_in.B + kSeq - 1) / kSeq;
+  auto ctas = [&](int ch) -> long long { return ((a_in.D + ch - 1) / ch) * seq_groups; };
   auto waves_cost = [&](int ch) -> double {
-    const long long ctas = ((a_in.D + ch - 1) / ch) * seq_groups;
-    const long long waves = (ctas + 147) / 148;
+    const long long waves = (ctas(ch) + 147) / 148;
     return (double)waves * ch;  // time ~ waves x work per CTA
   };
-  const int opt = g_options[OPT_MMA_TILE].load();
-  const bool use7 = opt == 7 || (opt != 8 && waves_cost(56) < waves_cost(64));
-#define MEGA_MMA_VARIANT(NORM, SILU)                                                          \
-  (use7 ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)              \
-        : launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
+  int tile = g_options[OPT_MMA_TILE].load();
+  if (tile != 2 && tile != 4 && tile != 7 && tile != 8) {
+    if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
+    else tile = ctas(32) >= 111 ? 4 : 2;
+  }
+#define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
+  (tile == 7   ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
+   : tile == 8 ? launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
+   : tile == 4 ? launch_variant<NORM, 4, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
+               : launch_variant<NORM, 2, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
   if (norm) return a_in.silu ? MEGA_MMA_VARIANT(true, true) : MEGA_MMA_VARIANT(true, false);
   return a_in.silu ? MEGA_MMA_VARIANT(false, true) : MEGA_MMA_VARIANT(false, false);
 #undef MEGA_MMA_VARIANT
