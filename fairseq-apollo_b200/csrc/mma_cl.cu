@@ -1,7 +1,7 @@
 // Tensor-core variant of the fused TimestepNorm -> causal EMA (and of the EMA alone) for bf16
 // activations with contiguous channels and no padding mask.
 //
-// Work split.  A CTA owns kCg column groups (8 channels = 16 bytes each; kCg = 8 or 7) of 8
+// Work split.  A CTA owns kCg column groups (8 channels = 16 bytes each; kCg = 8, 7, 4 or 2) of 8
 // sequences and walks time in steps of 32 positions.  Warp w owns column group w.  For one
 // channel the 8 sequences x 2 consecutive 16-position chunks of a step form the 16 rows of
 // warp-level MMAs (row g = sequence g, chunk 0; row g + 8 = sequence g, chunk 1), so every carry
@@ -12,12 +12,14 @@
 //
 // Math per channel and step (h = pole states, C = 16):
 //   TimestepNorm : with c the running mean at the start of the step and d = x - c, the prefix
-//                  sums of d and d^2 inside each chunk are products with 0/1 matrices (tf32
-//                  MMAs); the running second moment enters as the accumulator input.  Centring
+//                  sums of x and d^2 inside each half chunk are products with a 0/1 triangular
+//                  matrix (one tf32 MMA per half); the totals of the halves are the last prefixes,
+//                  handed round by a shuffle, and the running totals are added in fp32.  Centring
 //                  keeps mean^2 small against the variance, so the tf32 truncation of the MMA
 //                  inputs (11 significant bits) only costs ~2^-11 of the variance.  Then
-//                  u = sum(d)/n, mean = c + u, var = (M2 + sum(d^2))/n - u^2,
-//                  xn = (d - u) * rstd * w + b.
+//                  u = sum(x)/n - c, var = (M2 + sum(d^2))/n - u^2, xn = (d - u) * rstd * w + b.
+//                  MMAs that depend on one another are what a warp waits for (two warps per
+//                  scheduler cannot hide it), so no MMA here consumes another MMA's result.
 //   EMA          : y = T xn + G h_start   (T: 16x16 lower-triangular Toeplitz of the kernel
 //                  k[l] = sum_n p g q^l, omega folded into k[0]; G[t][n] = g q^(t+1))
 //                  h_local = P xn          (P[n][t] = p q^(15-t));  h_next = q^16 h + h_local.
@@ -313,20 +315,21 @@ __global__ void __launch_bounds__(kCg * 32, 1)
           const float cm = mu_run[e];
           float S1[8], S2[8];
           float tot1, tot2;
-          // Prefix sums inside the two chunks as tf32 MMAs against 0/1 matrices, two MMAs deep
-          // (first half of the chunk, then second half on top of the first half's total); the
-          // carries (running total; plus chunk 0's total for chunk 1) are added afterwards, which
-          // costs a few fp32 adds but keeps the dependent MMA chain short.
-          float c1a, c1b;  // carries of rows g / g + 8 for the sum of x
+          // Prefix sums inside each half (8 positions) of the two chunks: one tf32 MMA against the
+          // 0/1 upper-triangular matrix per half.  The total of a half is its last prefix, held
+          // by the lane with q = 3; a shuffle hands it to the row's other lanes, and the carries
+          // (running total + totals of the halves before) are added afterwards in fp32.
+          const int src3 = lane | 3;
+          float k1[4];  // carry of the sum of x for (row g, first half), (g, second), (g + 8, first), (g + 8, second)
           {  // sum of x: exact (bf16 inputs, fp32 accumulation)
-            float E[4], F[4], D0[4], D1[4];
+            float D0[4], D1[4];
             mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
-            mma_tf32(E, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
-            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, E[0], E[1], E[2], E[3]);
-            mma_tf32(F, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            c1a = s1_run[e];
-            c1b = c1a + F[0];
-            tot1 = c1b + F[2];
+            mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
+            k1[0] = s1_run[e];
+            k1[1] = k1[0] + __shfl_sync(0xffffffffu, D0[1], src3);
+            k1[2] = k1[1] + __shfl_sync(0xffffffffu, D1[1], src3);
+            k1[3] = k1[2] + __shfl_sync(0xffffffffu, D0[3], src3);
+            tot1 = k1[3] + __shfl_sync(0xffffffffu, D1[3], src3);
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
@@ -337,7 +340,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
           }
-          float c2a, c2b;  // carries of rows g / g + 8 for the sum of squared deviations
+          float k2[4];  // the same carries for the sum of squared deviations
           {  // sum of (x - c)^2
             float sq[8];
 #pragma unroll
@@ -347,14 +350,16 @@ __global__ void __launch_bounds__(kCg * 32, 1)
               sq[2 * jp] = lo * lo;
               sq[2 * jp + 1] = hi * hi;
             }
-            float E[4], F[4], D0[4], D1[4];
+            float D0[4], D1[4];
             mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
-            mma_tf32(E, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
-            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, E[0], E[1], E[2], E[3]);
-            mma_tf32(F, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, E[0], E[1], E[2], E[3]);
-            c2a = m2_run[e];
-            c2b = c2a + F[0];
-            tot2 = F[0] + F[2];
+            mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
+            const float ea = __shfl_sync(0xffffffffu, D0[1], src3), fa = __shfl_sync(0xffffffffu, D1[1], src3);
+            const float eb = __shfl_sync(0xffffffffu, D0[3], src3), fb = __shfl_sync(0xffffffffu, D1[3], src3);
+            k2[0] = m2_run[e];
+            k2[1] = k2[0] + ea;
+            k2[2] = k2[1] + fa;
+            k2[3] = k2[2] + eb;
+            tot2 = (ea + fa) + (eb + fb);
             S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
             S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
           }
@@ -379,9 +384,8 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
               const f32x2 in2 = pack2(invn[2 * jp], invn[2 * jp + 1]);
-              const float k1 = jp < 2 ? c1a : c1b, k2 = jp < 2 ? c2a : c2b;
-              const f32x2 u2 = fma2(add2(pack2(S1[2 * jp], S1[2 * jp + 1]), pack2(k1, k1)), in2, ncm2);  // mean - c
-              const f32x2 e2 = fma2(add2(pack2(S2[2 * jp], S2[2 * jp + 1]), pack2(k2, k2)), in2, eps2);
+              const f32x2 u2 = fma2(add2(pack2(S1[2 * jp], S1[2 * jp + 1]), pack2(k1[jp], k1[jp])), in2, ncm2);  // mean - c
+              const f32x2 e2 = fma2(add2(pack2(S2[2 * jp], S2[2 * jp + 1]), pack2(k2[jp], k2[jp])), in2, eps2);
               float va, vb;
               unpack2(sub2(e2, mul2(u2, u2)), va, vb);
               const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(va, eps)), rsqrt_fast(fmaxf(vb, eps))), w2);
