@@ -159,6 +159,60 @@ def time_cpu(step, steps, warmup):
     return sum(ts) / len(ts)
 
 
+def reference_gpu_leg(L, D):
+    """Informative: the reference's own GPU path for the EMA on this workload's shape, through its
+    CUDA operators compiled unmodified by ``oracle/build_ref.py --cuda`` and the lines of its Python
+    flow restated here (base_moving_average.py:137-172; fused_ops/fftconv.py:13-27,45-61: its
+    shared-memory FFT kernel up to L = 8192, torch.fft beyond).  The TimestepNorm half is absent:
+    the reference's chunked CUDA kernel (L >= 256) does not launch on sm_100 ("too many resources
+    requested for launch").  Returns a dict for the JSON line, or None without a GPU / the build."""
+    import torch
+    if not torch.cuda.is_available():
+        return None
+    from oracle.build_ref import load_ref_cuda
+    mod = load_ref_cuda()
+    if mod is None:
+        return {"unavailable": "oracle/_ref/mega_ref_cuda.so not built"}
+    R = mod.ops
+    try:
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        bsz = 8
+        gen = torch.Generator().manual_seed(4321)
+        alpha, delta, beta, gamma, omega = [t.to(dev) for t in make_ema_params(gen, D, NDIM)]
+        x = torch.randn(bsz, D, L, device=dev, dtype=torch.bfloat16)
+        n = L if (L & (L - 1)) == 0 else (1 << L.bit_length())
+
+        def step():
+            with torch.no_grad():
+                p = torch.sigmoid(alpha)
+                q = torch.polar(1.0 - p * torch.sigmoid(delta), torch.zeros_like(p))
+                g = torch.complex(gamma * beta.squeeze(-1), torch.zeros_like(gamma)) * (1.0 / NDIM) ** 0.5
+                w, _, _ = R.ema_parameters_fwd(p, q.log(), g, None, L)
+                if 32 <= L <= 8192:
+                    y, _ = R.fftconv_fwd(x, torch.fft.rfft(w.float(), 2 * n))
+                else:
+                    x_f = torch.fft.rfft(x.float(), n=2 * n)
+                    k_f = torch.fft.rfft(w, n=2 * n, norm="forward")
+                    y = torch.fft.irfft(x_f * k_f, n=2 * n, norm="forward")[..., :L].to(x.dtype)
+                return y + x * omega.view(D, 1).to(x.dtype)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / 3
+        return {"value": bsz * L / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                "what": "EMA only (no TimestepNorm: the reference's kernel does not launch on sm_100 for L >= 256), "
+                        "B=%d L=%d D=%d bf16 on one GPU" % (bsz, L, D)}
+    except Exception as exc:  # a reference kernel that does not run here is reported, not fatal
+        return {"unavailable": str(exc).splitlines()[0][:200]}
+
+
 def run_reference(args, B, L, D, dtype_name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -183,6 +237,9 @@ def run_reference(args, B, L, D, dtype_name):
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    gpu = reference_gpu_leg(L, D)
+    if gpu is not None:
+        line["reference_gpu"] = gpu
     print(json.dumps(line), flush=True)
 
 

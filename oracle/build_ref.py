@@ -50,6 +50,63 @@ def build(reference_root=DEFAULT_REFERENCE, verbose=False):
     return so_path()
 
 
+CUDA_MOD_NAME = "mega_ref_cuda"
+
+
+def cuda_so_path():
+    return os.path.join(OUT_DIR, CUDA_MOD_NAME + ".so")
+
+
+def build_cuda(reference_root=DEFAULT_REFERENCE, verbose=False):
+    """Compile the reference's whole native extension (CPU + CUDA operators, the 16 sources its
+    setup.py lists for ``fairseq.mega2_extension``) for sm_100 into
+    ``oracle/_ref/mega_ref_cuda.so``: the reference's own GPU path, to compare against and to time
+    on the GPU box.  nvcc cross-compiles without a GPU; the reference's build system is not run."""
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    from torch.utils.cpp_extension import load
+
+    csrc = os.path.join(reference_root, "fairseq", "csrc")
+    names = ["blas.cc", "mega2_extension.cc"]
+    for op in ("attention_softmax", "attention", "ema_parameters", "ema_hidden", "fftconv", "sequence_norm",
+               "timestep_norm"):
+        names += ["ops/%s.cc" % op, "ops/%s_kernel.cu" % op]
+    srcs = [os.path.join(csrc, n) for n in names]
+    for s in srcs:
+        if not os.path.exists(s):
+            raise FileNotFoundError(s)
+    os.makedirs(OUT_DIR, exist_ok=True)
+    import tempfile
+    build_dir = os.path.join(tempfile.gettempdir(), "mega_ref_cuda_build")  # objects stay out of the tree
+    os.makedirs(build_dir, exist_ok=True)
+    load(name=CUDA_MOD_NAME, sources=srcs, extra_include_paths=[csrc], extra_cflags=["-O3", "-std=c++17"],
+         # at::Context::alertCuBLASConfigNotDeterministic() (a warning hook the reference calls before
+         # its cuBLAS GEMMs) no longer exists in the installed torch; the define maps the call onto a
+         # harmless getter so that the untouched sources still compile
+         extra_cuda_cflags=["-O3", "-std=c++17", "--expt-relaxed-constexpr", "--expt-extended-lambda",
+                            "-DalertCuBLASConfigNotDeterministic=deterministicAlgorithms"],
+         extra_ldflags=["-lcublas"], with_cuda=True, build_directory=build_dir, verbose=verbose,
+         is_python_module=False)  # its init symbol is the reference's PyInit_mega2_extension, see load_ref_cuda
+    import shutil
+    shutil.copy2(os.path.join(build_dir, CUDA_MOD_NAME + ".so"), cuda_so_path())
+    return cuda_so_path()
+
+
+def load_ref_cuda():
+    """Import the prebuilt CUDA build of the reference extension; None when it was never built."""
+    p = cuda_so_path()
+    if not os.path.exists(p):
+        return None
+    import torch  # noqa: F401
+    if CUDA_MOD_NAME in sys.modules:
+        return sys.modules[CUDA_MOD_NAME]
+    # the reference names its module "mega2_extension" in PYBIND11_MODULE (mega2_extension.cc:14)
+    spec = importlib.util.spec_from_file_location("mega2_extension", p)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules[CUDA_MOD_NAME] = mod
+    return mod
+
+
 def load_ref():
     """Import the prebuilt ``oracle/_ref`` module; None when it was never built."""
     p = so_path()
@@ -69,5 +126,8 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=DEFAULT_REFERENCE)
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--cuda", action="store_true", help="also build the reference's CUDA operators (minutes)")
     a = ap.parse_args()
     print(build(a.reference, a.verbose))
+    if a.cuda:
+        print(build_cuda(a.reference, a.verbose))
