@@ -49,6 +49,8 @@ SIGNATURES = {
     "mega_cema_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p, c_p, c_i,
                       c_p, c_p, c_p, c_u, c_i, c_p],
     "mega_cema_step": [c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_u, c_p],
+    "mega_tsn_cema_fwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                          c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
     "mega_set_option": [c_i, c_i],
     "mega_debug_device_error": [ctypes.POINTER(c_i), c_i],
 }

@@ -4,6 +4,7 @@
 // length cap.  Four lanes share a (batch, channel) row and split its poles; the per-step output is
 // a two-shuffle reduction.
 #include "common.cuh"
+#include "stream_cl.cuh"
 
 namespace mega {
 
@@ -254,6 +255,16 @@ extern "C" int mega_cema_fwd(const void* x, void* y, int dtype, int B, int D, in
   if (bidir && (h_in || h_out)) return MEGA_ERR_UNSUPPORTED;
   if (!bidir && trunc) return MEGA_ERR_UNSUPPORTED;
   if (x == y && (bidir || trunc || xsb != ysb || xsd != ysd || xsl != ysl)) return MEGA_ERR_STRIDE;
+  if (!bidir && !trunc && x != y && N <= 16) {
+    // channel-contiguous activations: the streamed TMA kernel (one thread per channel, poles in registers)
+    StreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
+    sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+    sa.cplx = 1;
+    if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, true, sa, (cudaStream_t)stream))
+      return check_launch("cema_fwd(stream)");
+  }
   CemaArgs a{};
   a.x = x; a.y = y; a.B = B; a.D = D; a.L = L; a.N = N;
   a.xsb = xsb; a.xsd = xsd; a.xsl = xsl; a.ysb = ysb; a.ysd = ysd; a.ysl = ysl;
@@ -288,4 +299,40 @@ extern "C" int mega_cema_step(const void* x, void* y, int dtype, int B, int D, c
   MEGA_DISPATCH_DTYPE(dtype, launch(cema_step_kernel<T>, grid, 128, 0, stream, (const T*)x, (T*)y, B, D, N, p, q,
                                     gamma_hat, omega, h_in, h_out, (flags & MEGA_EMA_SILU) ? 1 : 0));
   return check_launch("cema_step");
+}
+
+extern "C" int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D, int64_t xsb,
+                                 int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                                 const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                                 const float* gamma, const float* beta, double eps, int64_t* count_out,
+                                 float* mean_out, float* var_out, const float* p, const float* q,
+                                 const float* gamma_hat, const float* omega, int N, const uint8_t* pad_mask,
+                                 const float* h_in, float* h_out, unsigned flags, mega_stream_t stream) {
+  if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
+      !var_out || !p || !q || !gamma_hat || !omega)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (flags & MEGA_EMA_BIDIRECTIONAL) return MEGA_ERR_UNSUPPORTED;
+  if (x == y) return MEGA_ERR_UNSUPPORTED;
+  if (N <= 16) {
+    StreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.prev_count = (const long long*)prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var;
+    sa.gamma = gamma; sa.beta = beta; sa.eps = (float)eps;
+    sa.count_out = (long long*)count_out; sa.mean_out = mean_out; sa.var_out = var_out;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
+    sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+    sa.cplx = 1;
+    if (stream_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, true, sa, (cudaStream_t)stream))
+      return check_launch("tsn_cema_fwd(stream)");
+  }
+  // outside the streamed kernel's envelope: the two operators in turn (the EMA runs in place)
+  void* mid = xn_out ? xn_out : y;
+  int rc = mega_timestep_norm_fwd(x, mid, dtype, B, L, D, xsb, xsl, xsd, ysb, ysl, ysd, prev_count, prev_mean,
+                                  prev_var, gamma, beta, pad_mask, D, eps, count_out, mean_out, var_out, stream);
+  if (rc != MEGA_OK) return rc;
+  return mega_cema_fwd(mid, y, dtype, B, D, L, ysb, ysd, ysl, ysb, ysd, ysl, p, q, gamma_hat, omega, N, pad_mask,
+                       h_in, h_out, flags, 0, stream);
 }

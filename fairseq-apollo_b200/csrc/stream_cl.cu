@@ -74,7 +74,7 @@ struct StreamCfg {
   static constexpr int smem_bytes(bool has_xn) { return kHead + kTile * (kS + 2 + (has_xn ? 2 : 0)) + 128; }
 };
 
-template <typename T, bool kNorm, bool kEma, bool kState>
+template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx>
 __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ CUtensorMap tmx,
                                                        const __grid_constant__ CUtensorMap tmy,
                                                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
@@ -116,8 +116,50 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
 
   // per-channel constants and running state
   f32x2 q2[kNP / 2], c2[kNP / 2], s2[kNP / 2], p2[kState ? kNP / 2 : 1];
+  // complex poles: q2 / c2 / s2 hold the real parts, these the imaginary parts (nq2i = -Im q,
+  // nc2i = -Im gamma: y = Re(gamma h) = gr hr - gi hi)
+  f32x2 nq2i[kCplx ? kNP / 2 : 1], q2i[kCplx ? kNP / 2 : 1], nc2i[kCplx ? kNP / 2 : 1], s2i[kCplx ? kNP / 2 : 1];
   float om = 0.f;
-  if (kEma) {
+  if (kEma && kCplx) {
+    om = __ldg(a.omega + dc);
+#pragma unroll
+    for (int j = 0; j < kNP / 2; ++j) {
+      float pv[2], qr[2], qi[2], gr[2], gi[2], hr[2], hi[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int n = 2 * j + k;
+        pv[k] = qr[k] = qi[k] = gr[k] = gi[k] = hr[k] = hi[k] = 0.f;
+        if (n < a.N) {
+          const size_t c = (size_t)dc * a.N + n;
+          pv[k] = __ldg(a.p + c);
+          qr[k] = __ldg(a.q + 2 * c);
+          qi[k] = __ldg(a.q + 2 * c + 1);
+          gr[k] = __ldg(a.g + 2 * c);
+          gi[k] = __ldg(a.g + 2 * c + 1);
+          if (kState && a.h_in) {
+            const size_t sidx = ((size_t)b * a.D + dc) * a.N + n;
+            hr[k] = __ldg(a.h_in + 2 * sidx);
+            hi[k] = __ldg(a.h_in + 2 * sidx + 1);
+          }
+        }
+      }
+      q2[j] = pack2(qr[0], qr[1]);
+      q2i[j] = pack2(qi[0], qi[1]);
+      nq2i[j] = pack2(-qi[0], -qi[1]);
+      if (kState) {  // true states, input gain applied per step
+        c2[j] = pack2(gr[0], gr[1]);
+        nc2i[j] = pack2(-gi[0], -gi[1]);
+        p2[j] = pack2(pv[0], pv[1]);
+        s2[j] = pack2(hr[0], hr[1]);
+        s2i[j] = pack2(hi[0], hi[1]);
+      } else {       // states scaled by 1 / p: the gain moves into the output weights
+        c2[j] = pack2(pv[0] * gr[0], pv[1] * gr[1]);
+        nc2i[j] = pack2(-pv[0] * gi[0], -pv[1] * gi[1]);
+        s2[j] = pack2(0.f, 0.f);
+        s2i[j] = pack2(0.f, 0.f);
+      }
+    }
+  } else if (kEma) {
     om = __ldg(a.omega + dc);
 #pragma unroll
     for (int j = 0; j < kNP / 2; ++j) {
@@ -213,6 +255,19 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
         if (kEma) {
           const f32x2 x2 = pack2(xn, xn);
           f32x2 acc0 = pack2(0.f, 0.f), acc1 = pack2(0.f, 0.f);
+          if (kCplx) {
+#pragma unroll
+            for (int j = 0; j < kNP / 2; ++j) {
+              // h' = q h + p x (complex); y += Re(gamma h')
+              const f32x2 in2 = kState ? mul2(p2[j], x2) : x2;
+              const f32x2 nr = fma2(q2[j], s2[j], fma2(nq2i[j], s2i[j], in2));
+              const f32x2 ni = fma2(q2i[j], s2[j], mul2(q2[j], s2i[j]));
+              s2[j] = nr;
+              s2i[j] = ni;
+              acc0 = fma2(c2[j], nr, acc0);
+              acc1 = fma2(nc2i[j], ni, acc1);
+            }
+          } else {
 #pragma unroll
           for (int j = 0; j < kNP / 2; j += 2) {
             if (kState) {
@@ -224,6 +279,7 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
             }
             acc0 = fma2(c2[j], s2[j], acc0);
             acc1 = fma2(c2[j + 1], s2[j + 1], acc1);
+          }
           }
           float lo, hi;
           unpack2(add2(acc0, acc1), lo, hi);
@@ -254,7 +310,23 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
       a.mean_out[(size_t)b * a.D + d] = mean;
       a.var_out[(size_t)b * a.D + d] = var;
     }
-    if (kEma && kState && a.h_out) {
+    if (kEma && kState && kCplx && a.h_out) {
+#pragma unroll
+      for (int j = 0; j < kNP / 2; ++j) {
+        float rl, rh, il, ih;
+        unpack2(s2[j], rl, rh);
+        unpack2(s2i[j], il, ih);
+        const size_t sidx = ((size_t)b * a.D + d) * a.N + 2 * j;
+        if (2 * j < a.N) {
+          a.h_out[2 * sidx] = rl;
+          a.h_out[2 * sidx + 1] = il;
+        }
+        if (2 * j + 1 < a.N) {
+          a.h_out[2 * sidx + 2] = rh;
+          a.h_out[2 * sidx + 3] = ih;
+        }
+      }
+    } else if (kEma && kState && a.h_out) {
 #pragma unroll
       for (int j = 0; j < kNP / 2; ++j) {
         float lo, hi;
@@ -270,10 +342,10 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <typename T, bool kNorm, bool kEma, bool kState>
+template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx = false>
 static bool launch_one(const CUtensorMap& tx, const CUtensorMap& ty, const CUtensorMap& tn, const StreamArgs& a,
                        cudaStream_t s) {
-  auto kern = stream_cl_kernel<T, kNorm, kEma, kState>;
+  auto kern = stream_cl_kernel<T, kNorm, kEma, kState, kCplx>;
   const int smem = StreamCfg<T>::smem_bytes(a.has_xn != 0);
   static std::once_flag once;
   static bool attr_ok = true;
@@ -315,7 +387,12 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
   switch (dtype) {
 #define MEGA_STREAM_CASE(DT, TY)                                                        \
   case DT:                                                                              \
-    if (norm && ema) ok = state ? launch_one<TY, true, true, true>(tx, ty, tn, a, s)    \
+    if (ema && a.cplx) {                                                                \
+      if (norm) ok = state ? launch_one<TY, true, true, true, true>(tx, ty, tn, a, s)   \
+                           : launch_one<TY, true, true, false, true>(tx, ty, tn, a, s); \
+      else ok = state ? launch_one<TY, false, true, true, true>(tx, ty, tn, a, s)       \
+                      : launch_one<TY, false, true, false, true>(tx, ty, tn, a, s);     \
+    } else if (norm && ema) ok = state ? launch_one<TY, true, true, true>(tx, ty, tn, a, s)    \
                                 : launch_one<TY, true, true, false>(tx, ty, tn, a, s);  \
     else if (ema) ok = state ? launch_one<TY, false, true, true>(tx, ty, tn, a, s)      \
                              : launch_one<TY, false, true, false>(tx, ty, tn, a, s);    \

@@ -17,6 +17,7 @@ struct StreamArgs {
   const unsigned char* mask;
   int silu;
   int has_xn;
+  int cplx;  // complex poles: q, g are interleaved (re, im) (K, N, 2); states (B, D, N, 2)
 };
 
 // Tries the streamed TMA path for TimestepNorm (norm), causal EMA (ema) or both fused.  Returns

@@ -27,12 +27,13 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     assert activation in (None, 'silu')
     per_feature = norm.num_groups is None or norm.num_groups == norm.num_features
     train = needs_grad(x, *norm.parameters(), *move.parameters())
-    if train or not per_feature or move.bidirectional or move.complex:
-        # training, grouped statistics, bidirectional or complex poles: the two modules in turn
+    if train or not per_feature or move.bidirectional:
+        # training, grouped statistics or a bidirectional layer: the two modules in turn
         xn = norm(x, padding_mask, incremental_state)
         mx = move(xn.transpose(1, 2), padding_mask, incremental_state, activation).transpose(1, 2)
         return (mx, xn) if return_normed else mx
-    if (incremental_state is not None and x.size(1) == 1 and padding_mask is None and x.is_contiguous()):
+    if (incremental_state is not None and x.size(1) == 1 and padding_mask is None and x.is_contiguous()
+            and not move.complex):
         return _decode_step(norm, move, x, incremental_state, activation, return_normed)
     prev_count, prev_mean, prev_var, nstate = norm.initial_statistics(x.size(0), incremental_state)
     p, q, g = move.coeffs()
@@ -44,7 +45,7 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     res = ops.tsn_ema_forward(x, prev_count, prev_mean, prev_var, norm.weight.detach().float() + 1.0, norm.bias,
                               norm.eps, p.squeeze(-1), q.squeeze(-1), g, move.omega, padding_mask, h_in,
                               want_state=incremental_state is not None, silu=activation == 'silu',
-                              want_normed=return_normed)
+                              want_normed=return_normed, complex_poles=move.complex)
     norm.store_statistics(incremental_state, nstate, res["count"], res["mean"], res["var"])
     if incremental_state is not None:
         estate['prev_state'] = res["h"]

@@ -215,14 +215,19 @@ def sequence_norm_fwd(x, gamma, beta, padding_mask=None, eps=1e-5, length_last=T
 
 
 def tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma, beta, eps, p, q, g, omega,
-                    padding_mask=None, h_in=None, want_state=False, silu=False, want_normed=False):
+                    padding_mask=None, h_in=None, want_state=False, silu=False, want_normed=False,
+                    complex_poles=False):
     """Fused per-feature TimestepNorm -> causal EMA on x (B, L, D).
-    Returns dict(y, count, mean, var[, h][, xn]); y and xn are (B, L, D) like x."""
+    Returns dict(y, count, mean, var[, h][, xn]); y and xn are (B, L, D) like x.
+    ``complex_poles``: q, g (and the states) are complex64, the layer is MultiHeadComplexEMA's."""
     _cuda(x, prev_count, prev_mean, prev_var, gamma, beta, p, q, g, omega, padding_mask, h_in)
     bsz, length, dim = x.shape
     prev_count = prev_count.detach().to(torch.int64).contiguous()
     prev_mean, prev_var, gamma, beta = _f32c(prev_mean), _f32c(prev_var), _f32c(gamma), _f32c(beta)
-    p, q, g, omega = _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
+    if complex_poles:
+        p, q, g, omega, h_in = _f32c(p), _c64(q), _c64(g), _f32c(omega).reshape(-1), _c64(h_in)
+    else:
+        p, q, g, omega = _f32c(p), _f32c(q), _f32c(g), _f32c(omega)
     n = p.shape[1]
     mask = _mask_u8(padding_mask, bsz, length)
     y = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \
@@ -231,18 +236,23 @@ def tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma, beta, eps, p, q, 
     count = torch.empty(bsz, device=x.device, dtype=torch.int64)
     mean = torch.empty(bsz, dim, device=x.device, dtype=torch.float32)
     var = torch.empty_like(mean)
-    h_in = _f32c(h_in)
-    h_out = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32) if want_state else None
+    if complex_poles:
+        h_out = torch.empty(bsz, dim, n, 2, device=x.device, dtype=torch.float32) if want_state else None
+        entry, what = _lib.lib().mega_tsn_cema_fwd, "tsn_cema_fwd"
+    else:
+        h_in = _f32c(h_in)
+        h_out = torch.empty(bsz, dim, n, device=x.device, dtype=torch.float32) if want_state else None
+        entry, what = _lib.lib().mega_tsn_ema_fwd, "tsn_ema_fwd"
     with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().mega_tsn_ema_fwd(
+        _lib.check(entry(
             x.data_ptr(), y.data_ptr(), _ptr(xn), _dt(x), bsz, length, dim, *x.stride(), *y.stride(),
             prev_count.data_ptr(), prev_mean.data_ptr(), prev_var.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
             float(eps), count.data_ptr(), mean.data_ptr(), var.data_ptr(),
             p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), _ptr(h_in), _ptr(h_out),
-            EMA_SILU if silu else 0, _stream()), "tsn_ema_fwd")
+            EMA_SILU if silu else 0, _stream()), what)
     res = {"y": y, "count": count, "mean": mean, "var": var}
     if want_state:
-        res["h"] = h_out
+        res["h"] = torch.view_as_complex(h_out) if complex_poles else h_out
     if want_normed:
         res["xn"] = xn
     return res

@@ -353,6 +353,22 @@ MEGA_API int mega_cema_step(const void* x, void* y, int dtype, int B, int D, con
                    const float* gamma_hat, const float* omega, int N, const float* h_in, float* h_out,
                    unsigned flags, mega_stream_t stream);
 
+/*
+ * mega_tsn_cema_fwd: mega_tsn_ema_fwd with the complex layer's coefficients (q, gamma_hat
+ * interleaved (K, N, 2); h_in / h_out (B, D, N, 2)): per-feature TimestepNorm fused with the causal
+ * complex EMA on x (B, L, D), one pass over x when the channels are contiguous.  x and y must not
+ * alias.
+ * Replaces: self.norm -> transpose -> self.move [-> move_act] of MovingAverageGatedAttention.forward
+ * (moving_average_gated_attention.py:306-316) with moving_layer='cema'.
+ */
+MEGA_API int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D, int64_t xsb,
+                      int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
+                      const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                      const float* gamma, const float* beta, double eps, int64_t* count_out, float* mean_out,
+                      float* var_out, const float* p, const float* q, const float* gamma_hat,
+                      const float* omega, int N, const uint8_t* pad_mask, const float* h_in, float* h_out,
+                      unsigned flags, mega_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

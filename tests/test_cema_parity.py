@@ -110,3 +110,36 @@ def test_chunked_equals_full_with_masks():
         for i in range(0, 96, 32):
             parts.append(m(x[..., i:i + 32], mask[:, i:i + 32], st))
     assert rel_l2(torch.cat(parts, -1), full) < 1e-5
+
+
+@pytest.mark.parametrize("bsz,length,dim,ndim", [(2, 70, 24, 16), (3, 257, 72, 3), (2, 64, 8, 16), (2, 40, 20, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_timestep_norm_complex_ema(bsz, length, dim, ndim, dtype):
+    """TimestepNorm -> complex EMA (+ SiLU) through the fused helper: one streamed kernel when
+    ndim <= 16, the two operators in turn otherwise; full pass and chunked with both states."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(length + dim)
+    torch.manual_seed(length + dim)
+    move = M.MultiHeadComplexEMA(dim, ndim=ndim).cuda().eval()
+    norm = M.TimestepNorm(dim, prior_count=2).cuda().eval()
+    with torch.no_grad():
+        move.gamma[:, :, 1].normal_(0, 1)
+        norm.weight.normal_(0, 0.1)
+        norm.bias.normal_(0, 0.1)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.2).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.3)
+    prm = [getattr(move, k).detach().cpu() for k in ("alpha", "delta", "theta", "gamma", "omega")]
+    xn_ref = O.timestep_norm(x.float(), torch.full((bsz,), 2, dtype=torch.int64), torch.zeros(bsz, dim),
+                             torch.ones(bsz, dim), norm.weight.detach().cpu() + 1.0, norm.bias.detach().cpu(), mask)[0]
+    y_ref = O.cema_forward_recurrence(xn_ref.transpose(1, 2), *prm, mask, silu=True).transpose(1, 2)
+    with torch.no_grad():
+        y, xn = M.timestep_norm_ema(norm, move, x.cuda(), mask.cuda(), None, 'silu', return_normed=True)
+        assert rel_l2(y.float(), y_ref) < TOL[dtype]
+        assert rel_l2(xn.float(), xn_ref) < TOL[dtype]
+        assert (xn.cpu()[mask] == 0).all()
+        st, parts = {}, []
+        step = 32
+        for i in range(0, length, step):
+            parts.append(M.timestep_norm_ema(norm, move, x[:, i:i + step].cuda(), mask[:, i:i + step].cuda(), st, 'silu'))
+        assert rel_l2(torch.cat(parts, 1).float(), y_ref) < TOL[dtype]
+        assert move._get_input_buffer(st)["prev_state"].dtype == torch.complex64
