@@ -36,7 +36,7 @@ WORKLOADS = {
     "tiny": (4, 2048, 256, "bf16"),
 }
 # side workloads (BASELINE configs 0, 2 and the decode half of config 4): own JSON line, N=1 only
-AUX_WORKLOADS = ("c0", "c2", "decode")
+AUX_WORKLOADS = ("c0", "c2", "decode", "cema", "train")
 NDIM = 16
 FALLBACK_HBM_GBS = 6650.0
 
@@ -481,8 +481,35 @@ def run_aux(args):
 
     steps, warm = max(args.steps, 5), max(args.warmup, 3)
     l0 = M.launch_count()
+    if args.workload == "train":
+        # forward + backward of TimestepNorm -> EMA on the config-1 shape through the modules' autograd
+        # Functions; compulsory traffic: x read twice, y written, dy read, dx written = 5 passes
+        L, B, D = 4096, 16, 1024
+        ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).train()
+        norm = M.TimestepNorm(D, prior_count=2).to(dev).train()
+        x = torch.randn(B, L, D, generator=gen).to(dev).bfloat16().requires_grad_(True)
+        dy = torch.randn(B, L, D, generator=gen).to(dev).bfloat16()
+
+        def train_step():
+            for prm in list(ema.parameters()) + list(norm.parameters()) + [x]:
+                prm.grad = None
+            M.timestep_norm_ema(norm, ema, x).backward(dy)
+        ms = timed(train_step, steps, warm)
+        tokens, bytes_alg, name, dt = B * L, 5.0 * B * L * D * 2, "train: TimestepNorm+MultiHeadEMA fwd+bwd bf16 L=4096 B=16 D=1024", "bf16"
     with torch.no_grad():
-        if args.workload == "c0":
+        if args.workload == "train":
+            pass
+        elif args.workload == "cema":
+            # the reference's default moving layer on the config-4 shape at B=16: fused TimestepNorm -> complex EMA
+            L, B, D = 32768, 16, 2048
+            x = torch.empty(B, L, D, dtype=torch.bfloat16, device=dev)
+            for b in range(B):
+                x[b] = torch.randn(L, D, device=dev, dtype=torch.bfloat16)
+            ema = M.MultiHeadComplexEMA(D, ndim=NDIM).to(dev).eval()
+            norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+            ms = timed(lambda: M.timestep_norm_ema(norm, ema, x), steps, warm)
+            tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 2, "cema: TimestepNorm+MultiHeadComplexEMA causal fwd bf16 L=32768 B=16 D=2048", "bf16"
+        elif args.workload == "c0":
             L, B, D = 1024, 8, 512
             x = torch.randn(L, B, D, generator=gen).to(dev)           # time-major, viewed as (B, D, L)
             ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()

@@ -25,9 +25,11 @@ struct EmaBwdArgs {
   int bidir, shift;
 };
 
-template <typename T, int NP>
+// kMask: whether a padding mask is given (a run-time pointer test inside the unrolled load
+// batches would serialise their loads).
+template <typename T, int NP, bool kMask>
 __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
-  constexpr int U = 4;
+  constexpr int U = 16;  // loads in flight per thread: few rows are resident, so latency is hidden per thread
   const int sub = threadIdx.x & 3;
   const long long row = (long long)blockIdx.x * 32 + (threadIdx.x >> 2);
   const bool live = row < (long long)a.B * a.D;  // dead rows keep running for the shuffles
@@ -37,7 +39,7 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
   const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
   const T* gp = reinterpret_cast<const T*>(a.dy) + b * a.gsb + d * a.gsd;
   T* dxp = reinterpret_cast<T*>(a.dx) + b * a.dsb + d * a.dsd;
-  const unsigned char* mp = a.mask ? a.mask + (size_t)b * L : nullptr;
+  const unsigned char* mp = kMask ? a.mask + (size_t)b * L : nullptr;
   const float om = __ldg(a.omega + d);
   float aw = 0.f;
 
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
           const float xt = Elem<T>::ld(xp + t * a.xsl);
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
           if (half == 0) aw = fmaf(gv[j], xt, aw);
-          xv[j] = (mp && mp[t]) ? 0.f : xt;
+          xv[j] = (kMask && __ldg(mp + t) != 0) ? 0.f : xt;
         }
       }
 #pragma unroll
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
         if (u >= 0 && live) {
           const int t = rev ? L - 1 - u : u;
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
-          mk[j] = mp && mp[t];
+          mk[j] = kMask && __ldg(mp + t) != 0;
           if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(dxp + t * a.dsl);  // plain load: written above
         }
       }
@@ -194,9 +196,9 @@ struct TsnBwdArgs {
   float *dgamma, *dbeta;          // (D) accumulators
 };
 
-template <typename T>
+template <typename T, bool kMask>
 __global__ void __launch_bounds__(128) tsn_bwd_plain_kernel(TsnBwdArgs a) {
-  constexpr int U = 4;
+  constexpr int U = 16;  // loads in flight per thread
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)a.B * a.D) return;
   const int d = (int)(gid % a.D);
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(128) tsn_bwd_plain_kernel(TsnBwdArgs a) {
   T* dxp = reinterpret_cast<T*>(a.dx) + b * a.dsb + d * a.dsd;
   const float* cm = a.cummean + (size_t)b * a.L * a.D + d;
   const float* cr = a.cumrstd + (size_t)b * a.L * a.D + d;
-  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  const unsigned char* mp = kMask ? a.mask + (size_t)b * a.L : nullptr;
   const float w = __ldg(a.gamma + d);
   const float pm = a.prev_mean[gid];
   long long cnt = a.count[b];
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(128) tsn_bwd_plain_kernel(TsnBwdArgs a) {
       xv[j] = gv[j] = uv[j] = pv[j] = rv[j] = 0.f;
       mk[j] = true;
       if (t >= 0) {
-        mk[j] = mp && mp[t];
+        mk[j] = kMask && __ldg(mp + t) != 0;
         xv[j] = Elem<T>::ld(xp + t * a.xsl);
         gv[j] = Elem<T>::ld(gp + t * a.gsl);
         uv[j] = __ldg(cm + (size_t)t * a.D);
@@ -453,12 +455,16 @@ extern "C" int mega_ema_bwd(const void* dy, const void* x, void* dx, int dtype, 
   a.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
   const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
   const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
+#define MEGA_EMA_BWD(NPV)                                                         \
+  if (pad_mask) launch(ema_bwd_kernel<T, NPV, true>, grid, 128, 0, stream, a);     \
+  else launch(ema_bwd_kernel<T, NPV, false>, grid, 128, 0, stream, a)
   MEGA_DISPATCH_DTYPE(dtype, {
-    if (np == 1) launch(ema_bwd_kernel<T, 1>, grid, 128, 0, stream, a);
-    else if (np == 2) launch(ema_bwd_kernel<T, 2>, grid, 128, 0, stream, a);
-    else if (np == 4) launch(ema_bwd_kernel<T, 4>, grid, 128, 0, stream, a);
-    else launch(ema_bwd_kernel<T, 8>, grid, 128, 0, stream, a);
+    if (np == 1) { MEGA_EMA_BWD(1); }
+    else if (np == 2) { MEGA_EMA_BWD(2); }
+    else if (np == 4) { MEGA_EMA_BWD(4); }
+    else { MEGA_EMA_BWD(8); }
   });
+#undef MEGA_EMA_BWD
   return check_launch("ema_bwd");
 }
 
@@ -507,7 +513,10 @@ extern "C" int mega_timestep_norm_bwd(const void* dy, const void* x, void* dx, i
   a.dprev_mean = dprev_mean; a.dprev_var = dprev_var; a.dgamma = dgamma; a.dbeta = dbeta;
   if (G == D) {
     const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
-    MEGA_DISPATCH_DTYPE(dtype, launch(tsn_bwd_plain_kernel<T>, grid, 128, 0, stream, a));
+    MEGA_DISPATCH_DTYPE(dtype, {
+      if (pad_mask) launch(tsn_bwd_plain_kernel<T, true>, grid, 128, 0, stream, a);
+      else launch(tsn_bwd_plain_kernel<T, false>, grid, 128, 0, stream, a);
+    });
   } else {
     const unsigned grid = (unsigned)(((long long)B * G * 32 + 127) / 128);
     MEGA_DISPATCH_DTYPE(dtype, launch(tsn_bwd_group_kernel<T>, grid, 128, 0, stream, a));

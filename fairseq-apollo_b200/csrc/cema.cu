@@ -89,7 +89,7 @@ __device__ __forceinline__ void cpow(float qr, float qi, int k, float& outr, flo
   outi = ri;
 }
 
-template <typename T, int NP, bool kTrunc>
+template <typename T, int NP, bool kTrunc, bool kMask>
 __global__ void __launch_bounds__(128) cema_scan_kernel(CemaArgs a) {
   constexpr int U = 4;
   const int sub = threadIdx.x & 3;
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(128) cema_scan_kernel(CemaArgs a) {
   const int L = a.L;
   const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
   T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
-  const unsigned char* mp = a.mask ? a.mask + (size_t)b * L : nullptr;
+  const unsigned char* mp = kMask ? a.mask + (size_t)b * L : nullptr;  // compile-time: see ema_scan_rows_kernel
   const float om = __ldg(a.omega + d);
   const size_t srow = ((size_t)b * a.D + d) * a.N;
 
@@ -137,10 +137,10 @@ __global__ void __launch_bounds__(128) cema_scan_kernel(CemaArgs a) {
         if (u < L && live) {
           const int t = rev ? L - 1 - u : u;
           xv[j] = Elem<T>::ld(xp + t * a.xsl);
-          xm[j] = (mp && mp[t]) ? 0.f : xv[j];
+          xm[j] = (kMask && __ldg(mp + t) != 0) ? 0.f : xv[j];
           if (kTrunc) {
             const int td = rev ? t + a.ksize : t - a.ksize;
-            if (td >= 0 && td < L && !(mp && mp[td])) xd[j] = Elem<T>::ld(xp + td * a.xsl);
+            if (td >= 0 && td < L && !(kMask && __ldg(mp + td) != 0)) xd[j] = Elem<T>::ld(xp + td * a.xsl);
           }
           if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(yp + t * a.ysl);  // written by the first half
         }
@@ -276,8 +276,10 @@ extern "C" int mega_cema_fwd(const void* x, void* y, int dtype, int B, int D, in
   const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
   const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
 #define MEGA_CEMA_LAUNCH(NPV)                                                                   \
-  if (trunc) launch(cema_scan_kernel<T, NPV, true>, grid, 128, 0, stream, a);                   \
-  else launch(cema_scan_kernel<T, NPV, false>, grid, 128, 0, stream, a)
+  if (trunc && pad_mask) launch(cema_scan_kernel<T, NPV, true, true>, grid, 128, 0, stream, a);   \
+  else if (trunc) launch(cema_scan_kernel<T, NPV, true, false>, grid, 128, 0, stream, a);         \
+  else if (pad_mask) launch(cema_scan_kernel<T, NPV, false, true>, grid, 128, 0, stream, a);      \
+  else launch(cema_scan_kernel<T, NPV, false, false>, grid, 128, 0, stream, a)
   MEGA_DISPATCH_DTYPE(dtype, {
     if (np == 1) { MEGA_CEMA_LAUNCH(1); }
     else if (np == 2) { MEGA_CEMA_LAUNCH(2); }

@@ -30,9 +30,17 @@ static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 template <typename T>
 struct Elem;
 
+// `ldv`: the same read-only load as `ld`, issued through a volatile asm statement so that the
+// compiler keeps a batch of independent loads together at the top of an unrolled block instead
+// of sinking each one to its use (kernels with few resident warps hide latency per thread).
 template <>
 struct Elem<float> {
   static __device__ __forceinline__ float ld(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ float ldv(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+  }
   static __device__ __forceinline__ float ld_shared(const float* p) { return *p; }
   static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
 };
@@ -40,6 +48,11 @@ template <>
 struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ float ld(const __nv_bfloat16* p) {
     return __bfloat162float(__ldg(p));
+  }
+  static __device__ __forceinline__ float ldv(const __nv_bfloat16* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __uint_as_float((unsigned)v << 16);
   }
   static __device__ __forceinline__ float ld_shared(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) {
@@ -49,10 +62,26 @@ struct Elem<__nv_bfloat16> {
 template <>
 struct Elem<__half> {
   static __device__ __forceinline__ float ld(const __half* p) { return __half2float(__ldg(p)); }
+  static __device__ __forceinline__ float ldv(const __half* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __half2float(__ushort_as_half(v));
+  }
   static __device__ __forceinline__ float ld_shared(const __half* p) { return __half2float(*p); }
   static __device__ __forceinline__ void st(__half* p, float v) { *p = __float2half_rn(v); }
 };
 
+// MUFU approximations (about 1 ulp): no slow path, no subroutine call in a serial loop
+__device__ __forceinline__ float rcp_approx(float v) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float rsqrt_approx(float v) {
+  float r;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
 __device__ __forceinline__ float siluf_(float v) { return v / (1.0f + __expf(-v)); }
 // silu(v) = v * sigmoid(v) = h + h * tanh(h), h = v / 2: one MUFU op (tanh.approx, relative error

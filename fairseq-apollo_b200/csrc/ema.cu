@@ -4,6 +4,8 @@
 // The convolution y = k * x with k[l] = sum_n p_n gamma_n q_n^l is evaluated as the
 // order-N diagonal recurrence h_t = q h_{t-1} + p x_t, y_t = sum_n gamma_n h_{n,t}:
 // O(L) work per row, no length cap, one pass over x.
+#include <type_traits>
+
 #include "common.cuh"
 #include "stream_cl.cuh"
 #include "rowres.cuh"
@@ -162,6 +164,10 @@ __global__ void __launch_bounds__(128) ema_scan_rows_kernel(EmaArgs a) {
   const bool fwd = a.dir > 0;
   const bool pre_output = (!fwd) && a.shift;  // anti-causal with lag-1 start: emit before update
   constexpr int U = 8;
+  // The optional mask and the accumulate pass are compile-time inside the loop: run-time tests of
+  // them between the loads of a batch serialise those loads.
+  auto scan = [&](auto mask_tag, auto acc_tag) {
+  constexpr bool kMask = decltype(mask_tag)::value, kAcc = decltype(acc_tag)::value;
   for (int t0 = 0; t0 < L; t0 += U) {
     float xv[U], xd[U], yo[U];
     bool mk[U];
@@ -172,11 +178,11 @@ __global__ void __launch_bounds__(128) ema_scan_rows_kernel(EmaArgs a) {
       xv[u] = 0.f; xd[u] = 0.f; yo[u] = 0.f; mk[u] = true;
       if (t < L) {
         xv[u] = Elem<T>::ld(xp + tt * a.xsl);
-        mk[u] = mp != nullptr && mp[tt] != 0;
-        if (a.accumulate) yo[u] = Elem<T>::ld(yp + tt * a.ysl);
+        mk[u] = kMask ? __ldg(mp + tt) != 0 : false;
+        if (kAcc) yo[u] = Elem<T>::ld_shared(yp + tt * a.ysl);  // written by the causal pass: plain load
         if (MODE == MODE_TRUNC) {
           const int td = fwd ? tt - a.ksize : tt + a.ksize;
-          if (td >= 0 && td < L && !(mp != nullptr && mp[td] != 0)) xd[u] = Elem<T>::ld(xp + td * a.xsl);
+          if (td >= 0 && td < L && !(kMask && __ldg(mp + td) != 0)) xd[u] = Elem<T>::ld(xp + td * a.xsl);
         }
       }
     }
@@ -194,11 +200,19 @@ __global__ void __launch_bounds__(128) ema_scan_rows_kernel(EmaArgs a) {
           st.update(xm, xd[u]);
           conv = st.output();
         }
-        float v = a.accumulate ? (yo[u] + conv) : fmaf(om, xv[u], conv);
+        float v = kAcc ? (yo[u] + conv) : fmaf(om, xv[u], conv);
         if (a.silu) v = siluf_(v);
         Elem<T>::st(yp + tt * a.ysl, v);
       }
     }
+  }
+  };
+  using std::true_type;
+  using std::false_type;
+  if (mp) {
+    if (a.accumulate) scan(true_type{}, true_type{}); else scan(true_type{}, false_type{});
+  } else {
+    if (a.accumulate) scan(false_type{}, true_type{}); else scan(false_type{}, false_type{});
   }
   st.export_state(a, b, d);
 }

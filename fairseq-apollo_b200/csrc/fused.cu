@@ -3,6 +3,8 @@
 // Generic variant: one thread per (batch, channel), sequential over time, so every
 // per-channel quantity (Welford state, pole states) lives in registers.  Works for any
 // strides; coalesced when the channel stride is 1.
+#include <type_traits>
+
 #include "common.cuh"
 #include "stream_cl.cuh"
 
@@ -53,10 +55,16 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
   T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
   T* np_ = a.xn ? reinterpret_cast<T*>(a.xn) + b * a.ysb + d * a.ysd : nullptr;
   const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
-  long long cnt = a.prev_count[b];
+  const long long cnt0 = a.prev_count[b];
+  const float cnt0f = (float)cnt0;  // 32-bit step counter on top: no 64-bit conversions in the loop
+  int seen = 0;
   float mean = a.prev_mean[gid], var = a.prev_var[gid];
   const float w = __ldg(a.gamma + d), bb = __ldg(a.beta + d), om = __ldg(a.omega + d);
   constexpr int U = 8;
+  // mask presence is compile-time inside the loop (a run-time pointer test between the loads of
+  // a batch serialises them)
+  auto scan = [&](auto mask_tag) {
+  constexpr bool kMask = decltype(mask_tag)::value;
   for (int t0 = 0; t0 < a.L; t0 += U) {
     float xv[U];
     bool mk[U];
@@ -66,7 +74,7 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
       xv[u] = 0.f; mk[u] = true;
       if (t < a.L) {
         xv[u] = Elem<T>::ld(xp + t * a.xsl);
-        mk[u] = mp != nullptr && mp[t] != 0;
+        mk[u] = kMask ? __ldg(mp + t) != 0 : false;
       }
     }
 #pragma unroll
@@ -74,14 +82,14 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
       const int t = t0 + u;
       if (t < a.L) {
         float m1, m2;
-        const float coef = __frcp_rn((float)(cnt + 1));
+        const float coef = rcp_approx(cnt0f + (float)(seen + 1));
         const float d1 = xv[u] - mean;
         m1 = fmaf(coef, d1, mean);
         const float d2 = fmaf(d1, xv[u] - m1, -var);
         m2 = fmaf(coef, d2, var);
-        const float rstd = rsqrtf(m2 + a.eps);
+        const float rstd = rsqrt_approx(m2 + a.eps);
         const float xn = mk[u] ? 0.f : fmaf((xv[u] - m1) * rstd, w, bb);
-        if (!mk[u]) { mean = m1; var = m2; ++cnt; }
+        if (!mk[u]) { mean = m1; var = m2; ++seen; }
         if (np_) Elem<T>::st(np_ + t * a.ysl, xn);
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll
@@ -102,9 +110,11 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
       }
     }
   }
+  };
+  if (mp) scan(std::true_type{}); else scan(std::false_type{});
   a.mean_out[gid] = mean;
   a.var_out[gid] = var;
-  if (d == 0) a.count_out[b] = cnt;
+  if (d == 0) a.count_out[b] = cnt0 + seen;
   if (kState && a.h_out) {
 #pragma unroll
     for (int n = 0; n < NP; ++n)
