@@ -9,6 +9,7 @@
 // computation on the reversed sequence, delayed by one step when the kernel is shifted.
 // Four lanes share a (batch, channel) row and split its poles; sums over the batch are atomic adds.
 #include "common.cuh"
+#include "stream_bwd.cuh"
 
 namespace mega {
 
@@ -445,6 +446,14 @@ extern "C" int mega_ema_bwd(const void* dy, const void* x, void* dx, int dtype, 
       cudaMemsetAsync(dgamma_hat, 0, K * N * sizeof(float), s) != cudaSuccess ||
       cudaMemsetAsync(domega, 0, (size_t)D * sizeof(float), s) != cudaSuccess)
     return check_launch("ema_bwd(memset)");
+  if (!bidir) {  // channel-contiguous activations: the streamed TMA kernel
+    EmaBwdStreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.mask = pad_mask; sa.h_in = h_in; sa.dh_out = dh_out;
+    sa.dp = dp; sa.dq = dq; sa.dg = dgamma_hat; sa.domega = domega; sa.dh_in = dh_in;
+    if (ema_bwd_stream_try(dtype, dy, x, dx, gsb, gsl, gsd, xsb, xsl, xsd, dsb, dsl, dsd, sa, s))
+      return check_launch("ema_bwd(stream)");
+  }
   EmaBwdArgs a{};
   a.dy = dy; a.x = x; a.dx = dx; a.B = B; a.D = D; a.L = L; a.N = N;
   a.gsb = gsb; a.gsd = gsd; a.gsl = gsl; a.xsb = xsb; a.xsd = xsd; a.xsl = xsl;
@@ -512,6 +521,12 @@ extern "C" int mega_timestep_norm_bwd(const void* dy, const void* x, void* dx, i
   a.cummean = cummean; a.cumrstd = cumrstd; a.group_mean = group_mean; a.gamma = gamma; a.mask = pad_mask;
   a.dprev_mean = dprev_mean; a.dprev_var = dprev_var; a.dgamma = dgamma; a.dbeta = dbeta;
   if (G == D) {
+    TsnBwdStreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.dmean = dmean; sa.dvar = dvar; sa.prev_mean = prev_mean;
+    sa.count = (const long long*)count; sa.gamma = gamma; sa.mask = pad_mask;
+    sa.dprev_mean = dprev_mean; sa.dprev_var = dprev_var; sa.dgamma = dgamma; sa.dbeta = dbeta;
+    if (tsn_bwd_stream_try(dtype, dy, x, dx, gsb, gsl, gsd, xsb, xsl, xsd, dsb, dsl, dsd, cummean, cumrstd, sa, s))
+      return check_launch("timestep_norm_bwd(stream)");
     const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
     MEGA_DISPATCH_DTYPE(dtype, {
       if (pad_mask) launch(tsn_bwd_plain_kernel<T, true>, grid, 128, 0, stream, a);

@@ -1,0 +1,35 @@
+// Interface of the streamed backward kernels (stream_bwd.cu): channel-contiguous activations only.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace mega {
+
+struct TsnBwdStreamArgs {
+  int B, L, D;
+  const float *dmean, *dvar, *prev_mean;  // (B, D); dmean / dvar may be NULL
+  const long long* count;                 // (B) final counts
+  const float* gamma;
+  const unsigned char* mask;
+  float *dprev_mean, *dprev_var, *dgamma, *dbeta;
+};
+
+struct EmaBwdStreamArgs {
+  int B, L, D, N;
+  const float *p, *q, *g, *omega;
+  const unsigned char* mask;
+  const float *h_in, *dh_out;
+  float *dp, *dq, *dg, *domega, *dh_in;
+};
+
+// Each returns false, having launched nothing, outside its envelope (channel stride != 1, bases or
+// strides not 16-byte aligned, more than 65535 sequences, ndim > 16 for the EMA).
+bool tsn_bwd_stream_try(int dtype, const void* dy, const void* x, void* dx, long long gsb, long long gsl,
+                        long long gsd, long long xsb, long long xsl, long long xsd, long long dsb, long long dsl,
+                        long long dsd, const float* cummean, const float* cumrstd, const TsnBwdStreamArgs& a,
+                        cudaStream_t s);
+bool ema_bwd_stream_try(int dtype, const void* dy, const void* x, void* dx, long long gsb, long long gsl,
+                        long long gsd, long long xsb, long long xsl, long long xsd, long long dsb, long long dsl,
+                        long long dsd, const EmaBwdStreamArgs& a, cudaStream_t s);
+cudaError_t stream_bwd_read_device_error(int* v, bool reset);
+
+}  // namespace mega

@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 #include "stream_cl.cuh"
+#include "stream_bwd.cuh"
 
 namespace mega {
 
@@ -415,6 +416,9 @@ extern "C" MEGA_API int mega_debug_device_error(int* host_value, int reset) {
   int v2 = 0;
   if (mega::read_device_error(&v, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
   if (mega::mma_cl_read_device_error(&v2, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
+  int v3 = 0;
+  if (mega::stream_bwd_read_device_error(&v3, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
+  v2 |= v3;
   *host_value = v | v2;
   return MEGA_OK;
 }
