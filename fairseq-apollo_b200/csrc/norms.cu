@@ -356,12 +356,13 @@ static int tsn_fwd_common(const void* x, void* y, int dtype, int B, int L, int D
   a.count_out = (long long*)count_out; a.mean_out = mean_out; a.var_out = var_out;
   a.cummean = cummean; a.cumrstd = cumrstd; a.group_mean = group_mean;
   if (G == D) {
-    if (x != y && !cummean) {
+    if (x != y) {
       StreamArgs sa{};
       sa.B = B; sa.L = L; sa.D = D; sa.N = 0;
       sa.prev_count = a.prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var; sa.gamma = gamma;
       sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
       sa.mask = pad_mask;
+      sa.cummean = cummean; sa.cumrstd = cumrstd;
       if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, false, sa, (cudaStream_t)stream))
         return check_launch("timestep_norm_fwd(stream)");
     }

@@ -72,13 +72,18 @@ struct StreamCfg {
   static constexpr int kS = sizeof(T) == 2 ? 4 : 3;  // input ring depth
   static constexpr int kTile = kR * kW * (int)sizeof(T);
   static constexpr int kHead = 512;  // coefficient double buffer + barriers, keeps tiles 128 B aligned
-  static constexpr int smem_bytes(bool has_xn) { return kHead + kTile * (kS + 2 + (has_xn ? 2 : 0)) + 128; }
+  static constexpr int kTileF = kR * kW * 4;  // fp32 tiles of the training saves
+  static constexpr int smem_bytes(bool has_xn, bool save = false) {
+    return kHead + kTile * (kS + 2 + (has_xn ? 2 : 0)) + (save ? 4 * kTileF : 0) + 128;
+  }
 };
 
-template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx>
+template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx, bool kSave>
 __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ CUtensorMap tmx,
                                                        const __grid_constant__ CUtensorMap tmy,
-                                                       const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
+                                                       const __grid_constant__ CUtensorMap tmn,
+                                                       const __grid_constant__ CUtensorMap tmm,
+                                                       const __grid_constant__ CUtensorMap tmr, StreamArgs a) {
   constexpr int kS = StreamCfg<T>::kS;
   constexpr int kTile = StreamCfg<T>::kTile;
   extern __shared__ unsigned char smem_raw[];
@@ -89,6 +94,9 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
   T* xs = reinterpret_cast<T*>(base + kHead);                          // [kS][kR][kW]
   T* ys = reinterpret_cast<T*>(base + kHead + kS * kTile);             // [2][kR][kW]
   T* ns = reinterpret_cast<T*>(base + kHead + (kS + 2) * kTile);       // [2][kR][kW], only with has_xn
+  // training saves (norm-only mode): running mean and rstd per step, fp32 [2][kR][kW] each
+  float* cms = reinterpret_cast<float*>(base + kHead + (kS + 2) * kTile);
+  float* crs = cms + 2 * kR * kW;
 
   const int tid = threadIdx.x;
   const int d0 = blockIdx.x * kW;
@@ -249,6 +257,10 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
           xn = mk ? 0.f : fmaf(dm * rstd, w, bb);
           mean = mk ? mean : m1;
           var = mk ? var : m2;
+          if (kSave) {  // the running mean after this step (unchanged by a padded step)
+            cms[(o * kR + r) * kW + tid] = mean;
+            crs[(o * kR + r) * kW + tid] = rstd;
+          }
           if (!kEma || a.has_xn) Elem<T>::st((kEma ? ntile : yt) + r * kW, xn);
         } else {
           xn = mk ? 0.f : xr;
@@ -297,6 +309,10 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
     if (tid == 0) {
       tma_store_3d(&tmy, d0, i * kR, b, ys + (size_t)o * kR * kW);
       if (kNorm && kEma && a.has_xn) tma_store_3d(&tmn, d0, i * kR, b, ns + (size_t)o * kR * kW);
+      if (kSave) {
+        tma_store_3d(&tmm, d0, i * kR, b, cms + (size_t)o * kR * kW);
+        tma_store_3d(&tmr, d0, i * kR, b, crs + (size_t)o * kR * kW);
+      }
       bulk_commit();
       if (i + kS < nt) {
         mbar_expect_tx(&full[s], kTile);
@@ -343,23 +359,23 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx = false>
+template <typename T, bool kNorm, bool kEma, bool kState, bool kCplx = false, bool kSave = false>
 static bool launch_one(const CUtensorMap& tx, const CUtensorMap& ty, const CUtensorMap& tn, const StreamArgs& a,
-                       cudaStream_t s) {
-  auto kern = stream_cl_kernel<T, kNorm, kEma, kState, kCplx>;
-  const int smem = StreamCfg<T>::smem_bytes(a.has_xn != 0);
+                       cudaStream_t s, const CUtensorMap* tm = nullptr, const CUtensorMap* tr = nullptr) {
+  auto kern = stream_cl_kernel<T, kNorm, kEma, kState, kCplx, kSave>;
+  const int smem = StreamCfg<T>::smem_bytes(a.has_xn != 0, kSave);
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
     attr_ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   StreamCfg<T>::smem_bytes(true)) == cudaSuccess;
+                                   StreamCfg<T>::smem_bytes(true, kSave)) == cudaSuccess;
   });
   if (!attr_ok) {
     cudaGetLastError();
     return false;
   }
   dim3 grid((a.D + kW - 1) / kW, a.B);
-  launch(kern, grid, dim3(kW), (size_t)smem, (void*)s, tx, ty, tn, a);
+  launch(kern, grid, dim3(kW), (size_t)smem, (void*)s, tx, ty, tn, tm ? *tm : ty, tr ? *tr : ty, a);
   return true;
 }
 
@@ -384,6 +400,15 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
       !make_tensor_map_3d(&tn, dtype, xn, a.D, a.L, a.B, ysl, ysb, kW, kR, 1, CU_TENSOR_MAP_SWIZZLE_NONE))
     return false;
   const bool state = ema && (a.h_in || a.h_out);
+  const bool save = norm && !ema && a.cummean != nullptr && a.cumrstd != nullptr;
+  CUtensorMap tm, tr;
+  if (save) {
+    if (!make_tensor_map_3d(&tm, MEGA_F32, a.cummean, a.D, a.L, a.B, a.D, (long long)a.L * a.D, kW, kR, 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_tensor_map_3d(&tr, MEGA_F32, a.cumrstd, a.D, a.L, a.B, a.D, (long long)a.L * a.D, kW, kR, 1,
+                            CU_TENSOR_MAP_SWIZZLE_NONE))
+      return false;
+  }
   bool ok = false;
   switch (dtype) {
 #define MEGA_STREAM_CASE(DT, TY)                                                        \
@@ -397,6 +422,7 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
                                 : launch_one<TY, true, true, false>(tx, ty, tn, a, s);  \
     else if (ema) ok = state ? launch_one<TY, false, true, true>(tx, ty, tn, a, s)      \
                              : launch_one<TY, false, true, false>(tx, ty, tn, a, s);    \
+    else if (save) ok = launch_one<TY, true, false, false, false, true>(tx, ty, tn, a, s, &tm, &tr); \
     else ok = launch_one<TY, true, false, false>(tx, ty, tn, a, s);                     \
     break;
     MEGA_STREAM_CASE(MEGA_F32, float)

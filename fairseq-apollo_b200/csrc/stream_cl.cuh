@@ -17,6 +17,7 @@ struct StreamArgs {
   const unsigned char* mask;
   int silu;
   int has_xn;
+  float *cummean, *cumrstd;  // training saves of the norm-only mode, (B, L, D) fp32 contiguous, or NULL
   int cplx;  // complex poles: q, g are interleaved (re, im) (K, N, 2); states (B, D, N, 2)
 };
 
