@@ -30,7 +30,7 @@ struct EmaBwdArgs {
 // batches would serialise their loads).
 template <typename T, int NP, bool kMask>
 __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
-  constexpr int U = 16;  // loads in flight per thread: few rows are resident, so latency is hidden per thread
+  constexpr int U = 8;
   const int sub = threadIdx.x & 3;
   const long long row = (long long)blockIdx.x * 32 + (threadIdx.x >> 2);
   const bool live = row < (long long)a.B * a.D;  // dead rows keep running for the shuffles

@@ -212,6 +212,191 @@ __global__ void __launch_bounds__(128) cema_step_kernel(const T* x, T* y, int B,
   Elem<T>::st(y + gid, v);
 }
 
+// ---------------------------------------------------------------------------------------------
+// backward of the complex layer.  h is holomorphic in q and linear in p, so with the complex
+// sensitivities s = dh/dq (s_t = q s_{t-1} + h_{t-1}) and r = dh/dp (r_t = q r_{t-1} + x_t):
+//   dL/dp = Re(gamma sum_t dy_t r_t),  dL/dq_re = Re(gamma sum_t dy_t s_t),  dL/dq_im = -Im(same),
+//   dL/dgamma_re = sum_t dy_t Re h_t,  dL/dgamma_im = -sum_t dy_t Im h_t,
+// and the input gradient is dx_t = sum_n p_n Re(lambda_{n,t}), lambda_t = gamma dy_t + q lambda_{t+1}.
+// Same structure as the real layer's kernel: four lanes per (batch, channel) row, no stored history.
+// ---------------------------------------------------------------------------------------------
+struct CemaBwdArgs {
+  const void *dy, *x;
+  void* dx;
+  int B, D, L, N;
+  long long gsb, gsd, gsl, xsb, xsd, xsl, dsb, dsd, dsl;
+  const float *p, *q, *g, *omega;
+  const unsigned char* mask;
+  float *dp, *dq, *dg, *domega;
+  int bidir, shift;
+};
+
+template <typename T, int NP, bool kMask>
+__global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
+  constexpr int U = 8;
+  const int sub = threadIdx.x & 3;
+  const long long row = (long long)blockIdx.x * 32 + (threadIdx.x >> 2);
+  const bool live = row < (long long)a.B * a.D;
+  const int d = live ? (int)(row % a.D) : 0;
+  const int b = live ? (int)(row / a.D) : 0;
+  const int L = a.L;
+  const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+  const T* gp = reinterpret_cast<const T*>(a.dy) + b * a.gsb + d * a.gsd;
+  T* dxp = reinterpret_cast<T*>(a.dx) + b * a.dsb + d * a.dsd;
+  const unsigned char* mp = kMask ? a.mask + (size_t)b * L : nullptr;
+  const float om = __ldg(a.omega + d);
+  float aw = 0.f;
+
+  for (int half = 0; half < (a.bidir ? 2 : 1); ++half) {
+    const bool rev = half == 1;
+    const bool shift = rev && a.shift;
+    const size_t prow = (size_t)(d + half * a.D) * a.N;
+    float pp[NP], qr[NP], qi[NP], gr[NP], gi[NP];
+    float hr[NP], hi[NP], sr[NP], si[NP], rr[NP], ri[NP];
+    float ahr[NP], ahi[NP], asr[NP], asi[NP], arr[NP], ari[NP];
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+      const int n = k * 4 + sub;
+      const bool ok = n < a.N;
+      pp[k] = ok ? __ldg(a.p + prow + n) : 0.f;
+      qr[k] = ok ? __ldg(a.q + 2 * (prow + n)) : 0.f;
+      qi[k] = ok ? __ldg(a.q + 2 * (prow + n) + 1) : 0.f;
+      gr[k] = ok ? __ldg(a.g + 2 * (prow + n)) : 0.f;
+      gi[k] = ok ? __ldg(a.g + 2 * (prow + n) + 1) : 0.f;
+      hr[k] = hi[k] = sr[k] = si[k] = rr[k] = ri[k] = 0.f;
+      ahr[k] = ahi[k] = asr[k] = asi[k] = arr[k] = ari[k] = 0.f;
+    }
+    for (int u0 = 0; u0 < L; u0 += U) {
+      float xv[U], gv[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int u = u0 + j;
+        xv[j] = gv[j] = 0.f;
+        if (u < L && live) {
+          const int t = rev ? L - 1 - u : u;
+          const float xt = Elem<T>::ld(xp + t * a.xsl);
+          gv[j] = Elem<T>::ld(gp + t * a.gsl);
+          if (half == 0) aw = fmaf(gv[j], xt, aw);
+          xv[j] = (kMask && __ldg(mp + t) != 0) ? 0.f : xt;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        if (u0 + j < L) {
+          const float dy = gv[j], xm = xv[j];
+#pragma unroll
+          for (int k = 0; k < NP; ++k) {
+            if (shift) {
+              ahr[k] = fmaf(dy, hr[k], ahr[k]); ahi[k] = fmaf(dy, hi[k], ahi[k]);
+              asr[k] = fmaf(dy, sr[k], asr[k]); asi[k] = fmaf(dy, si[k], asi[k]);
+              arr[k] = fmaf(dy, rr[k], arr[k]); ari[k] = fmaf(dy, ri[k], ari[k]);
+            }
+            const float nsr = fmaf(qr[k], sr[k], fmaf(-qi[k], si[k], hr[k]));
+            const float nsi = fmaf(qi[k], sr[k], fmaf(qr[k], si[k], hi[k]));
+            const float nhr = fmaf(qr[k], hr[k], fmaf(-qi[k], hi[k], pp[k] * xm));
+            const float nhi = fmaf(qi[k], hr[k], qr[k] * hi[k]);
+            const float nrr = fmaf(qr[k], rr[k], fmaf(-qi[k], ri[k], xm));
+            const float nri = fmaf(qi[k], rr[k], qr[k] * ri[k]);
+            sr[k] = nsr; si[k] = nsi; hr[k] = nhr; hi[k] = nhi; rr[k] = nrr; ri[k] = nri;
+            if (!shift) {
+              ahr[k] = fmaf(dy, nhr, ahr[k]); ahi[k] = fmaf(dy, nhi, ahi[k]);
+              asr[k] = fmaf(dy, nsr, asr[k]); asi[k] = fmaf(dy, nsi, asi[k]);
+              arr[k] = fmaf(dy, nrr, arr[k]); ari[k] = fmaf(dy, nri, ari[k]);
+            }
+          }
+        }
+      }
+    }
+    float lr[NP], li[NP];
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+      const int n = k * 4 + sub;
+      lr[k] = li[k] = 0.f;
+      if (n < a.N && live) {
+        atomicAdd(a.dg + 2 * (prow + n), ahr[k]);
+        atomicAdd(a.dg + 2 * (prow + n) + 1, -ahi[k]);
+        atomicAdd(a.dp + prow + n, gr[k] * arr[k] - gi[k] * ari[k]);
+        atomicAdd(a.dq + 2 * (prow + n), gr[k] * asr[k] - gi[k] * asi[k]);
+        atomicAdd(a.dq + 2 * (prow + n) + 1, -(gr[k] * asi[k] + gi[k] * asr[k]));
+      }
+    }
+    for (int u0 = L - 1; u0 >= 0; u0 -= U) {
+      float gv[U], old[U];
+      bool mk[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int u = u0 - j;
+        gv[j] = old[j] = 0.f;
+        mk[j] = false;
+        if (u >= 0 && live) {
+          const int t = rev ? L - 1 - u : u;
+          gv[j] = Elem<T>::ld(gp + t * a.gsl);
+          mk[j] = kMask && __ldg(mp + t) != 0;
+          if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(dxp + t * a.dsl);  // written by the first half
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int u = u0 - j;
+        if (u >= 0) {
+          float part = 0.f;
+#pragma unroll
+          for (int k = 0; k < NP; ++k) {
+            if (shift) {
+              part = fmaf(pp[k], lr[k], part);
+              const float nr = fmaf(qr[k], lr[k], fmaf(-qi[k], li[k], gr[k] * gv[j]));
+              const float ni = fmaf(qi[k], lr[k], fmaf(qr[k], li[k], gi[k] * gv[j]));
+              lr[k] = nr; li[k] = ni;
+            } else {
+              const float cr = fmaf(gr[k], gv[j], lr[k]), ci = fmaf(gi[k], gv[j], li[k]);
+              part = fmaf(pp[k], cr, part);
+              lr[k] = qr[k] * cr - qi[k] * ci;
+              li[k] = qi[k] * cr + qr[k] * ci;
+            }
+          }
+          part += __shfl_xor_sync(0xffffffffu, part, 1);
+          part += __shfl_xor_sync(0xffffffffu, part, 2);
+          if (live && sub == 0) {
+            const int t = rev ? L - 1 - u : u;
+            const float v = mk[j] ? 0.f : part;
+            Elem<T>::st(dxp + t * a.dsl, half == 0 ? fmaf(om, gv[j], v) : old[j] + v);
+          }
+        }
+      }
+    }
+  }
+  if (live && sub == 0) atomicAdd(a.domega + d, aw);
+}
+
+// Chain rule to the raw parameters: rho = 1 - sigmoid(alpha) sigmoid(delta), phi_n = (n + 1)
+// sigmoid(theta) 2 pi / N, q = rho e^{i phi}: dL/drho = G . e^{i phi}, dL/dphi = G . (i q) with
+// G = (dL/dq_re, dL/dq_im) and "." the real dot product.  One thread per parameter row.
+__global__ void cema_coeffs_bwd_kernel(const float* alpha, const float* delta, const float* theta, const float* q,
+                                       const float* dp, const float* dq, const float* dg, int K, int N,
+                                       float scale, float* dalpha, float* ddelta, float* dtheta, float* dgamma) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  const float st = 1.f / (1.f + __expf(-theta[k]));
+  const float wave = 6.283185307179586f / (float)N;
+  float dth = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const int i = k * N + n;
+    const float a = 1.f / (1.f + __expf(-alpha[i])), dl = 1.f / (1.f + __expf(-delta[i]));
+    const float qr = q[2 * i], qi = q[2 * i + 1];
+    const float rho = 1.f - a * dl;
+    const float cs = rho != 0.f ? qr / rho : 1.f, sn = rho != 0.f ? qi / rho : 0.f;
+    const float gr_ = dq[2 * i], gi_ = dq[2 * i + 1];
+    const float drho = gr_ * cs + gi_ * sn;
+    const float dphi = -gr_ * qi + gi_ * qr;
+    dalpha[i] = (dp[i] - drho * dl) * a * (1.f - a);
+    ddelta[i] = -drho * a * dl * (1.f - dl);
+    dth += dphi * (float)(n + 1);
+    dgamma[2 * i] = dg[2 * i] * scale;
+    dgamma[2 * i + 1] = dg[2 * i + 1] * scale;
+  }
+  dtheta[k] = dth * wave * st * (1.f - st);
+}
+
 }  // namespace mega
 
 using namespace mega;
@@ -337,4 +522,62 @@ extern "C" int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype
   if (rc != MEGA_OK) return rc;
   return mega_cema_fwd(mid, y, dtype, B, D, L, ysb, ysd, ysl, ysb, ysd, ysl, p, q, gamma_hat, omega, N, pad_mask,
                        h_in, h_out, flags, 0, stream);
+}
+
+extern "C" int mega_cema_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int D, int L, int64_t gsb,
+                             int64_t gsd, int64_t gsl, int64_t xsb, int64_t xsd, int64_t xsl, int64_t dsb,
+                             int64_t dsd, int64_t dsl, const float* p, const float* q, const float* gamma_hat,
+                             const float* omega, int N, const uint8_t* pad_mask, unsigned flags, int truncation,
+                             float* dp, float* dq, float* dgamma_hat, float* domega, mega_stream_t stream) {
+  if (!dy || !x || !dx || !p || !q || !gamma_hat || !omega || !dp || !dq || !dgamma_hat || !domega)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || D <= 0 || L <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (flags & MEGA_EMA_SILU) return MEGA_ERR_UNSUPPORTED;
+  if (truncation > 0 && truncation < L) return MEGA_ERR_UNSUPPORTED;
+  const size_t es = elem_size(dtype);
+  if (!aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(dx, es)) return MEGA_ERR_ALIGN;
+  const bool bidir = (flags & MEGA_EMA_BIDIRECTIONAL) != 0;
+  const size_t K = (size_t)(bidir ? 2 : 1) * D;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemsetAsync(dp, 0, K * N * sizeof(float), s) != cudaSuccess ||
+      cudaMemsetAsync(dq, 0, K * N * 2 * sizeof(float), s) != cudaSuccess ||
+      cudaMemsetAsync(dgamma_hat, 0, K * N * 2 * sizeof(float), s) != cudaSuccess ||
+      cudaMemsetAsync(domega, 0, (size_t)D * sizeof(float), s) != cudaSuccess)
+    return check_launch("cema_bwd(memset)");
+  CemaBwdArgs a{};
+  a.dy = dy; a.x = x; a.dx = dx; a.B = B; a.D = D; a.L = L; a.N = N;
+  a.gsb = gsb; a.gsd = gsd; a.gsl = gsl; a.xsb = xsb; a.xsd = xsd; a.xsl = xsl;
+  a.dsb = dsb; a.dsd = dsd; a.dsl = dsl;
+  a.p = p; a.q = q; a.g = gamma_hat; a.omega = omega; a.mask = pad_mask;
+  a.dp = dp; a.dq = dq; a.dg = dgamma_hat; a.domega = domega;
+  a.bidir = bidir ? 1 : 0;
+  a.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
+  const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
+  const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
+#define MEGA_CEMA_BWD(NPV)                                                          \
+  if (pad_mask) launch(cema_bwd_kernel<T, NPV, true>, grid, 128, 0, stream, a);      \
+  else launch(cema_bwd_kernel<T, NPV, false>, grid, 128, 0, stream, a)
+  MEGA_DISPATCH_DTYPE(dtype, {
+    if (np == 1) { MEGA_CEMA_BWD(1); }
+    else if (np == 2) { MEGA_CEMA_BWD(2); }
+    else if (np == 4) { MEGA_CEMA_BWD(4); }
+    else { MEGA_CEMA_BWD(8); }
+  });
+#undef MEGA_CEMA_BWD
+  return check_launch("cema_bwd");
+}
+
+extern "C" int mega_cema_coeffs_bwd(const float* alpha, const float* delta, const float* theta, const float* q,
+                                    const float* dp, const float* dq, const float* dgamma_hat, int K, int N,
+                                    float* dalpha, float* ddelta, float* dtheta, float* dgamma,
+                                    mega_stream_t stream) {
+  if (!alpha || !delta || !theta || !q || !dp || !dq || !dgamma_hat || !dalpha || !ddelta || !dtheta || !dgamma)
+    return MEGA_ERR_NULL;
+  if (K <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  launch(cema_coeffs_bwd_kernel, (unsigned)((K + 127) / 128), 128, 0, stream, alpha, delta, theta, q, dp, dq,
+         dgamma_hat, K, N, rsqrtf((float)N), dalpha, ddelta, dtheta, dgamma);
+  return check_launch("cema_coeffs_bwd");
 }

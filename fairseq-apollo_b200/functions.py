@@ -35,6 +35,29 @@ class EMAFunction(torch.autograd.Function):
                 dom.to(omega.dtype), None, None, None)
 
 
+class ComplexEMAFunction(torch.autograd.Function):
+    """y = complex EMA(x) for x (B, D, L); parameters alpha, delta (K, N, 1), theta (K, 1, 1),
+    gamma (K, N, 2), omega (D, 1) as in MultiHeadComplexEMA."""
+
+    @staticmethod
+    def forward(ctx, x, alpha, delta, theta, gamma, omega, padding_mask, bidirectional, shift):
+        p, q, g = ops.cema_coeffs(alpha, delta, theta, gamma)
+        y = ops.cema_forward(x, p, q, g, omega, padding_mask, None, False, bidirectional=bidirectional, shift=shift)
+        ctx.save_for_backward(x, alpha, delta, theta, omega, padding_mask, p, q, g)
+        ctx.bidirectional, ctx.shift = bidirectional, shift
+        ctx.gamma_dtype = gamma.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, alpha, delta, theta, omega, padding_mask, p, q, g = ctx.saved_tensors
+        dx, dp, dq, dg, dom = ops.cema_backward(dy, x, p, q, g, omega, padding_mask,
+                                                bidirectional=ctx.bidirectional, shift=ctx.shift)
+        da, dd, dt, dgm = ops.cema_coeffs_bwd(alpha, delta, theta, q, dp, dq, dg)
+        return (dx, da.to(alpha.dtype), dd.to(delta.dtype), dt.to(theta.dtype), dgm.to(ctx.gamma_dtype),
+                dom.view_as(omega).to(omega.dtype), None, None, None)
+
+
 class TimestepNormFunction(torch.autograd.Function):
     """(y, count, mean, var) = TimestepNorm(x (B, L, D)); gamma is the effective scale."""
 

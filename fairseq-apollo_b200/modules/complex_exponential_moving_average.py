@@ -6,7 +6,8 @@ Same constructor, parameters (alpha, delta (K, N, 1); theta (K, 1, 1); gamma (K,
 (D, 1)), state-dict keys, ``forward(x (B, D, L), padding_mask, incremental_state)``, the
 ``"ema_state"/{"prev_state"}`` buffer holding a complex64 (B, D, N) state, ``coeffs``, ``kernel``,
 ``step``, ``one_step``, ``parameters_no_weight_decay`` and ``reorder_incremental_state``.
-Forward only: the backward kernels of this build cover the real-valued layer.
+With autograd enabled the layer runs through an autograd Function whose forward and backward are
+library kernels (no incremental state and no truncated kernel on that path).
 """
 import math
 from collections import OrderedDict
@@ -16,6 +17,7 @@ import torch
 from torch import Tensor, nn
 
 from .. import ops
+from ..functions import ComplexEMAFunction, needs_grad
 from ..incremental_state import IncrementalStateMixin, require_no_grad
 
 
@@ -137,12 +139,21 @@ class MultiHeadComplexEMA(IncrementalStateMixin, nn.Module):
                 activation: Optional[str] = None) -> Tensor:
         """x: (B, D, L) (any strides).  padding_mask: (B, L), non-zero = pad.
         ``activation='silu'`` fuses the caller's move_act into the epilogue."""
-        require_no_grad(x, self.alpha, self.delta, self.theta, self.gamma, self.omega)
         bsz, embed_dim, seq_len = x.size()
         assert embed_dim == self.embed_dim
         assert activation in (None, 'silu')
         assert not self.bidirectional or incremental_state is None, \
             'Bidirectional EMA does not support incremental state'
+        if needs_grad(x, self.alpha, self.delta, self.theta, self.gamma, self.omega):
+            # differentiable path: forward and backward kernels behind an autograd Function; the
+            # activation is applied by torch on the result, as the reference's caller does
+            if incremental_state is not None:
+                raise NotImplementedError("the incremental state is an inference feature: use torch.no_grad()")
+            if self.truncation is not None and self.truncation >= 1:
+                raise NotImplementedError("the backward kernel does not implement a truncated kernel")
+            y = ComplexEMAFunction.apply(x, self.alpha, self.delta, self.theta, self.gamma, self.omega,
+                                         padding_mask, self.bidirectional, self.shift)
+            return torch.nn.functional.silu(y) if activation == 'silu' else y
         p, q, g = self.coeffs()
         p, q = p.squeeze(-1), q.squeeze(-1)
         silu = activation == 'silu'

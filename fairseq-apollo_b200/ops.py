@@ -581,3 +581,45 @@ def cema_step(x, p, q, g, omega, h=None, silu=False):
                                              q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(h),
                                              h_out.data_ptr(), EMA_SILU if silu else 0, _stream()), "cema_step")
     return y.view(shape), torch.view_as_complex(h_out)
+
+
+def cema_backward(dy, x, p, q, g, omega, padding_mask=None, bidirectional=False, shift=True):
+    """Gradients of cema_forward (no activation, no truncation, no carried state):
+    (dx, dp (K, N), dq (K, N) complex64 = dL/dRe q + i dL/dIm q, dgamma_hat likewise, domega (D))."""
+    _cuda(dy, x, p, q, g, omega, padding_mask)
+    bsz, dim, length = x.shape
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    p, q, g, omega = _f32c(p), _c64(q), _c64(g), _f32c(omega).reshape(-1)
+    n = p.shape[1]
+    mask = _mask_u8(padding_mask, bsz, length)
+    dx = _like(x)
+    dp = torch.empty_like(p)
+    dq = torch.empty_like(q)
+    dg = torch.empty_like(g)
+    dom = torch.empty(dim, device=x.device, dtype=torch.float32)
+    flags = (EMA_BIDIRECTIONAL if bidirectional else 0) | (0 if shift else EMA_NO_SHIFT)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_cema_bwd(
+            dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *dy.stride(), *x.stride(),
+            *dx.stride(), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), flags, 0,
+            dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(), _stream()), "cema_bwd")
+    return dx, dp, torch.view_as_complex(dq), torch.view_as_complex(dg), dom
+
+
+def cema_coeffs_bwd(alpha, delta, theta, q, dp, dq, dg):
+    """(dalpha, ddelta (K, N, 1), dtheta (K, 1, 1), dgamma (K, N, 2)) from the coefficient gradients."""
+    _cuda(alpha, delta, theta, q, dp, dq, dg)
+    k, n = alpha.shape[0], alpha.shape[1]
+    a, d, t = _f32c(alpha).view(k, n), _f32c(delta).view(k, n), _f32c(theta).view(k)
+    q, dp, dq, dg = _c64(q), _f32c(dp), _c64(dq), _c64(dg)
+    da = torch.empty(k, n, device=alpha.device, dtype=torch.float32)
+    dd = torch.empty_like(da)
+    dt = torch.empty(k, device=alpha.device, dtype=torch.float32)
+    dgm = torch.empty(k, n, 2, device=alpha.device, dtype=torch.float32)
+    with torch.cuda.device(alpha.device):
+        _lib.check(_lib.lib().mega_cema_coeffs_bwd(a.data_ptr(), d.data_ptr(), t.data_ptr(), q.data_ptr(),
+                                                   dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), k, n, da.data_ptr(),
+                                                   dd.data_ptr(), dt.data_ptr(), dgm.data_ptr(), _stream()),
+                   "cema_coeffs_bwd")
+    return da.unsqueeze(-1), dd.unsqueeze(-1), dt.view(k, 1, 1), dgm

@@ -369,6 +369,22 @@ MEGA_API int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, 
                       const float* omega, int N, const uint8_t* pad_mask, const float* h_in, float* h_out,
                       unsigned flags, mega_stream_t stream);
 
+/*
+ * mega_cema_bwd / mega_cema_coeffs_bwd: gradients of mega_cema_fwd (no SiLU flag, no truncation, no
+ * carried state), same argument conventions as mega_ema_bwd; dq and dgamma_hat are (K, N, 2) with
+ * the gradients of the real and imaginary parts, dtheta is (K).
+ * Replaces: autograd through MultiHeadComplexEMA (ema_parameters_bwd + the FFT convolution backward +
+ * _calc_coeffs, complex_exponential_moving_average.py:79-109).
+ */
+MEGA_API int mega_cema_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int D, int L, int64_t gsb,
+                  int64_t gsd, int64_t gsl, int64_t xsb, int64_t xsd, int64_t xsl, int64_t dsb, int64_t dsd,
+                  int64_t dsl, const float* p, const float* q, const float* gamma_hat, const float* omega,
+                  int N, const uint8_t* pad_mask, unsigned flags, int truncation, float* dp, float* dq,
+                  float* dgamma_hat, float* domega, mega_stream_t stream);
+MEGA_API int mega_cema_coeffs_bwd(const float* alpha, const float* delta, const float* theta, const float* q,
+                         const float* dp, const float* dq, const float* dgamma_hat, int K, int N,
+                         float* dalpha, float* ddelta, float* dtheta, float* dgamma, mega_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,7 +5,7 @@ Run in a container where the reference checkout is mounted (default
 ``oracle/_ref/mega_ref_cpu.so`` (python oracle/build_ref.py).  The fixtures are
 committed; nothing at test time reads the reference checkout.
 
-Usage: python tests/golden/make_golden.py [all|forward|backward|cema].
+Usage: python tests/golden/make_golden.py [all|forward|backward|cema|cema_backward].
 
 What runs:
   * the reference's CPU C++ ops (timestep_norm_fwd, group_timestep_norm_fwd,
@@ -372,8 +372,36 @@ def cema_fixtures():
         step_y1=y1, step_h1=torch.view_as_real(h1), step_y2=y2, step_h2=torch.view_as_real(h2), **params_of(m))
 
 
+def cema_backward_fixtures():
+    """Gradients of MultiHeadComplexEMA by autograd through the reference module itself
+    (ema_parameters_bwd C++ op + the Python FFT convolution backward)."""
+    ops, cema, tsn, sqn = import_reference()
+    gen = torch.Generator().manual_seed(20251128)
+    torch.manual_seed(20251128)
+    for tag, (bsz, dim, length, ndim, bidir, shift, pad) in {
+        "cema_bwd_uni": (3, 6, 45, 16, False, True, 0.3),
+        "cema_bwd_uni_n3": (2, 5, 40, 3, False, True, 0.0),
+        "cema_bwd_bidir_shift": (2, 5, 37, 16, True, True, 0.4),
+        "cema_bwd_bidir_noshift": (2, 4, 32, 16, True, False, 0.3),
+    }.items():
+        m = cema.MultiHeadComplexEMA(dim, ndim=ndim, bidirectional=bidir, shift=shift).train()
+        with torch.no_grad():
+            m.gamma[:, :, 1].normal_(0, 1, generator=gen)
+        x = torch.randn(bsz, dim, length, generator=gen).requires_grad_(True)
+        dy = torch.randn(bsz, dim, length, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None
+        y = m(x, mask, None)
+        (y * dy).sum().backward()
+        npz(tag, x=x, dy=dy, mask=(mask if mask is not None else np.zeros((0,), bool)), bidirectional=bidir,
+            shift=shift, y=y, alpha=m.alpha, delta=m.delta, theta=m.theta, gamma=m.gamma, omega=m.omega,
+            dx=x.grad, dalpha=m.alpha.grad, ddelta=m.delta.grad, dtheta=m.theta.grad, dgamma=m.gamma.grad,
+            domega=m.omega.grad)
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "cema_backward"):
+        cema_backward_fixtures()
     if which in ("all", "cema"):
         cema_fixtures()
     if which in ("all", "forward"):

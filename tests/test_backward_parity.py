@@ -238,3 +238,53 @@ def test_block_training_step():
     assert rel_l2(norm.weight.grad, w.grad) < 2e-4 and rel_l2(norm.bias.grad, b.grad) < 2e-4
     for t, r in zip((move.alpha, move.delta, move.beta, move.gamma, move.omega), leaves):
         assert rel_l2(t.grad, r.grad) < 2e-4
+
+
+@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift"])
+def test_complex_ema_golden(name):
+    """MultiHeadComplexEMA under autograd against the gradients of the reference module."""
+    M, _ = _mods()
+    g = golden(name)
+    m = M.MultiHeadComplexEMA(g["x"].shape[1], ndim=g["alpha"].shape[1], bidirectional=bool(g["bidirectional"]),
+                              shift=bool(g["shift"])).cuda().train()
+    with torch.no_grad():
+        for k in ("alpha", "delta", "theta", "gamma", "omega"):
+            getattr(m, k).copy_(g[k])
+    x = g["x"].cuda().requires_grad_(True)
+    mask = opt_mask(g["mask"])
+    y = m(x, None if mask is None else mask.cuda())
+    assert rel_l2(y, g["y"]) < 1e-5
+    (y * g["dy"].cuda()).sum().backward()
+    assert rel_l2(x.grad, g["dx"]) < 2e-5
+    for k in ("alpha", "delta", "theta", "gamma", "omega"):
+        assert rel_l2(getattr(m, k).grad, g["d" + k]) < 1e-4, k
+
+
+@pytest.mark.parametrize("bsz,dim,length,ndim,bidir,shift", [(2, 7, 33, 16, False, True), (3, 5, 130, 2, False, True),
+                                                             (2, 9, 65, 32, False, True), (2, 6, 40, 16, True, True),
+                                                             (2, 3, 31, 5, True, False)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_complex_ema_grid(bsz, dim, length, ndim, bidir, shift, dtype):
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(dim * 100 + length)
+    torch.manual_seed(dim * 100 + length)
+    m = M.MultiHeadComplexEMA(dim, ndim=ndim, bidirectional=bidir, shift=shift).cuda().train()
+    with torch.no_grad():
+        m.gamma[:, :, 1].normal_(0, 1)
+    x0 = torch.randn(bsz, length, dim, generator=gen).to(dtype)
+    dy = torch.randn(bsz, dim, length, generator=gen).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.4)
+    if length > 4:
+        mask[0, 2] = True
+    names = ("alpha", "delta", "theta", "gamma", "omega")
+    leaves = [_leaf(getattr(m, k).detach().cpu()) for k in names]
+    xr = _leaf(x0.float().transpose(1, 2))
+    yr = O.cema_forward_recurrence(xr, *leaves, mask, bidirectional=bidir, shift=shift)
+    (yr * dy.double()).sum().backward()
+    xd = x0.cuda().requires_grad_(True)
+    y = m(xd.transpose(1, 2), mask.cuda())
+    (y.float() * dy.cuda().float()).sum().backward()
+    tol_x, tol_p = (2e-5, 1e-4) if dtype == torch.float32 else (2e-2, 2e-2)
+    assert rel_l2(xd.grad.float().transpose(1, 2), xr.grad) < tol_x
+    for k, r in zip(names, leaves):
+        assert rel_l2(getattr(m, k).grad, r.grad) < tol_p, k

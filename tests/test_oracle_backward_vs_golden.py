@@ -49,3 +49,15 @@ def test_sequence_norm_gradients(name):
     (y * g["dy"].double()).sum().backward()
     for t, k in ((x, "dx"), (gamma, "dgamma"), (beta, "dbeta")):
         assert rel_l2(t.grad, g[k]) < 2e-5, k
+
+
+@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift"])
+def test_complex_ema_gradients(name):
+    g = golden(name)
+    leaves = [_leaf(g[k]) for k in ("x", "alpha", "delta", "theta", "gamma", "omega")]
+    y = O.cema_forward_recurrence(*leaves, opt_mask(g["mask"]), bidirectional=bool(g["bidirectional"]),
+                                  shift=bool(g["shift"]))
+    assert rel_l2(y, g["y"]) < 2e-6
+    (y * g["dy"].double()).sum().backward()
+    for t, k in zip(leaves, ("dx", "dalpha", "ddelta", "dtheta", "dgamma", "domega")):
+        assert rel_l2(t.grad, g[k]) < 2e-5, k
