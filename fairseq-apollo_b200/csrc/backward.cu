@@ -418,6 +418,92 @@ __global__ void __launch_bounds__(256) sqn_bwd_kernel(SqnBwdArgs a) {
   }
 }
 
+// Grouped SequenceNorm backward (fairseq/csrc/ops/sequence_norm.cc:657-860): statistics are shared by
+// the D / G channels of a group.  One CTA per (batch, group): per-channel masked sums of dy and
+// dy * x (kept for dgamma / dbeta), combined with the scale into the group's sums, then dx.
+struct SqnGroupBwdArgs {
+  SqnBwdArgs base;
+  int G;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) sqn_bwd_group_kernel(SqnGroupBwdArgs ga) {
+  extern __shared__ float chan[];  // [2][gs]: ds, db per channel of the group
+  __shared__ float red[2][8];
+  const SqnBwdArgs& a = ga.base;
+  const int gs = a.D / ga.G;
+  const int g = blockIdx.x % ga.G, b = blockIdx.x / ga.G;
+  const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
+  float dsw = 0.f, dbw = 0.f;  // meaningful in thread 0
+  for (int k = 0; k < gs; ++k) {
+    const int d = g * gs + k;
+    const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+    const T* gp = reinterpret_cast<const T*>(a.dy) + b * a.gsb + d * a.gsd;
+    float ds = 0.f, db = 0.f;
+    for (int t = threadIdx.x; t < a.L; t += blockDim.x) {
+      if (mp && mp[t]) continue;
+      const float dy = Elem<T>::ld(gp + t * a.gsl);
+      ds = fmaf(dy, Elem<T>::ld(xp + t * a.xsl), ds);
+      db += dy;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ds += __shfl_xor_sync(0xffffffffu, ds, o);
+      db += __shfl_xor_sync(0xffffffffu, db, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = ds;
+      red[1][threadIdx.x >> 5] = db;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ds = db = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        ds += red[0][w];
+        db += red[1][w];
+      }
+      chan[k] = ds;
+      chan[gs + k] = db;
+      const float w = __ldg(a.gamma + d);
+      dsw = fmaf(ds, w, dsw);
+      dbw = fmaf(db, w, dbw);
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    red[0][0] = dsw;
+    red[1][0] = dbw;
+  }
+  __syncthreads();
+  dsw = red[0][0];
+  dbw = red[1][0];
+  const float u = a.mean[blockIdx.x], r = a.rstd[blockIdx.x];
+  const long long cnt = a.count[b];
+  const float coef = cnt > 0 ? 1.f / ((float)cnt * (float)gs) : 0.f;
+  const float dv = 0.5f * (r * r * r) * (u * dbw - dsw);
+  const float du = -r * dbw;
+  for (int k = 0; k < gs; ++k) {
+    const int d = g * gs + k;
+    const T* xp = reinterpret_cast<const T*>(a.x) + b * a.xsb + d * a.xsd;
+    const T* gp = reinterpret_cast<const T*>(a.dy) + b * a.gsb + d * a.gsd;
+    T* dxp = reinterpret_cast<T*>(a.dx) + b * a.dsb + d * a.dsd;
+    const float w = __ldg(a.gamma + d);
+    for (int t = threadIdx.x; t < a.L; t += blockDim.x) {
+      float out = 0.f;
+      if (!(mp && mp[t])) {
+        const float dy = Elem<T>::ld(gp + t * a.gsl), x = Elem<T>::ld(xp + t * a.xsl);
+        out = r * w * dy + 2.f * coef * (x - u) * dv + coef * du;
+      }
+      Elem<T>::st(dxp + t * a.dsl, out);
+    }
+  }
+  for (int k = threadIdx.x; k < gs; k += blockDim.x) {
+    atomicAdd(a.dgamma + g * gs + k, r * (chan[k] - u * chan[gs + k]));
+    atomicAdd(a.dbeta + g * gs + k, chan[gs + k]);
+  }
+}
+
 }  // namespace mega
 
 using namespace mega;
@@ -548,7 +634,8 @@ extern "C" int mega_sequence_norm_bwd(const void* dy, const void* x, void* dx, i
   if (!dy || !x || !dx || !count || !mean || !rstd || !gamma || !dgamma || !dbeta) return MEGA_ERR_NULL;
   if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
   if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
-  if (num_groups > 0 && num_groups != D) return MEGA_ERR_UNSUPPORTED;  // grouped backward not built
+  const int G = (num_groups <= 0 || num_groups == D) ? D : num_groups;
+  if (D % G != 0) return MEGA_ERR_SHAPE;
   const size_t es = elem_size(dtype);
   if (!aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(dx, es)) return MEGA_ERR_ALIGN;
   cudaStream_t s = (cudaStream_t)stream;
@@ -561,6 +648,13 @@ extern "C" int mega_sequence_norm_bwd(const void* dy, const void* x, void* dx, i
   a.dsb = dsb; a.dsd = dsd; a.dsl = dsl;
   a.count = (const long long*)count; a.mean = mean; a.rstd = rstd; a.gamma = gamma; a.mask = pad_mask;
   a.dgamma = dgamma; a.dbeta = dbeta;
+  if (G != D) {
+    SqnGroupBwdArgs ga{a, G};
+    const size_t smem = (size_t)(D / G) * 2 * sizeof(float);
+    if (smem > 48 * 1024) return MEGA_ERR_UNSUPPORTED;  // more than 6144 channels per group
+    MEGA_DISPATCH_DTYPE(dtype, launch(sqn_bwd_group_kernel<T>, (unsigned)((long long)B * G), 256, smem, stream, ga));
+    return check_launch("sequence_norm_bwd(group)");
+  }
   MEGA_DISPATCH_DTYPE(dtype, launch(sqn_bwd_kernel<T>, (unsigned)((long long)B * D), 256, 0, stream, a));
   return check_launch("sequence_norm_bwd");
 }

@@ -82,18 +82,20 @@ class TimestepNormFunction(torch.autograd.Function):
 
 
 class SequenceNormFunction(torch.autograd.Function):
-    """y = SequenceNorm(x); per-channel statistics; gamma is the effective scale."""
+    """y = SequenceNorm(x), per channel or per channel group; gamma is the effective scale."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, padding_mask, eps, length_last):
-        y, count, mean, rstd = ops.sequence_norm_fwd(x, gamma, beta, padding_mask, eps, length_last, None)
+    def forward(ctx, x, gamma, beta, padding_mask, eps, length_last, num_groups=None):
+        y, count, mean, rstd = ops.sequence_norm_fwd(x, gamma, beta, padding_mask, eps, length_last, num_groups)
         ctx.save_for_backward(x, count, mean, rstd, gamma, padding_mask)
         ctx.length_last = length_last
+        ctx.num_groups = num_groups
         ctx.dtypes = (gamma.dtype, beta.dtype)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, count, mean, rstd, gamma, padding_mask = ctx.saved_tensors
-        dx, dgamma, dbeta = ops.sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask, ctx.length_last)
-        return dx, dgamma.to(ctx.dtypes[0]), dbeta.to(ctx.dtypes[1]), None, None, None
+        dx, dgamma, dbeta = ops.sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask, ctx.length_last,
+                                                  ctx.num_groups)
+        return dx, dgamma.to(ctx.dtypes[0]), dbeta.to(ctx.dtypes[1]), None, None, None, None

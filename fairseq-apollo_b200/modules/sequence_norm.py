@@ -26,10 +26,8 @@ class SequenceNorm(nn.Module):
     def forward(self, x: torch.Tensor, padding_mask: Optional[torch.Tensor] = None,
                 length_last: bool = True) -> torch.Tensor:
         if needs_grad(x, self.weight, self.bias):
-            if self.num_groups is not None and self.num_groups != self.num_features:
-                raise NotImplementedError("the grouped SequenceNorm backward is not part of this build")
             return SequenceNormFunction.apply(x, self.weight.float() + 1.0, self.bias.float(), padding_mask,
-                                              self.eps, length_last)
+                                              self.eps, length_last, self.num_groups)
         y, _, _, _ = ops.sequence_norm_fwd(x, self.weight.detach().float() + 1.0, self.bias, padding_mask,
                                            self.eps, length_last, self.num_groups)
         return y

@@ -435,8 +435,8 @@ def timestep_norm_bwd(dy, dmean, dvar, x, prev_mean, count, cummean, cumrstd, gr
     return dx, dpm, dpv, dgamma, dbeta
 
 
-def sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask=None, length_last=True):
-    """Gradients of the per-channel SequenceNorm: (dx, dgamma, dbeta)."""
+def sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask=None, length_last=True, num_groups=None):
+    """Gradients of SequenceNorm (per channel, or per group with ``num_groups``): (dx, dgamma, dbeta)."""
     _cuda(dy, x, count, mean, rstd, gamma, padding_mask)
     if length_last:
         bsz, dim, length = x.shape
@@ -455,8 +455,9 @@ def sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask=None, length
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().mega_sequence_norm_bwd(
             dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *gs, *xs, *ds,
-            count.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gamma.data_ptr(), _ptr(mask), dim,
-            dgamma.data_ptr(), dbeta.data_ptr(), _stream()), "sequence_norm_bwd")
+            count.data_ptr(), mean.data_ptr(), rstd.data_ptr(), gamma.data_ptr(), _ptr(mask),
+            dim if num_groups is None else int(num_groups), dgamma.data_ptr(), dbeta.data_ptr(), _stream()),
+            "sequence_norm_bwd")
     return dx, dgamma, dbeta
 
 

@@ -282,11 +282,11 @@ MEGA_API int mega_timestep_norm_bwd(const void* dy, const void* x, void* dx, int
                            float* dgamma, float* dbeta, mega_stream_t stream);
 
 /*
- * mega_sequence_norm_bwd: gradients of SequenceNorm (per-channel form).  dy, x, dx are (B, D, L)
+ * mega_sequence_norm_bwd: gradients of SequenceNorm (per-channel and grouped forms; mean, rstd are (B, G)).  dy, x, dx are (B, D, L)
  * with strides in elements (the length-major order of a (B, L, D) tensor is a stride pattern);
  * count (B), mean, rstd (B, D) are the forward's outputs.  dgamma, dbeta (D) are zeroed on the
- * stream and accumulated over the batch.  num_groups other than 0 / D: MEGA_ERR_UNSUPPORTED.
- * Replaces: sequence_norm_bwd (fairseq/csrc/ops/sequence_norm.cc:374-529).
+ * stream and accumulated over the batch.
+ * Replaces: sequence_norm_bwd, group_sequence_norm_bwd (fairseq/csrc/ops/sequence_norm.cc:374-529, 657-860).
  */
 MEGA_API int mega_sequence_norm_bwd(const void* dy, const void* x, void* dx, int dtype, int B, int D, int L,
                            int64_t gsb, int64_t gsd, int64_t gsl, int64_t xsb, int64_t xsd, int64_t xsl,

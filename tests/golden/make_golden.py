@@ -306,6 +306,21 @@ def backward_fixtures():
             prev_mean=prev_mean, prev_var=prev_var, gamma=gamma, beta=beta, dmean=dmean, dvar=dvar,
             groups=(-1 if groups is None else groups), dx=dx, dprev_mean=dpm, dprev_var=dpv, dgamma=dg, dbeta=db)
 
+    for tag, (bsz, feat, length, length_last, groups) in {
+        "sqn_bwd_bhl_group": (3, 12, 41, True, 3),
+        "sqn_bwd_blh_group": (2, 12, 38, False, 4),
+    }.items():
+        shape = (bsz, feat, length) if length_last else (bsz, length, feat)
+        x = torch.randn(*shape, generator=gen) * 2.0 - 0.5
+        dy = torch.randn(*shape, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, 0.5)
+        gamma = torch.randn(feat, generator=gen) * 0.1 + 1.0
+        beta = torch.randn(feat, generator=gen) * 0.1
+        y, cnt, mean, rstd = ops.group_sequence_norm_fwd(x, gamma, beta, mask, groups, 1e-5, length_last)
+        dx, dg, db = ops.group_sequence_norm_bwd(dy, x, cnt, mean, rstd, gamma, mask, groups, length_last)
+        npz(tag, x=x, dy=dy, mask=mask, gamma=gamma, beta=beta, length_last=length_last, groups=groups, dx=dx,
+            dgamma=dg, dbeta=db)
+
     for tag, (bsz, feat, length, length_last, pad) in {
         "sqn_bwd_bhl": (3, 6, 41, True, 0.5),
         "sqn_bwd_blh": (3, 7, 38, False, 0.5),

@@ -76,8 +76,8 @@ def test_argument_rejection_training_and_complex_entry_points():
                                             1e-5, one, one, one, None, None, None, None) == 1
     assert lib.mega_timestep_norm_fwd_train(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 2,
                                             1e-5, one, one, one, one, one, None, None) == 1
-    # mega_sequence_norm_bwd: the grouped form is not built
-    assert lib.mega_sequence_norm_bwd(one, one, one, 0, 1, 8, 4, *st9, one, one, one, one, None, 2, one, one, None) == 7
+    # mega_sequence_norm_bwd: groups must divide the channels
+    assert lib.mega_sequence_norm_bwd(one, one, one, 0, 1, 8, 4, *st9, one, one, one, one, None, 3, one, one, None) == 3
     assert lib.mega_sequence_norm_bwd(one, one, one, 5, 1, 8, 4, *st9, one, one, one, one, None, 8, one, one, None) == 2
     # complex EMA: same envelope rules as the real layer
     cema = lambda x, N, flags, trunc, h: lib.mega_cema_fwd(x, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, N,

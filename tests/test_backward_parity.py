@@ -171,22 +171,25 @@ def test_tsn_module_grid(bsz, length, feat, groups, dtype):
         assert rel_l2(t.grad, r.grad) < (2e-4 if f32 else 2e-2), k
 
 
-@pytest.mark.parametrize("name", ["sqn_bwd_bhl", "sqn_bwd_blh"])
+@pytest.mark.parametrize("name", ["sqn_bwd_bhl", "sqn_bwd_blh", "sqn_bwd_bhl_group", "sqn_bwd_blh_group"])
 def test_sqn_golden(name):
     M, _ = _mods()
     g = golden(name)
     ll = bool(g["length_last"])
+    groups = g.get("groups")
     mask = g["mask"].bool().cuda()
-    y, cnt, mean, rstd = M.ops.sequence_norm_fwd(g["x"].cuda(), g["gamma"].cuda(), g["beta"].cuda(), mask, 1e-5, ll)
+    y, cnt, mean, rstd = M.ops.sequence_norm_fwd(g["x"].cuda(), g["gamma"].cuda(), g["beta"].cuda(), mask, 1e-5, ll,
+                                                 groups)
     dx, dgamma, dbeta = M.ops.sequence_norm_bwd(g["dy"].cuda(), g["x"].cuda(), cnt, mean, rstd, g["gamma"].cuda(),
-                                                mask, ll)
+                                                mask, ll, groups)
     assert rel_l2(dx, g["dx"]) < 2e-5
     assert rel_l2(dgamma, g["dgamma"]) < 1e-4 and rel_l2(dbeta, g["dbeta"]) < 1e-4
 
 
-@pytest.mark.parametrize("bsz,feat,length", [(1, 1, 1), (2, 5, 300), (3, 64, 1000), (2, 7, 4100)])
+@pytest.mark.parametrize("bsz,feat,length,groups", [(1, 1, 1, None), (2, 5, 300, None), (3, 64, 1000, None),
+                                                     (2, 7, 4100, None), (2, 48, 500, 4), (3, 30, 77, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_sqn_module_grid(bsz, feat, length, dtype):
+def test_sqn_module_grid(bsz, feat, length, groups, dtype):
     M, O = _mods()
     gen = torch.Generator().manual_seed(length + feat)
     x = (torch.randn(bsz, feat, length, generator=gen) * 2 - 0.5).to(dtype)
@@ -194,13 +197,13 @@ def test_sqn_module_grid(bsz, feat, length, dtype):
     mask = right_pad_mask(gen, bsz, length, 0.5)
     if length > 4:
         mask[0, 1] = True
-    mod = M.SequenceNorm(feat).cuda().train()
+    mod = M.SequenceNorm(feat, groups).cuda().train()
     with torch.no_grad():
         mod.weight.copy_(torch.randn(feat, generator=gen) * 0.1)
         mod.bias.copy_(torch.randn(feat, generator=gen) * 0.1)
     w, b = _leaf(mod.weight.detach().cpu()), _leaf(mod.bias.detach().cpu())
     xr = _leaf(x.float())
-    yr = O.sequence_norm(xr, w + 1.0, b, mask, None, 1e-5, True, acc_dtype=torch.float64)[0]
+    yr = O.sequence_norm(xr, w + 1.0, b, mask, groups, 1e-5, True, acc_dtype=torch.float64)[0]
     (yr * dy.double()).sum().backward()
     xd = x.cuda().requires_grad_(True)
     y = mod(xd, mask.cuda())

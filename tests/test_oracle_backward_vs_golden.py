@@ -41,11 +41,12 @@ def test_timestep_norm_gradients(name):
         assert rel_l2(t.grad, g[k]) < 2e-5, k
 
 
-@pytest.mark.parametrize("name", ["sqn_bwd_bhl", "sqn_bwd_blh"])
+@pytest.mark.parametrize("name", ["sqn_bwd_bhl", "sqn_bwd_blh", "sqn_bwd_bhl_group", "sqn_bwd_blh_group"])
 def test_sequence_norm_gradients(name):
     g = golden(name)
     x, gamma, beta = [_leaf(g[k]) for k in ("x", "gamma", "beta")]
-    y = O.sequence_norm(x, gamma, beta, g["mask"].bool(), None, 1e-5, bool(g["length_last"]))[0]
+    y = O.sequence_norm(x, gamma, beta, g["mask"].bool(), g.get("groups"), 1e-5, bool(g["length_last"]),
+                        acc_dtype=torch.float64)[0]
     (y * g["dy"].double()).sum().backward()
     for t, k in ((x, "dx"), (gamma, "dgamma"), (beta, "dbeta")):
         assert rel_l2(t.grad, g[k]) < 2e-5, k
