@@ -4,6 +4,7 @@
 // length cap.  Four lanes share a (batch, channel) row and split its poles; the per-step output is
 // a two-shuffle reduction.
 #include "common.cuh"
+#include "stream_bwd.cuh"
 #include "stream_cl.cuh"
 
 namespace mega {
@@ -546,6 +547,14 @@ extern "C" int mega_cema_bwd(const void* dy, const void* x, void* dx, int dtype,
       cudaMemsetAsync(dgamma_hat, 0, K * N * 2 * sizeof(float), s) != cudaSuccess ||
       cudaMemsetAsync(domega, 0, (size_t)D * sizeof(float), s) != cudaSuccess)
     return check_launch("cema_bwd(memset)");
+  if (!bidir) {  // channel-contiguous activations: the streamed TMA kernel
+    EmaBwdStreamArgs sa{};
+    sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+    sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.mask = pad_mask;
+    sa.dp = dp; sa.dq = dq; sa.dg = dgamma_hat; sa.domega = domega;
+    if (cema_bwd_stream_try(dtype, dy, x, dx, gsb, gsl, gsd, xsb, xsl, xsd, dsb, dsl, dsd, sa, s))
+      return check_launch("cema_bwd(stream)");
+  }
   CemaBwdArgs a{};
   a.dy = dy; a.x = x; a.dx = dx; a.B = B; a.D = D; a.L = L; a.N = N;
   a.gsb = gsb; a.gsd = gsd; a.gsl = gsl; a.xsb = xsb; a.xsd = xsd; a.xsl = xsl;

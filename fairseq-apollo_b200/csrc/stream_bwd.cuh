@@ -30,6 +30,11 @@ bool tsn_bwd_stream_try(int dtype, const void* dy, const void* x, void* dx, long
 bool ema_bwd_stream_try(int dtype, const void* dy, const void* x, void* dx, long long gsb, long long gsl,
                         long long gsd, long long xsb, long long xsl, long long xsd, long long dsb, long long dsl,
                         long long dsd, const EmaBwdStreamArgs& a, cudaStream_t s);
+// Complex layer: q, g of the arguments are interleaved (re, im) (D, N, 2), dq / dg likewise; h_in,
+// dh_out, dh_in are not used.
+bool cema_bwd_stream_try(int dtype, const void* dy, const void* x, void* dx, long long gsb, long long gsl,
+                         long long gsd, long long xsb, long long xsl, long long xsd, long long dsb, long long dsl,
+                         long long dsd, const EmaBwdStreamArgs& a, cudaStream_t s);
 cudaError_t stream_bwd_read_device_error(int* v, bool reset);
 
 }  // namespace mega

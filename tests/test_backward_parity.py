@@ -47,7 +47,9 @@ def test_ema_golden(name):
 
 @pytest.mark.parametrize("bsz,dim,length,ndim,bidir,shift", [
     (1, 1, 1, 16, False, True), (2, 7, 33, 16, False, True), (3, 5, 130, 2, False, True),
-    (2, 9, 65, 32, False, True), (2, 6, 40, 16, True, True), (2, 3, 31, 5, True, False), (9, 33, 17, 1, True, True)])
+    (2, 9, 65, 32, False, True), (2, 6, 40, 16, True, True), (2, 3, 31, 5, True, False), (9, 33, 17, 1, True, True),
+    # channel counts the streamed (TMA) backward kernel accepts: rows of 16-byte multiples
+    (2, 16, 70, 16, False, True), (3, 72, 257, 3, False, True), (2, 136, 33, 16, False, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_ema_grid(bsz, dim, length, ndim, bidir, shift, dtype):
     """Module autograd against autograd through the fp64 recurrence; interior pads; x given as the
@@ -75,12 +77,14 @@ def test_ema_grid(bsz, dim, length, ndim, bidir, shift, dtype):
         assert rel_l2(t.grad, r.grad) < tol_p, k
 
 
-def test_ema_state_gradients():
+@pytest.mark.parametrize("dim,channel_contiguous", [(6, False), (16, True)])
+def test_ema_state_gradients(dim, channel_contiguous):
     """Carried state in, state out: gradients w.r.t. the incoming state and through the returned
-    one (operator level; the module keeps states out of autograd)."""
+    one (operator level; the module keeps states out of autograd); the generic kernel and, on
+    (B, L, D) memory, the streamed one."""
     M, O = _mods()
     gen = torch.Generator().manual_seed(5)
-    bsz, dim, length, ndim = 2, 6, 29, 16
+    bsz, length, ndim = 2, 29, 16
     params = make_ema_params(gen, dim, ndim)
     x = torch.randn(bsz, dim, length, generator=gen)
     h0 = torch.randn(bsz, dim, ndim, generator=gen) * 0.3
@@ -101,7 +105,11 @@ def test_ema_state_gradients():
         st = qr * st + pr * xs[:, :, t:t + 1]
         tot = tot + ((st * gr).sum(-1) * dy[:, :, t].double()).sum()
     (tot + (st * dh.double()).sum()).backward()
-    dx, dp, dq, dg, dom, dh_in = M.ops.ema_backward(dy.cuda(), x.cuda(), p.float().cuda(), q.float().cuda(),
+    xd, dyd = x.cuda(), dy.cuda()
+    if channel_contiguous:  # (B, D, L) views of (B, L, D) memory
+        xd = xd.transpose(1, 2).contiguous().transpose(1, 2)
+        dyd = dyd.transpose(1, 2).contiguous().transpose(1, 2)
+    dx, dp, dq, dg, dom, dh_in = M.ops.ema_backward(dyd, xd, p.float().cuda(), q.float().cuda(),
                                                     g.float().cuda(), params[4].cuda(), mask.cuda(), h0.cuda(),
                                                     dh.cuda(), want_dh_in=True)
     assert rel_l2(dx, xr.grad) < 2e-5
@@ -265,7 +273,8 @@ def test_complex_ema_golden(name):
 
 @pytest.mark.parametrize("bsz,dim,length,ndim,bidir,shift", [(2, 7, 33, 16, False, True), (3, 5, 130, 2, False, True),
                                                              (2, 9, 65, 32, False, True), (2, 6, 40, 16, True, True),
-                                                             (2, 3, 31, 5, True, False)])
+                                                             (2, 3, 31, 5, True, False), (2, 16, 70, 16, False, True),
+                                                             (3, 72, 257, 3, False, True), (2, 136, 33, 11, False, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_complex_ema_grid(bsz, dim, length, ndim, bidir, shift, dtype):
     M, O = _mods()
