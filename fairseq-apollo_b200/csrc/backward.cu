@@ -619,6 +619,13 @@ extern "C" int mega_timestep_norm_bwd(const void* dy, const void* x, void* dx, i
       else launch(tsn_bwd_plain_kernel<T, false>, grid, 128, 0, stream, a);
     });
   } else {
+    GroupStreamBwdArgs ga{};
+    ga.B = B; ga.L = L; ga.D = D; ga.G = G; ga.dmean = dmean; ga.dvar = dvar; ga.prev_mean = prev_mean;
+    ga.count = (const long long*)count; ga.cummean = cummean; ga.cumrstd = cumrstd; ga.group_mean = group_mean;
+    ga.gamma = gamma; ga.mask = pad_mask;
+    ga.dprev_mean = dprev_mean; ga.dprev_var = dprev_var; ga.dgamma = dgamma; ga.dbeta = dbeta;
+    if (tsn_group_bwd_stream_try(dtype, dy, x, dx, gsb, gsl, gsd, xsb, xsl, xsd, dsb, dsl, dsd, ga, s))
+      return check_launch("timestep_norm_bwd(group stream)");
     const unsigned grid = (unsigned)(((long long)B * G * 32 + 127) / 128);
     MEGA_DISPATCH_DTYPE(dtype, launch(tsn_bwd_group_kernel<T>, grid, 128, 0, stream, a));
   }

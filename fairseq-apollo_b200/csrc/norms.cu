@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "stream_bwd.cuh"
 #include "stream_cl.cuh"
 
 namespace mega {
@@ -374,6 +375,13 @@ static int tsn_fwd_common(const void* x, void* y, int dtype, int B, int L, int D
       else launch(tsn_plain_kernel<T, false, false>, grid, 128, 0, stream, a);
     });
   } else {
+    GroupStreamArgs ga{};
+    ga.B = B; ga.L = L; ga.D = D; ga.G = G;
+    ga.prev_count = a.prev_count; ga.prev_mean = prev_mean; ga.prev_var = prev_var; ga.gamma = gamma; ga.beta = beta;
+    ga.mask = pad_mask; ga.eps = (float)eps; ga.count_out = a.count_out; ga.mean_out = mean_out; ga.var_out = var_out;
+    ga.cummean = cummean; ga.cumrstd = cumrstd; ga.group_mean = group_mean;
+    if (tsn_group_stream_try(dtype, x, y, xsb, xsl, xsd, ysb, ysl, ysd, ga, (cudaStream_t)stream))
+      return check_launch("timestep_norm_fwd(group stream)");
     const unsigned grid = (unsigned)(((long long)B * G * 32 + 127) / 128);
     MEGA_DISPATCH_DTYPE(dtype, launch(tsn_group_kernel<T>, grid, 128, 0, stream, a));
   }

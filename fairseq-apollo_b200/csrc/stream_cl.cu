@@ -445,6 +445,8 @@ extern "C" MEGA_API int mega_debug_device_error(int* host_value, int reset) {
   int v3 = 0;
   if (mega::stream_bwd_read_device_error(&v3, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
   v2 |= v3;
+  if (mega::stream_group_read_device_error(&v3, reset != 0) != cudaSuccess) return mega::check_launch("device_error");
+  v2 |= v3;
   *host_value = v | v2;
   return MEGA_OK;
 }

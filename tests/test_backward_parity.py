@@ -139,7 +139,8 @@ def test_tsn_golden(name):
 
 
 @pytest.mark.parametrize("bsz,length,feat,groups", [(1, 1, 1, None), (2, 130, 33, None), (9, 17, 128, None),
-                                                     (2, 50, 64, 4), (3, 33, 96, 3), (2, 20, 70, 1)])
+                                                     (2, 50, 64, 4), (3, 33, 96, 3), (2, 20, 70, 1),
+                                                     (2, 70, 128, 16), (2, 257, 128, 2), (3, 100, 192, 6)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_tsn_module_grid(bsz, length, feat, groups, dtype):
     """Module autograd (prior statistics, weight, bias and x) against autograd through the fp64

@@ -32,7 +32,8 @@ def test_tsn_golden(name):
 
 
 @pytest.mark.parametrize("bsz,length,feat,groups", [(1, 1, 1, None), (2, 300, 33, None), (9, 17, 128, None),
-                                                     (2, 50, 64, 4), (3, 33, 96, 3), (2, 20, 70, 1)])
+                                                     (2, 50, 64, 4), (3, 33, 96, 3), (2, 20, 70, 1),
+                                                     (2, 70, 128, 16), (2, 257, 128, 2), (3, 100, 192, 6)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_tsn_grid(bsz, length, feat, groups, dtype):
     M, O = _mods()
