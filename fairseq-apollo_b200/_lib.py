@@ -51,6 +51,8 @@ SIGNATURES = {
     "mega_cema_step": [c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_u, c_p],
     "mega_cema_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 4 + [c_i, c_p, c_u, c_i] + [c_p] * 5,
     "mega_cema_coeffs_bwd": [c_p] * 7 + [c_i, c_i] + [c_p] * 5,
+    "mega_attention_softmax_fwd": [c_p, c_p, c_i, c_l, c_l, c_i, c_i, c_p],
+    "mega_attention_softmax_bwd": [c_p, c_p, c_p, c_i, c_l, c_l, c_i, c_i, c_p],
     "mega_tsn_cema_fwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
                           c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
     "mega_set_option": [c_i, c_i],

@@ -624,3 +624,33 @@ def cema_coeffs_bwd(alpha, delta, theta, q, dp, dq, dg):
                                                    dd.data_ptr(), dt.data_ptr(), dgm.data_ptr(), _stream()),
                    "cema_coeffs_bwd")
     return da.unsqueeze(-1), dd.unsqueeze(-1), dt.view(k, 1, 1), dgm
+
+
+# ----------------------------------------------------------------------- attention
+def attention_softmax_fwd(x, causal=True):
+    """softmax over the last axis of the score tensor x (..., C_q, C_k); with ``causal`` row r keeps
+    its first C_k - C_q + r + 1 columns (the rest is 0).  A row of -inf scores gives zeros."""
+    _cuda(x)
+    xc = x.contiguous()
+    outer, inner = xc.shape[-2], xc.shape[-1]
+    batch = xc.numel() // (outer * inner)
+    y = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_attention_softmax_fwd(xc.data_ptr(), y.data_ptr(), _dt(xc), batch, outer, inner,
+                                                         1 if causal else 0, _stream()), "attention_softmax_fwd")
+    return y
+
+
+def attention_softmax_bwd(dy, y, causal=True):
+    """Gradient of attention_softmax_fwd with respect to the scores."""
+    _cuda(dy, y)
+    yc = y.contiguous()
+    dyc = dy.to(yc.dtype).contiguous()
+    outer, inner = yc.shape[-2], yc.shape[-1]
+    batch = yc.numel() // (outer * inner)
+    dx = torch.empty_like(yc)
+    with torch.cuda.device(y.device):
+        _lib.check(_lib.lib().mega_attention_softmax_bwd(dyc.data_ptr(), yc.data_ptr(), dx.data_ptr(), _dt(yc), batch,
+                                                         outer, inner, 1 if causal else 0, _stream()),
+                   "attention_softmax_bwd")
+    return dx

@@ -385,6 +385,20 @@ MEGA_API int mega_cema_coeffs_bwd(const float* alpha, const float* delta, const 
                          const float* dp, const float* dq, const float* dgamma_hat, int K, int N,
                          float* dalpha, float* ddelta, float* dtheta, float* dgamma, mega_stream_t stream);
 
+/*
+ * Attention-weight softmax of the Mega block.  x, y (and dy, dx) are contiguous (batch, outer, inner)
+ * score tensors; softmax over `inner`; with `causal` row r keeps its first inner - outer + r + 1
+ * columns and the rest of the row is 0; a row whose kept scores are all -inf is all zeros.
+ * inner <= 8192.  DropKey (the reference's stochastic training option) is not implemented.
+ * Replaces: attention_softmax_fwd / attention_softmax_bwd with dropout = 0
+ * (fairseq/csrc/ops/attention_softmax.cc:6-18, fairseq/csrc/softmax.cuh:90-153; called from
+ * fairseq/modules/attention_softmax.py:11-40).
+ */
+MEGA_API int mega_attention_softmax_fwd(const void* x, void* y, int dtype, int64_t batch, int64_t outer, int inner,
+                               int causal, mega_stream_t stream);
+MEGA_API int mega_attention_softmax_bwd(const void* dy, const void* y, void* dx, int dtype, int64_t batch,
+                               int64_t outer, int inner, int causal, mega_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

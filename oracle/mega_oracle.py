@@ -489,3 +489,24 @@ def mega_gate_output(residual, u, hx, h_lin):
     h = silu(hx + h_lin); out = residual + u * (h - residual)."""
     h = torch.nn.functional.silu(hx + h_lin)
     return torch.addcmul(residual, u, h - residual)
+
+
+# --------------------------------------------------------------------------
+# Attention-weight softmax
+# --------------------------------------------------------------------------
+def attention_softmax(x, use_causal_mask=True):
+    """fairseq/csrc/softmax.cuh:90-153 (AttentionSoftmaxFwdKernel): softmax over the last axis of
+    x (..., C_q, C_k); with the causal mask row r keeps its first C_k - C_q + r + 1 columns and the
+    rest of the row is 0; a row whose kept scores are all -inf is all zeros."""
+    outer, inner = x.shape[-2], x.shape[-1]
+    xs = x.double()
+    if use_causal_mask:
+        cols = torch.arange(inner).view(1, inner)
+        keep = cols < (inner - outer + torch.arange(outer).view(outer, 1) + 1)
+        xs = xs.masked_fill(~keep, float("-inf"))
+    m = xs.max(dim=-1, keepdim=True).values
+    dead = torch.isinf(m) & (m < 0)
+    e = torch.exp(xs - torch.where(dead, torch.zeros_like(m), m))
+    e = torch.where(dead.expand_as(e), torch.zeros_like(e), e)
+    d = e.sum(-1, keepdim=True)
+    return torch.where(d == 0, torch.zeros_like(e), e / torch.where(d == 0, torch.ones_like(d), d))
