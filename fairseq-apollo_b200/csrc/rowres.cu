@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tma.cuh"
 #include "rowres.cuh"
 
 namespace mega {
@@ -90,7 +91,16 @@ __device__ __forceinline__ void carry_scan(float (&st)[kRowNP], const float* qro
 template <int kDir, bool kEmit, bool kAccum, bool kPreEmit>
 __device__ __forceinline__ void walk_segment(float* src, float* dst, int base, int seg, const float (&q)[kRowNP],
                                              const float (&c)[kRowNP], float (&st)[kRowNP], float om) {
-  // kDir = +1 left to right, -1 right to left; four positions per shared-memory access
+  // kDir = +1 left to right, -1 right to left; four positions per shared-memory access; two poles
+  // per packed fp32x2 operation (the kernel is bound by issue slots, not by the FMA pipe)
+  constexpr int kH = kRowNP / 2;
+  f32x2 q2[kH], c2[kH], s2[kH];
+#pragma unroll
+  for (int n = 0; n < kH; ++n) {
+    q2[n] = pack2(q[2 * n], q[2 * n + 1]);
+    c2[n] = pack2(c[2 * n], c[2 * n + 1]);
+    s2[n] = pack2(st[2 * n], st[2 * n + 1]);
+  }
   const int nq4 = seg >> 2;
   for (int k4 = 0; k4 < nq4; ++k4) {
     const int off = base + 4 * (kDir > 0 ? k4 : nq4 - 1 - k4);
@@ -105,29 +115,34 @@ __device__ __forceinline__ void walk_segment(float* src, float* dst, int base, i
     for (int u = 0; u < 4; ++u) {
       const int e = kDir > 0 ? u : 3 - u;
       const float xv = xs[e];
+      const f32x2 x2 = pack2(xv, xv);
       if (!kEmit) {
 #pragma unroll
-        for (int n = 0; n < kRowNP; ++n) st[n] = fmaf(q[n], st[n], xv);
+        for (int n = 0; n < kH; ++n) s2[n] = fma2(q2[n], s2[n], x2);
       } else {
-        float a0 = 0.f, a1 = 0.f;
+        f32x2 a0 = pack2(0.f, 0.f), a1 = pack2(0.f, 0.f);
 #pragma unroll
-        for (int n = 0; n < kRowNP; n += 2) {
+        for (int n = 0; n < kH; n += 2) {
           if (kPreEmit) {
-            a0 = fmaf(c[n], st[n], a0);
-            a1 = fmaf(c[n + 1], st[n + 1], a1);
+            a0 = fma2(c2[n], s2[n], a0);
+            a1 = fma2(c2[n + 1], s2[n + 1], a1);
           }
-          st[n] = fmaf(q[n], st[n], xv);
-          st[n + 1] = fmaf(q[n + 1], st[n + 1], xv);
+          s2[n] = fma2(q2[n], s2[n], x2);
+          s2[n + 1] = fma2(q2[n + 1], s2[n + 1], x2);
           if (!kPreEmit) {
-            a0 = fmaf(c[n], st[n], a0);
-            a1 = fmaf(c[n + 1], st[n + 1], a1);
+            a0 = fma2(c2[n], s2[n], a0);
+            a1 = fma2(c2[n + 1], s2[n + 1], a1);
           }
         }
-        ys[e] = kAccum ? ys[e] + (a0 + a1) : fmaf(om, xv, a0 + a1);
+        float lo, hi;
+        unpack2(add2(a0, a1), lo, hi);
+        ys[e] = kAccum ? ys[e] + (lo + hi) : fmaf(om, xv, lo + hi);
       }
     }
     if (kEmit) *reinterpret_cast<float4*>(dst + off) = make_float4(ys[0], ys[1], ys[2], ys[3]);
   }
+#pragma unroll
+  for (int n = 0; n < kH; ++n) unpack2(s2[n], st[2 * n], st[2 * n + 1]);
 }
 
 template <typename T, bool kBidir, bool kNorm, int kT>
