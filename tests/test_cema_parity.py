@@ -112,7 +112,8 @@ def test_chunked_equals_full_with_masks():
     assert rel_l2(torch.cat(parts, -1), full) < 1e-5
 
 
-@pytest.mark.parametrize("bsz,length,dim,ndim", [(2, 70, 24, 16), (3, 257, 72, 3), (2, 64, 8, 16), (2, 40, 20, 32)])
+@pytest.mark.parametrize("bsz,length,dim,ndim", [(2, 70, 24, 16), (3, 257, 72, 3), (2, 64, 8, 16), (2, 40, 20, 32),
+                                                 (50, 40, 1024, 16)])   # the last: one thread per channel
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_fused_timestep_norm_complex_ema(bsz, length, dim, ndim, dtype):
     """TimestepNorm -> complex EMA (+ SiLU) through the fused helper: one streamed kernel when

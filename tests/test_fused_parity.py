@@ -91,7 +91,8 @@ def test_config1_reduced_bf16():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("bsz,length,dim", [(2, 1, 8), (3, 31, 72), (2, 32, 64), (2, 33, 136), (1, 1000, 200), (5, 257, 8)])
+@pytest.mark.parametrize("bsz,length,dim", [(2, 1, 8), (3, 31, 72), (2, 32, 64), (2, 33, 136), (1, 1000, 200), (5, 257, 8),
+                                            (50, 40, 1024)])   # the last: enough rows for one thread per channel
 def test_streamed_path_matches_generic(dtype, bsz, length, dim):
     """The TMA-streamed kernels and the generic kernels are two implementations of the same
     entry points: run both (a test switch disables the streamed one) on shapes inside the
