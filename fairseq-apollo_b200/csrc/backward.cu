@@ -24,11 +24,17 @@ struct EmaBwdArgs {
   const float *h_in, *dh_out;
   float *dp, *dq, *dg, *domega, *dh_in;
   int bidir, shift;
+  int ksize;  // kTrunc: support of the truncated kernel (taps 0 .. ksize - 1)
 };
 
 // kMask: whether a padding mask is given (a run-time pointer test inside the unrolled load
 // batches would serialise their loads).
-template <typename T, int NP, bool kMask>
+// kTrunc: the kernel is cut after ksize taps.  The states then are sliding-window sums: with
+// Q = q^ksize the sample leaving the window is taken out again,
+//   h_t = q h_{t-1} + p (x~_t - Q x~_{t-ksize}),   r_t = q r_{t-1} + x~_t - Q x~_{t-ksize},
+//   s_t = q s_{t-1} + h_{t-1} - p ksize q^(ksize-1) x~_{t-ksize},
+//   lambda_t = q lambda_{t+1} + g (dy_t - Q dy_{t+ksize}).
+template <typename T, int NP, bool kMask, bool kTrunc>
 __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
   constexpr int U = 8;
   const int sub = threadIdx.x & 3;
@@ -50,6 +56,7 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
     const size_t prow = (size_t)(d + half * a.D) * a.N;
     const size_t srow = ((size_t)b * a.D + d) * a.N;
     float pp[NP], qq[NP], gg[NP], h[NP], s[NP], r[NP], ag[NP], aq[NP], ap[NP];
+    float qw[kTrunc ? NP : 1], tq[kTrunc ? NP : 1];  // q^ksize, p ksize q^(ksize-1)
 #pragma unroll
     for (int k = 0; k < NP; ++k) {
       const int n = k * 4 + sub;
@@ -57,22 +64,32 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
       pp[k] = ok ? __ldg(a.p + prow + n) : 0.f;
       qq[k] = ok ? __ldg(a.q + prow + n) : 0.f;
       gg[k] = ok ? __ldg(a.g + prow + n) : 0.f;
+      if (kTrunc) {
+        const float qm1 = qq[k] > 0.f ? expf((float)(a.ksize - 1) * logf(qq[k])) : 0.f;
+        qw[k] = qm1 * qq[k];
+        tq[k] = pp[k] * (float)a.ksize * qm1;
+      }
       h[k] = (ok && live && half == 0 && a.h_in) ? __ldg(a.h_in + srow + n) : 0.f;
       s[k] = r[k] = ag[k] = aq[k] = ap[k] = 0.f;
     }
     // ---- forward in (possibly reversed) time: states, sensitivities, parameter sums -------
     for (int u0 = 0; u0 < L; u0 += U) {
-      float xv[U], gv[U];
+      float xv[U], gv[U], xd[kTrunc ? U : 1];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         const int u = u0 + j;
         xv[j] = gv[j] = 0.f;
+        if (kTrunc) xd[j] = 0.f;
         if (u < L && live) {
           const int t = rev ? L - 1 - u : u;
           const float xt = Elem<T>::ld(xp + t * a.xsl);
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
           if (half == 0) aw = fmaf(gv[j], xt, aw);
           xv[j] = (kMask && __ldg(mp + t) != 0) ? 0.f : xt;
+          if (kTrunc && u >= a.ksize) {  // the sample leaving the window
+            const int td = rev ? t + a.ksize : t - a.ksize;
+            if (!(kMask && __ldg(mp + td) != 0)) xd[j] = Elem<T>::ld(xp + td * a.xsl);
+          }
         }
       }
 #pragma unroll
@@ -85,9 +102,16 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
               aq[k] = fmaf(gv[j], s[k], aq[k]);
               ap[k] = fmaf(gv[j], r[k], ap[k]);
             }
-            s[k] = fmaf(qq[k], s[k], h[k]);
-            h[k] = fmaf(qq[k], h[k], pp[k] * xv[j]);
-            r[k] = fmaf(qq[k], r[k], xv[j]);
+            if (kTrunc) {
+              const float xin = fmaf(-qw[k], xd[j], xv[j]);
+              s[k] = fmaf(qq[k], s[k], fmaf(-tq[k], xd[j], h[k]));
+              h[k] = fmaf(qq[k], h[k], pp[k] * xin);
+              r[k] = fmaf(qq[k], r[k], xin);
+            } else {
+              s[k] = fmaf(qq[k], s[k], h[k]);
+              h[k] = fmaf(qq[k], h[k], pp[k] * xv[j]);
+              r[k] = fmaf(qq[k], r[k], xv[j]);
+            }
             if (!shift) {
               ag[k] = fmaf(gv[j], h[k], ag[k]);
               aq[k] = fmaf(gv[j], s[k], aq[k]);
@@ -112,16 +136,18 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
     }
     // ---- backward in time: input gradient ---------------------------------------------------
     for (int u0 = L - 1; u0 >= 0; u0 -= U) {
-      float gv[U], old[U];
+      float gv[U], old[U], gd[kTrunc ? U : 1];
       bool mk[U];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         const int u = u0 - j;
         gv[j] = old[j] = 0.f;
+        if (kTrunc) gd[j] = 0.f;
         mk[j] = false;
         if (u >= 0 && live) {
           const int t = rev ? L - 1 - u : u;
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
+          if (kTrunc && u + a.ksize < L) gd[j] = Elem<T>::ld(gp + (rev ? t - a.ksize : t + a.ksize) * a.gsl);
           mk[j] = kMask && __ldg(mp + t) != 0;
           if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(dxp + t * a.dsl);  // plain load: written above
         }
@@ -133,11 +159,12 @@ __global__ void __launch_bounds__(128) ema_bwd_kernel(EmaBwdArgs a) {
           float part = 0.f;
 #pragma unroll
           for (int k = 0; k < NP; ++k) {
+            const float gin = kTrunc ? fmaf(-qw[k], gd[j], gv[j]) : gv[j];
             if (shift) {
               part = fmaf(pp[k], lam[k], part);
-              lam[k] = fmaf(qq[k], lam[k], gg[k] * gv[j]);
+              lam[k] = fmaf(qq[k], lam[k], gg[k] * gin);
             } else {
-              const float l = fmaf(gg[k], gv[j], lam[k]);
+              const float l = fmaf(gg[k], gin, lam[k]);
               part = fmaf(pp[k], l, part);
               lam[k] = qq[k] * l;
             }
@@ -521,7 +548,8 @@ extern "C" int mega_ema_bwd(const void* dy, const void* x, void* dx, int dtype, 
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
   const bool bidir = (flags & MEGA_EMA_BIDIRECTIONAL) != 0;
   if (flags & MEGA_EMA_SILU) return MEGA_ERR_UNSUPPORTED;  // differentiate the activation outside
-  if (truncation > 0 && truncation < L) return MEGA_ERR_UNSUPPORTED;
+  const bool trunc = truncation > 0 && truncation < L;
+  if (trunc && !bidir) return MEGA_ERR_UNSUPPORTED;  // as the forward: one direction is never truncated
   if (bidir && (h_in || dh_out || dh_in)) return MEGA_ERR_UNSUPPORTED;
   const size_t es = elem_size(dtype);
   if (!aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(dx, es)) return MEGA_ERR_ALIGN;
@@ -548,11 +576,15 @@ extern "C" int mega_ema_bwd(const void* dy, const void* x, void* dx, int dtype, 
   a.dp = dp; a.dq = dq; a.dg = dgamma_hat; a.domega = domega; a.dh_in = dh_in;
   a.bidir = bidir ? 1 : 0;
   a.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
+  a.ksize = trunc ? truncation : L;
   const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
   const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
-#define MEGA_EMA_BWD(NPV)                                                         \
-  if (pad_mask) launch(ema_bwd_kernel<T, NPV, true>, grid, 128, 0, stream, a);     \
-  else launch(ema_bwd_kernel<T, NPV, false>, grid, 128, 0, stream, a)
+#define MEGA_EMA_BWD(NPV)                                                                 \
+  if (trunc) {                                                                            \
+    if (pad_mask) launch(ema_bwd_kernel<T, NPV, true, true>, grid, 128, 0, stream, a);     \
+    else launch(ema_bwd_kernel<T, NPV, false, true>, grid, 128, 0, stream, a);             \
+  } else if (pad_mask) launch(ema_bwd_kernel<T, NPV, true, false>, grid, 128, 0, stream, a); \
+  else launch(ema_bwd_kernel<T, NPV, false, false>, grid, 128, 0, stream, a)
   MEGA_DISPATCH_DTYPE(dtype, {
     if (np == 1) { MEGA_EMA_BWD(1); }
     else if (np == 2) { MEGA_EMA_BWD(2); }

@@ -230,9 +230,13 @@ struct CemaBwdArgs {
   const unsigned char* mask;
   float *dp, *dq, *dg, *domega;
   int bidir, shift;
+  int ksize;  // kTrunc: support of the truncated kernel
 };
 
-template <typename T, int NP, bool kMask>
+// kTrunc: sliding-window states as in the real layer's backward kernel, with complex
+// Q = q^ksize: h, r take x~_t - Q x~_{t-ksize}, s loses p ksize q^(ksize-1) x~_{t-ksize}, and
+// lambda takes g dy_t - (g Q) dy_{t+ksize}.
+template <typename T, int NP, bool kMask, bool kTrunc>
 __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
   constexpr int U = 8;
   const int sub = threadIdx.x & 3;
@@ -255,6 +259,8 @@ __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
     float pp[NP], qr[NP], qi[NP], gr[NP], gi[NP];
     float hr[NP], hi[NP], sr[NP], si[NP], rr[NP], ri[NP];
     float ahr[NP], ahi[NP], asr[NP], asi[NP], arr[NP], ari[NP];
+    constexpr int NT = kTrunc ? NP : 1;
+    float qwr[NT], qwi[NT], tqr[NT], tqi[NT], gqr[NT], gqi[NT];  // Q, p ksize q^(ksize-1), g Q
 #pragma unroll
     for (int k = 0; k < NP; ++k) {
       const int n = k * 4 + sub;
@@ -264,27 +270,50 @@ __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
       qi[k] = ok ? __ldg(a.q + 2 * (prow + n) + 1) : 0.f;
       gr[k] = ok ? __ldg(a.g + 2 * (prow + n)) : 0.f;
       gi[k] = ok ? __ldg(a.g + 2 * (prow + n) + 1) : 0.f;
+      if (kTrunc) {
+        const float rho = hypotf(qr[k], qi[k]);
+        float m1r = 0.f, m1i = 0.f;  // q^(ksize-1)
+        if (rho > 0.f) {
+          const float mag = expf((float)(a.ksize - 1) * logf(rho));
+          float sn, cs;
+          sincosf((float)(a.ksize - 1) * atan2f(qi[k], qr[k]), &sn, &cs);
+          m1r = mag * cs;
+          m1i = mag * sn;
+        }
+        qwr[k] = m1r * qr[k] - m1i * qi[k];
+        qwi[k] = m1r * qi[k] + m1i * qr[k];
+        tqr[k] = pp[k] * (float)a.ksize * m1r;
+        tqi[k] = pp[k] * (float)a.ksize * m1i;
+        gqr[k] = gr[k] * qwr[k] - gi[k] * qwi[k];
+        gqi[k] = gr[k] * qwi[k] + gi[k] * qwr[k];
+      }
       hr[k] = hi[k] = sr[k] = si[k] = rr[k] = ri[k] = 0.f;
       ahr[k] = ahi[k] = asr[k] = asi[k] = arr[k] = ari[k] = 0.f;
     }
     for (int u0 = 0; u0 < L; u0 += U) {
-      float xv[U], gv[U];
+      float xv[U], gv[U], xd[kTrunc ? U : 1];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         const int u = u0 + j;
         xv[j] = gv[j] = 0.f;
+        if (kTrunc) xd[j] = 0.f;
         if (u < L && live) {
           const int t = rev ? L - 1 - u : u;
           const float xt = Elem<T>::ld(xp + t * a.xsl);
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
           if (half == 0) aw = fmaf(gv[j], xt, aw);
           xv[j] = (kMask && __ldg(mp + t) != 0) ? 0.f : xt;
+          if (kTrunc && u >= a.ksize) {  // the sample leaving the window
+            const int td = rev ? t + a.ksize : t - a.ksize;
+            if (!(kMask && __ldg(mp + td) != 0)) xd[j] = Elem<T>::ld(xp + td * a.xsl);
+          }
         }
       }
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         if (u0 + j < L) {
           const float dy = gv[j], xm = xv[j];
+          const float xo = kTrunc ? xd[j] : 0.f;
 #pragma unroll
           for (int k = 0; k < NP; ++k) {
             if (shift) {
@@ -292,12 +321,20 @@ __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
               asr[k] = fmaf(dy, sr[k], asr[k]); asi[k] = fmaf(dy, si[k], asi[k]);
               arr[k] = fmaf(dy, rr[k], arr[k]); ari[k] = fmaf(dy, ri[k], ari[k]);
             }
-            const float nsr = fmaf(qr[k], sr[k], fmaf(-qi[k], si[k], hr[k]));
-            const float nsi = fmaf(qi[k], sr[k], fmaf(qr[k], si[k], hi[k]));
-            const float nhr = fmaf(qr[k], hr[k], fmaf(-qi[k], hi[k], pp[k] * xm));
-            const float nhi = fmaf(qi[k], hr[k], qr[k] * hi[k]);
-            const float nrr = fmaf(qr[k], rr[k], fmaf(-qi[k], ri[k], xm));
-            const float nri = fmaf(qi[k], rr[k], qr[k] * ri[k]);
+            float nsr = fmaf(qr[k], sr[k], fmaf(-qi[k], si[k], hr[k]));
+            float nsi = fmaf(qi[k], sr[k], fmaf(qr[k], si[k], hi[k]));
+            float nhr = fmaf(qr[k], hr[k], fmaf(-qi[k], hi[k], pp[k] * xm));
+            float nhi = fmaf(qi[k], hr[k], qr[k] * hi[k]);
+            float nrr = fmaf(qr[k], rr[k], fmaf(-qi[k], ri[k], xm));
+            float nri = fmaf(qi[k], rr[k], qr[k] * ri[k]);
+            if (kTrunc) {
+              nsr = fmaf(-tqr[k], xo, nsr);
+              nsi = fmaf(-tqi[k], xo, nsi);
+              nhr = fmaf(-pp[k] * qwr[k], xo, nhr);
+              nhi = fmaf(-pp[k] * qwi[k], xo, nhi);
+              nrr = fmaf(-qwr[k], xo, nrr);
+              nri = fmaf(-qwi[k], xo, nri);
+            }
             sr[k] = nsr; si[k] = nsi; hr[k] = nhr; hi[k] = nhi; rr[k] = nrr; ri[k] = nri;
             if (!shift) {
               ahr[k] = fmaf(dy, nhr, ahr[k]); ahi[k] = fmaf(dy, nhi, ahi[k]);
@@ -322,16 +359,18 @@ __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
       }
     }
     for (int u0 = L - 1; u0 >= 0; u0 -= U) {
-      float gv[U], old[U];
+      float gv[U], old[U], gd[kTrunc ? U : 1];
       bool mk[U];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         const int u = u0 - j;
         gv[j] = old[j] = 0.f;
+        if (kTrunc) gd[j] = 0.f;
         mk[j] = false;
         if (u >= 0 && live) {
           const int t = rev ? L - 1 - u : u;
           gv[j] = Elem<T>::ld(gp + t * a.gsl);
+          if (kTrunc && u + a.ksize < L) gd[j] = Elem<T>::ld(gp + (rev ? t - a.ksize : t + a.ksize) * a.gsl);
           mk[j] = kMask && __ldg(mp + t) != 0;
           if (half == 1 && sub == 0) old[j] = Elem<T>::ld_shared(dxp + t * a.dsl);  // written by the first half
         }
@@ -343,13 +382,19 @@ __global__ void __launch_bounds__(128) cema_bwd_kernel(CemaBwdArgs a) {
           float part = 0.f;
 #pragma unroll
           for (int k = 0; k < NP; ++k) {
+            // g dy_t (- g Q dy_{t+ksize})
+            float inr = gr[k] * gv[j], ini = gi[k] * gv[j];
+            if (kTrunc) {
+              inr = fmaf(-gqr[k], gd[j], inr);
+              ini = fmaf(-gqi[k], gd[j], ini);
+            }
             if (shift) {
               part = fmaf(pp[k], lr[k], part);
-              const float nr = fmaf(qr[k], lr[k], fmaf(-qi[k], li[k], gr[k] * gv[j]));
-              const float ni = fmaf(qi[k], lr[k], fmaf(qr[k], li[k], gi[k] * gv[j]));
+              const float nr = fmaf(qr[k], lr[k], fmaf(-qi[k], li[k], inr));
+              const float ni = fmaf(qi[k], lr[k], fmaf(qr[k], li[k], ini));
               lr[k] = nr; li[k] = ni;
             } else {
-              const float cr = fmaf(gr[k], gv[j], lr[k]), ci = fmaf(gi[k], gv[j], li[k]);
+              const float cr = lr[k] + inr, ci = li[k] + ini;
               part = fmaf(pp[k], cr, part);
               lr[k] = qr[k] * cr - qi[k] * ci;
               li[k] = qi[k] * cr + qr[k] * ci;
@@ -536,7 +581,8 @@ extern "C" int mega_cema_bwd(const void* dy, const void* x, void* dx, int dtype,
   if (B <= 0 || D <= 0 || L <= 0) return MEGA_ERR_SHAPE;
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
   if (flags & MEGA_EMA_SILU) return MEGA_ERR_UNSUPPORTED;
-  if (truncation > 0 && truncation < L) return MEGA_ERR_UNSUPPORTED;
+  const bool trunc = truncation > 0 && truncation < L;
+  if (trunc && !(flags & MEGA_EMA_BIDIRECTIONAL)) return MEGA_ERR_UNSUPPORTED;  // as the forward
   const size_t es = elem_size(dtype);
   if (!aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(dx, es)) return MEGA_ERR_ALIGN;
   const bool bidir = (flags & MEGA_EMA_BIDIRECTIONAL) != 0;
@@ -563,11 +609,15 @@ extern "C" int mega_cema_bwd(const void* dy, const void* x, void* dx, int dtype,
   a.dp = dp; a.dq = dq; a.dg = dgamma_hat; a.domega = domega;
   a.bidir = bidir ? 1 : 0;
   a.shift = (flags & MEGA_EMA_NO_SHIFT) ? 0 : 1;
+  a.ksize = trunc ? truncation : L;
   const unsigned grid = (unsigned)(((long long)B * D + 31) / 32);
   const int np = N <= 4 ? 1 : N <= 8 ? 2 : N <= 16 ? 4 : 8;
 #define MEGA_CEMA_BWD(NPV)                                                          \
-  if (pad_mask) launch(cema_bwd_kernel<T, NPV, true>, grid, 128, 0, stream, a);      \
-  else launch(cema_bwd_kernel<T, NPV, false>, grid, 128, 0, stream, a)
+  if (trunc) {                                                                             \
+    if (pad_mask) launch(cema_bwd_kernel<T, NPV, true, true>, grid, 128, 0, stream, a);     \
+    else launch(cema_bwd_kernel<T, NPV, false, true>, grid, 128, 0, stream, a);             \
+  } else if (pad_mask) launch(cema_bwd_kernel<T, NPV, true, false>, grid, 128, 0, stream, a); \
+  else launch(cema_bwd_kernel<T, NPV, false, false>, grid, 128, 0, stream, a)
   MEGA_DISPATCH_DTYPE(dtype, {
     if (np == 1) { MEGA_CEMA_BWD(1); }
     else if (np == 2) { MEGA_CEMA_BWD(2); }

@@ -17,22 +17,23 @@ class EMAFunction(torch.autograd.Function):
     the chain rule to (alpha, delta, beta, gamma)."""
 
     @staticmethod
-    def forward(ctx, x, alpha, delta, beta, gamma, omega, padding_mask, bidirectional, shift):
+    def forward(ctx, x, alpha, delta, beta, gamma, omega, padding_mask, bidirectional, shift, truncation=None):
         p, q, g = ops.ema_coeffs(alpha, delta, beta, gamma)
         y = ops.ema_forward(x, p, q, g, omega, padding_mask, None, False, bidirectional=bidirectional,
-                            shift=shift)
+                            shift=shift, truncation=truncation)
         ctx.save_for_backward(x, alpha, delta, beta, omega, padding_mask, p, q, g)
-        ctx.bidirectional, ctx.shift = bidirectional, shift
+        ctx.bidirectional, ctx.shift, ctx.truncation = bidirectional, shift, truncation
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, alpha, delta, beta, omega, padding_mask, p, q, g = ctx.saved_tensors
         dx, dp, dq, dg, dom, _ = ops.ema_backward(dy, x, p, q, g, omega, padding_mask,
-                                                  bidirectional=ctx.bidirectional, shift=ctx.shift)
+                                                  bidirectional=ctx.bidirectional, shift=ctx.shift,
+                                                  truncation=ctx.truncation)
         da, dd, db, dgm = ops.ema_coeffs_bwd(alpha, delta, beta, dp, dq, dg)
         return (dx, da.to(alpha.dtype), dd.to(delta.dtype), db.to(beta.dtype), dgm.to(alpha.dtype),
-                dom.to(omega.dtype), None, None, None)
+                dom.to(omega.dtype), None, None, None, None)
 
 
 class ComplexEMAFunction(torch.autograd.Function):
@@ -40,11 +41,12 @@ class ComplexEMAFunction(torch.autograd.Function):
     gamma (K, N, 2), omega (D, 1) as in MultiHeadComplexEMA."""
 
     @staticmethod
-    def forward(ctx, x, alpha, delta, theta, gamma, omega, padding_mask, bidirectional, shift):
+    def forward(ctx, x, alpha, delta, theta, gamma, omega, padding_mask, bidirectional, shift, truncation=None):
         p, q, g = ops.cema_coeffs(alpha, delta, theta, gamma)
-        y = ops.cema_forward(x, p, q, g, omega, padding_mask, None, False, bidirectional=bidirectional, shift=shift)
+        y = ops.cema_forward(x, p, q, g, omega, padding_mask, None, False, bidirectional=bidirectional, shift=shift,
+                             truncation=truncation)
         ctx.save_for_backward(x, alpha, delta, theta, omega, padding_mask, p, q, g)
-        ctx.bidirectional, ctx.shift = bidirectional, shift
+        ctx.bidirectional, ctx.shift, ctx.truncation = bidirectional, shift, truncation
         ctx.gamma_dtype = gamma.dtype
         return y
 
@@ -52,10 +54,11 @@ class ComplexEMAFunction(torch.autograd.Function):
     def backward(ctx, dy):
         x, alpha, delta, theta, omega, padding_mask, p, q, g = ctx.saved_tensors
         dx, dp, dq, dg, dom = ops.cema_backward(dy, x, p, q, g, omega, padding_mask,
-                                                bidirectional=ctx.bidirectional, shift=ctx.shift)
+                                                bidirectional=ctx.bidirectional, shift=ctx.shift,
+                                                truncation=ctx.truncation)
         da, dd, dt, dgm = ops.cema_coeffs_bwd(alpha, delta, theta, q, dp, dq, dg)
         return (dx, da.to(alpha.dtype), dd.to(delta.dtype), dt.to(theta.dtype), dgm.to(ctx.gamma_dtype),
-                dom.view_as(omega).to(omega.dtype), None, None, None)
+                dom.view_as(omega).to(omega.dtype), None, None, None, None)
 
 
 class TimestepNormFunction(torch.autograd.Function):

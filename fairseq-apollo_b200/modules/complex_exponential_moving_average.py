@@ -7,7 +7,7 @@ Same constructor, parameters (alpha, delta (K, N, 1); theta (K, 1, 1); gamma (K,
 ``"ema_state"/{"prev_state"}`` buffer holding a complex64 (B, D, N) state, ``coeffs``, ``kernel``,
 ``step``, ``one_step``, ``parameters_no_weight_decay`` and ``reorder_incremental_state``.
 With autograd enabled the layer runs through an autograd Function whose forward and backward are
-library kernels (no incremental state and no truncated kernel on that path).
+library kernels (no incremental state on that path).
 """
 import math
 from collections import OrderedDict
@@ -149,10 +149,8 @@ class MultiHeadComplexEMA(IncrementalStateMixin, nn.Module):
             # activation is applied by torch on the result, as the reference's caller does
             if incremental_state is not None:
                 raise NotImplementedError("the incremental state is an inference feature: use torch.no_grad()")
-            if self.truncation is not None and self.truncation >= 1:
-                raise NotImplementedError("the backward kernel does not implement a truncated kernel")
             y = ComplexEMAFunction.apply(x, self.alpha, self.delta, self.theta, self.gamma, self.omega,
-                                         padding_mask, self.bidirectional, self.shift)
+                                         padding_mask, self.bidirectional, self.shift, self.truncation)
             return torch.nn.functional.silu(y) if activation == 'silu' else y
         p, q, g = self.coeffs()
         p, q = p.squeeze(-1), q.squeeze(-1)

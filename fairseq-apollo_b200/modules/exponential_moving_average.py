@@ -163,10 +163,8 @@ class MultiHeadEMA(IncrementalStateMixin, nn.Module):
         activation is applied by torch on the result, as the reference's caller does."""
         if incremental_state is not None:
             raise NotImplementedError("the incremental state is an inference feature: use torch.no_grad()")
-        if self.truncation is not None and self.truncation >= 1:
-            raise NotImplementedError("the backward kernel does not implement a truncated kernel")
         y = EMAFunction.apply(x, self.alpha, self.delta, self.beta, self.gamma, self.omega, padding_mask,
-                              self.bidirectional, self.shift)
+                              self.bidirectional, self.shift, self.truncation)
         return torch.nn.functional.silu(y) if activation == 'silu' else y
 
     def forward_time_major(self, x, padding_mask=None, incremental_state=None, activation=None):

@@ -99,6 +99,10 @@ def ema_bias(q, g, h, length):
     return out
 
 
+def _trunc(truncation):
+    return 0 if truncation is None or truncation < 1 else int(truncation)
+
+
 def ema_forward(x, p, q, g, omega, padding_mask=None, h_in=None, want_state=False,
                 bidirectional=False, shift=True, truncation=None, silu=False, out=None):
     """EMA layer forward on x (B, D, L) with any strides (a transposed view of (B, L, D)
@@ -462,9 +466,10 @@ def sequence_norm_bwd(dy, x, count, mean, rstd, gamma, padding_mask=None, length
 
 
 def ema_backward(dy, x, p, q, g, omega, padding_mask=None, h_in=None, dh_out=None, bidirectional=False,
-                 shift=True, want_dh_in=False):
-    """Gradients of ema_forward (no activation, no truncation) on (B, D, L) tensors with any
-    strides: (dx, dp, dq, dgamma_hat, domega, dh_in or None)."""
+                 shift=True, want_dh_in=False, truncation=None):
+    """Gradients of ema_forward (no activation) on (B, D, L) tensors with any strides:
+    (dx, dp, dq, dgamma_hat, domega, dh_in or None).  ``truncation``: kernel support of a
+    bidirectional layer, as in the forward."""
     _cuda(dy, x, p, q, g, omega, padding_mask, h_in, dh_out)
     bsz, dim, length = x.shape
     if dy.dtype != x.dtype:
@@ -483,7 +488,8 @@ def ema_backward(dy, x, p, q, g, omega, padding_mask=None, h_in=None, dh_out=Non
         _lib.check(_lib.lib().mega_ema_bwd(
             dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *dy.stride(), *x.stride(),
             *dx.stride(), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), _ptr(h_in),
-            _ptr(dh_out), flags, 0, dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(), _ptr(dh_in),
+            _ptr(dh_out), flags, _trunc(truncation), dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(),
+            _ptr(dh_in),
             _stream()), "ema_bwd")
     return dx, dp, dq, dg, dom, dh_in
 
@@ -584,8 +590,8 @@ def cema_step(x, p, q, g, omega, h=None, silu=False):
     return y.view(shape), torch.view_as_complex(h_out)
 
 
-def cema_backward(dy, x, p, q, g, omega, padding_mask=None, bidirectional=False, shift=True):
-    """Gradients of cema_forward (no activation, no truncation, no carried state):
+def cema_backward(dy, x, p, q, g, omega, padding_mask=None, bidirectional=False, shift=True, truncation=None):
+    """Gradients of cema_forward (no activation, no carried state; ``truncation`` as in the forward):
     (dx, dp (K, N), dq (K, N) complex64 = dL/dRe q + i dL/dIm q, dgamma_hat likewise, domega (D))."""
     _cuda(dy, x, p, q, g, omega, padding_mask)
     bsz, dim, length = x.shape
@@ -603,8 +609,8 @@ def cema_backward(dy, x, p, q, g, omega, padding_mask=None, bidirectional=False,
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().mega_cema_bwd(
             dy.data_ptr(), x.data_ptr(), dx.data_ptr(), _dt(x), bsz, dim, length, *dy.stride(), *x.stride(),
-            *dx.stride(), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), flags, 0,
-            dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(), _stream()), "cema_bwd")
+            *dx.stride(), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(), n, _ptr(mask), flags,
+            _trunc(truncation), dp.data_ptr(), dq.data_ptr(), dg.data_ptr(), dom.data_ptr(), _stream()), "cema_bwd")
     return dx, dp, torch.view_as_complex(dq), torch.view_as_complex(dg), dom
 
 

@@ -295,7 +295,8 @@ MEGA_API int mega_sequence_norm_bwd(const void* dy, const void* x, void* dx, int
                            float* dgamma, float* dbeta, mega_stream_t stream);
 
 /*
- * mega_ema_bwd: gradients of mega_ema_fwd (without the SiLU flag and without truncation).
+ * mega_ema_bwd: gradients of mega_ema_fwd (without the SiLU flag; truncation as in the forward:
+ * bidirectional form only).
  * dy, x, dx are (B, D, L) with strides in elements; p, q, gamma_hat are (K, N) with K = D or 2D
  * (bidirectional).  h_in (B, D, N) is the state the forward started from, dh_out the gradient
  * flowing into the state it returned (either may be NULL; causal form only).  Outputs: dx;
@@ -370,8 +371,8 @@ MEGA_API int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, 
                       unsigned flags, mega_stream_t stream);
 
 /*
- * mega_cema_bwd / mega_cema_coeffs_bwd: gradients of mega_cema_fwd (no SiLU flag, no truncation, no
- * carried state), same argument conventions as mega_ema_bwd; dq and dgamma_hat are (K, N, 2) with
+ * mega_cema_bwd / mega_cema_coeffs_bwd: gradients of mega_cema_fwd (no SiLU flag, no carried state;
+ * truncation as in the forward), same argument conventions as mega_ema_bwd; dq and dgamma_hat are (K, N, 2) with
  * the gradients of the real and imaginary parts, dtheta is (K).
  * Replaces: autograd through MultiHeadComplexEMA (ema_parameters_bwd + the FFT convolution backward +
  * _calc_coeffs, complex_exponential_moving_average.py:79-109).

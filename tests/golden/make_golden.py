@@ -5,7 +5,7 @@ Run in a container where the reference checkout is mounted (default
 ``oracle/_ref/mega_ref_cpu.so`` (python oracle/build_ref.py).  The fixtures are
 committed; nothing at test time reads the reference checkout.
 
-Usage: python tests/golden/make_golden.py [all|forward|backward|cema|cema_backward].
+Usage: python tests/golden/make_golden.py [all|forward|backward|cema|cema_backward|backward_truncated].
 
 What runs:
   * the reference's CPU C++ ops (timestep_norm_fwd, group_timestep_norm_fwd,
@@ -413,8 +413,49 @@ def cema_backward_fixtures():
             domega=m.omega.grad)
 
 
+def truncated_backward_fixtures():
+    """Gradients of the bidirectional layers with a truncated kernel (autograd through the reference
+    module: the kernel is built for min(truncation, L) taps, fused_ops/fftconv.py does the rest)."""
+    ops, cema, tsn, sqn = import_reference()
+    gen = torch.Generator().manual_seed(20251129)
+    bsz, dim, length, ndim, trunc = 2, 5, 40, 16, 7
+    for tag, shift, pad in (("ema_bwd_bidir_trunc", True, 0.3), ("ema_bwd_bidir_trunc_noshift", False, 0.0)):
+        params = ema_params(gen, dim, ndim, True)
+        x = torch.randn(bsz, dim, length, generator=gen).requires_grad_(True)
+        dy = torch.randn(bsz, dim, length, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None
+        m = cema_from_real(cema, dim, ndim, params, bidirectional=True, truncation=trunc, shift=shift).train()
+        y = m(x, mask, None)
+        (y * dy).sum().backward()
+        g0 = m.gamma.grad[:, :, 0]
+        alpha, delta, beta, gamma, omega = params
+        npz(tag, x=x, dy=dy, alpha=alpha, delta=delta, beta=beta, gamma=gamma, omega=omega,
+            mask=(mask if mask is not None else np.zeros((0,), bool)), bidirectional=True, shift=shift,
+            truncation=trunc, y=y, dx=x.grad, dalpha=m.alpha.grad, ddelta=m.delta.grad,
+            dbeta=(g0 * gamma).unsqueeze(-1), dgamma=g0 * beta.squeeze(-1), domega=m.omega.grad.view(dim))
+    for tag, shift, pad in (("cema_bwd_bidir_trunc", True, 0.3), ("cema_bwd_bidir_trunc_noshift", False, 0.0)):
+        m = cema.MultiHeadComplexEMA(dim, ndim=ndim, bidirectional=True, truncation=trunc, shift=shift).train()
+        with torch.no_grad():
+            m.alpha.normal_(0, 0.2, generator=gen)
+            m.delta.normal_(0, 0.2, generator=gen)
+            m.theta.normal_(0, 1.0, generator=gen)
+            m.gamma.normal_(0, 1, generator=gen)
+            m.omega.normal_(0, 1, generator=gen)
+        x = torch.randn(bsz, dim, length, generator=gen).requires_grad_(True)
+        dy = torch.randn(bsz, dim, length, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, pad) if pad > 0 else None
+        y = m(x, mask, None)
+        (y * dy).sum().backward()
+        npz(tag, x=x, dy=dy, mask=(mask if mask is not None else np.zeros((0,), bool)), bidirectional=True,
+            shift=shift, truncation=trunc, y=y, alpha=m.alpha, delta=m.delta, theta=m.theta, gamma=m.gamma,
+            omega=m.omega, dx=x.grad, dalpha=m.alpha.grad, ddelta=m.delta.grad, dtheta=m.theta.grad,
+            dgamma=m.gamma.grad, domega=m.omega.grad)
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "backward_truncated"):
+        truncated_backward_fixtures()
     if which in ("all", "cema_backward"):
         cema_backward_fixtures()
     if which in ("all", "cema"):

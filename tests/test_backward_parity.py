@@ -20,20 +20,22 @@ def _leaf(t):
     return t.double().clone().requires_grad_(True)
 
 
-def _ema_module(M, dim, ndim, params, bidirectional=False, shift=True):
-    m = M.MultiHeadEMA(dim, ndim=ndim, bidirectional=bidirectional, shift=shift).cuda().train()
+def _ema_module(M, dim, ndim, params, bidirectional=False, shift=True, truncation=None):
+    m = M.MultiHeadEMA(dim, ndim=ndim, bidirectional=bidirectional, shift=shift, truncation=truncation).cuda().train()
     with torch.no_grad():
         for dst, src in zip((m.alpha, m.delta, m.beta, m.gamma, m.omega), params):
             dst.copy_(src)
     return m
 
 
-@pytest.mark.parametrize("name", ["ema_bwd_uni", "ema_bwd_uni_n3", "ema_bwd_bidir_shift", "ema_bwd_bidir_noshift"])
+@pytest.mark.parametrize("name", ["ema_bwd_uni", "ema_bwd_uni_n3", "ema_bwd_bidir_shift", "ema_bwd_bidir_noshift",
+                                  "ema_bwd_bidir_trunc", "ema_bwd_bidir_trunc_noshift"])
 def test_ema_golden(name):
     M, _ = _mods()
     g = golden(name)
     params = [g[k] for k in ("alpha", "delta", "beta", "gamma", "omega")]
-    m = _ema_module(M, g["x"].shape[1], g["alpha"].shape[1], params, bool(g["bidirectional"]), bool(g["shift"]))
+    m = _ema_module(M, g["x"].shape[1], g["alpha"].shape[1], params, bool(g["bidirectional"]), bool(g["shift"]),
+                    g.get("truncation"))
     x = g["x"].cuda().requires_grad_(True)
     mask = opt_mask(g["mask"])
     y = m(x, None if mask is None else mask.cuda())
@@ -75,6 +77,43 @@ def test_ema_grid(bsz, dim, length, ndim, bidir, shift, dtype):
     assert rel_l2(xd.grad.float().transpose(1, 2), xr.grad) < tol_x
     for t, r, k in zip((m.alpha, m.delta, m.beta, m.gamma, m.omega), leaves, "adbgo"):
         assert rel_l2(t.grad, r.grad) < tol_p, k
+
+@pytest.mark.parametrize("bsz,dim,length,ndim,shift,trunc", [(2, 6, 40, 16, True, 5), (3, 5, 33, 3, False, 9),
+                                                             (2, 9, 70, 32, True, 1), (2, 4, 20, 16, True, 64)])
+@pytest.mark.parametrize("complex_poles", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_truncated_kernel_grid(bsz, dim, length, ndim, shift, trunc, complex_poles, dtype):
+    """Bidirectional layers with a truncated kernel (taps 0 .. trunc - 1; trunc >= L is the full
+    kernel) under autograd against autograd through the fp64 recurrence, interior pads included."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(dim * 100 + length + trunc)
+    torch.manual_seed(dim * 100 + length + trunc)
+    x0 = torch.randn(bsz, length, dim, generator=gen).to(dtype)
+    dy = torch.randn(bsz, dim, length, generator=gen).to(dtype)
+    mask = right_pad_mask(gen, bsz, length, 0.4)
+    mask[0, 2] = True
+    if complex_poles:
+        m = M.MultiHeadComplexEMA(dim, ndim=ndim, bidirectional=True, shift=shift, truncation=trunc).cuda().train()
+        with torch.no_grad():
+            m.gamma[:, :, 1].normal_(0, 1)
+        names = ("alpha", "delta", "theta", "gamma", "omega")
+        ref_fn = O.cema_forward_recurrence
+    else:
+        m = _ema_module(M, dim, ndim, make_ema_params(gen, dim, ndim, True), True, shift, trunc)
+        names = ("alpha", "delta", "beta", "gamma", "omega")
+        ref_fn = O.ema_forward_recurrence
+    leaves = [_leaf(getattr(m, k).detach().cpu()) for k in names]
+    xr = _leaf(x0.float().transpose(1, 2))
+    yr = ref_fn(xr, *leaves, mask, bidirectional=True, shift=shift, truncation=trunc)
+    (yr * dy.double()).sum().backward()
+    xd = x0.cuda().requires_grad_(True)
+    y = m(xd.transpose(1, 2), mask.cuda())
+    (y.float() * dy.cuda().float()).sum().backward()
+    tol_x, tol_p = (2e-5, 1e-4) if dtype == torch.float32 else (2e-2, 2e-2)
+    assert rel_l2(y.float(), yr) < (1e-5 if dtype == torch.float32 else 1e-2)
+    assert rel_l2(xd.grad.float().transpose(1, 2), xr.grad) < tol_x
+    for k, r in zip(names, leaves):
+        assert rel_l2(getattr(m, k).grad, r.grad) < tol_p, k
 
 
 @pytest.mark.parametrize("dim,channel_contiguous", [(6, False), (16, True)])
@@ -252,13 +291,14 @@ def test_block_training_step():
         assert rel_l2(t.grad, r.grad) < 2e-4
 
 
-@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift"])
+@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift",
+                                  "cema_bwd_bidir_trunc", "cema_bwd_bidir_trunc_noshift"])
 def test_complex_ema_golden(name):
     """MultiHeadComplexEMA under autograd against the gradients of the reference module."""
     M, _ = _mods()
     g = golden(name)
     m = M.MultiHeadComplexEMA(g["x"].shape[1], ndim=g["alpha"].shape[1], bidirectional=bool(g["bidirectional"]),
-                              shift=bool(g["shift"])).cuda().train()
+                              shift=bool(g["shift"]), truncation=g.get("truncation")).cuda().train()
     with torch.no_grad():
         for k in ("alpha", "delta", "theta", "gamma", "omega"):
             getattr(m, k).copy_(g[k])

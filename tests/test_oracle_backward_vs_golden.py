@@ -12,12 +12,14 @@ def _leaf(t):
     return t.double().clone().requires_grad_(True)
 
 
-@pytest.mark.parametrize("name", ["ema_bwd_uni", "ema_bwd_uni_n3", "ema_bwd_bidir_shift", "ema_bwd_bidir_noshift"])
+@pytest.mark.parametrize("name", ["ema_bwd_uni", "ema_bwd_uni_n3", "ema_bwd_bidir_shift", "ema_bwd_bidir_noshift",
+                                  "ema_bwd_bidir_trunc", "ema_bwd_bidir_trunc_noshift"])
 def test_ema_gradients(name):
     g = golden(name)
     x, alpha, delta, beta, gamma, omega = [_leaf(g[k]) for k in ("x", "alpha", "delta", "beta", "gamma", "omega")]
     y = O.ema_forward_recurrence(x, alpha, delta, beta, gamma, omega, opt_mask(g["mask"]),
-                                 bidirectional=bool(g["bidirectional"]), shift=bool(g["shift"]))
+                                 bidirectional=bool(g["bidirectional"]), shift=bool(g["shift"]),
+                                 truncation=g.get("truncation"))
     assert rel_l2(y, g["y"]) < 2e-6
     (y * g["dy"].double()).sum().backward()
     for t, k in ((x, "dx"), (alpha, "dalpha"), (delta, "ddelta"), (beta, "dbeta"), (gamma, "dgamma"),
@@ -52,12 +54,13 @@ def test_sequence_norm_gradients(name):
         assert rel_l2(t.grad, g[k]) < 2e-5, k
 
 
-@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift"])
+@pytest.mark.parametrize("name", ["cema_bwd_uni", "cema_bwd_uni_n3", "cema_bwd_bidir_shift", "cema_bwd_bidir_noshift",
+                                  "cema_bwd_bidir_trunc", "cema_bwd_bidir_trunc_noshift"])
 def test_complex_ema_gradients(name):
     g = golden(name)
     leaves = [_leaf(g[k]) for k in ("x", "alpha", "delta", "theta", "gamma", "omega")]
     y = O.cema_forward_recurrence(*leaves, opt_mask(g["mask"]), bidirectional=bool(g["bidirectional"]),
-                                  shift=bool(g["shift"]))
+                                  shift=bool(g["shift"]), truncation=g.get("truncation"))
     assert rel_l2(y, g["y"]) < 2e-6
     (y * g["dy"].double()).sum().backward()
     for t, k in zip(leaves, ("dx", "dalpha", "ddelta", "dtheta", "dgamma", "domega")):
