@@ -213,6 +213,90 @@ __global__ void __launch_bounds__(128) cema_step_kernel(const T* x, T* y, int B,
   Elem<T>::st(y + gid, v);
 }
 
+// The same step with LN = N / 2 lanes per (batch, channel): a lane owns two complex poles (one
+// 16-byte state vector), so a warp moves whole contiguous state rows, and a thread walks BB
+// batch entries with its coefficients in registers.  h_in may be NULL and may alias h_out.
+template <typename T, int LN, int BB>
+__global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restrict__ x, T* __restrict__ y, int B,
+                                                              int D, const float* __restrict__ p,
+                                                              const float* __restrict__ q,
+                                                              const float* __restrict__ g,
+                                                              const float* __restrict__ omega, const float* h_in,
+                                                              float* h_out, int silu) {
+  constexpr int N = LN * 2;
+  const int sub = threadIdx.x % LN;
+  const int d = blockIdx.x * (128 / LN) + threadIdx.x / LN;
+  const bool live = d < D;  // dead lanes stay for the shuffles
+  const int b0 = blockIdx.y * BB;
+  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), gv = qv;
+  float2 pv = make_float2(0.f, 0.f);
+  float om = 0.f;
+  if (live) {
+    qv = __ldg(reinterpret_cast<const float4*>(q + (size_t)d * N * 2) + sub);
+    gv = __ldg(reinterpret_cast<const float4*>(g + (size_t)d * N * 2) + sub);
+    pv = __ldg(reinterpret_cast<const float2*>(p + (size_t)d * N) + sub);
+    om = __ldg(omega + d);
+  }
+  float4 hv[BB];
+  float xv[BB];
+#pragma unroll
+  for (int j = 0; j < BB; ++j) {
+    const int b = b0 + j;
+    const size_t gid = (size_t)b * D + d;
+    hv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    xv[j] = 0.f;
+    if (live && b < B) {
+      if (h_in) hv[j] = *(reinterpret_cast<const float4*>(h_in + gid * N * 2) + sub);
+      xv[j] = Elem<T>::ld(x + gid);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < BB; ++j) {
+    const int b = b0 + j;
+    const size_t gid = (size_t)b * D + d;
+    const float4 h = hv[j];
+    float4 hn;
+    hn.x = fmaf(qv.x, h.x, fmaf(-qv.y, h.y, pv.x * xv[j]));
+    hn.y = fmaf(qv.y, h.x, qv.x * h.y);
+    hn.z = fmaf(qv.z, h.z, fmaf(-qv.w, h.w, pv.y * xv[j]));
+    hn.w = fmaf(qv.w, h.z, qv.z * h.w);
+    float acc = (gv.x * hn.x - gv.y * hn.y) + (gv.z * hn.z - gv.w * hn.w);
+#pragma unroll
+    for (int o = 1; o < LN; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (live && b < B) {
+      *(reinterpret_cast<float4*>(h_out + gid * N * 2) + sub) = hn;
+      if (sub == 0) {
+        float v = fmaf(om, xv[j], acc);
+        if (silu) v = siluf_(v);
+        Elem<T>::st(y + gid, v);
+      }
+    }
+  }
+}
+
+template <typename T>
+static bool launch_cema_step_lanes(const T* x, T* y, int B, int D, int N, const float* p, const float* q,
+                                   const float* g, const float* omega, const float* h_in, float* h_out, int silu,
+                                   void* stream) {
+  if (N != 2 && N != 4 && N != 8 && N != 16 && N != 32) return false;
+  if (!aligned_to(h_out, 16) || (h_in && !aligned_to(h_in, 16)) || !aligned_to(p, 8) || !aligned_to(q, 16) ||
+      !aligned_to(g, 16))
+    return false;
+  constexpr int BB = 4;
+  const int ln = N / 2;
+  dim3 grid((unsigned)((D + 128 / ln - 1) / (128 / ln)), (unsigned)((B + BB - 1) / BB));
+  if (grid.y > 65535) return false;
+#define MEGA_CEMA_STEP_LANES(LNV) \
+  launch(cema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, B, D, p, q, g, omega, h_in, h_out, silu)
+  if (ln == 1) MEGA_CEMA_STEP_LANES(1);
+  else if (ln == 2) MEGA_CEMA_STEP_LANES(2);
+  else if (ln == 4) MEGA_CEMA_STEP_LANES(4);
+  else if (ln == 8) MEGA_CEMA_STEP_LANES(8);
+  else MEGA_CEMA_STEP_LANES(16);
+#undef MEGA_CEMA_STEP_LANES
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------------
 // backward of the complex layer.  h is holomorphic in q and linear in p, so with the complex
 // sensitivities s = dh/dq (s_t = q s_{t-1} + h_{t-1}) and r = dh/dp (r_t = q r_{t-1} + x_t):
@@ -529,6 +613,11 @@ extern "C" int mega_cema_step(const void* x, void* y, int dtype, int B, int D, c
   if (B <= 0 || D <= 0) return MEGA_ERR_SHAPE;
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
+  const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  bool lanes = false;
+  MEGA_DISPATCH_DTYPE(dtype, lanes = launch_cema_step_lanes<T>((const T*)x, (T*)y, B, D, N, p, q, gamma_hat, omega,
+                                                              h_in, h_out, silu, stream));
+  if (lanes) return check_launch("cema_step(lanes)");
   MEGA_DISPATCH_DTYPE(dtype, launch(cema_step_kernel<T>, grid, 128, 0, stream, (const T*)x, (T*)y, B, D, N, p, q,
                                     gamma_hat, omega, h_in, h_out, (flags & MEGA_EMA_SILU) ? 1 : 0));
   return check_launch("cema_step");

@@ -19,6 +19,14 @@ extern std::atomic<int> g_options[8];
 enum { OPT_DISABLE_STREAM = 0, OPT_DISABLE_MMA = 1, OPT_MMA_TILE = 2 };
 int check_launch(const char* what);
 
+// Single-token step with N / 4 lanes per (sequence, channel) (csrc/fused.cu): TimestepNorm update
+// when count is given, then the pole update; false (nothing launched) when N is not 4, 8, 16 or 32
+// or a state / coefficient pointer is not 16-byte aligned.
+bool step_lanes_try(int dtype, const void* x, void* y, void* xn_out, int B, int D, int N, const long long* count,
+                    float* mean, float* var, const float* gamma, const float* beta, float eps, const float* p,
+                    const float* q, const float* g, const float* omega, const float* h_in, float* h_out, int silu,
+                    void* stream);
+
 template <typename... KArgs, typename... Args>
 static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
                           Args... args) {

@@ -448,6 +448,9 @@ extern "C" int mega_ema_step(const void* x, void* y, int dtype, int B, int D, co
   const int np = next_pow2_ndim(N);
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
   const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  if (step_lanes_try(dtype, x, y, nullptr, B, D, N, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f, p, q, gamma_hat,
+                     omega, h_in, h_out, silu, stream))
+    return check_launch("ema_step(lanes)");
   MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, launch(ema_step_kernel<T, NP>, grid, 128, 0, stream,
                                                               (const T*)x, (T*)y, B, D, N, p, q, gamma_hat,
                                                               omega, h_in, h_out, silu)));

@@ -184,6 +184,143 @@ __global__ void __launch_bounds__(128) tsn_ema_step_kernel(const T* __restrict__
   Elem<T>::st(y + gid, v);
 }
 
+// The same step with LN = N / 4 lanes per (sequence, channel): a lane owns four poles, so a warp
+// reads and writes the states as whole contiguous rows (32 / LN channels x N floats per access),
+// and a thread walks BB sequences with the coefficients of its poles in registers (all loads of
+// the BB steps are issued before the arithmetic).  With use_norm the TimestepNorm update runs
+// redundantly in the LN lanes; lane 0 stores the statistics and the output.  h_in may be NULL
+// (zero state) and may alias h_out.
+template <typename T, int LN, int BB>
+__global__ void __launch_bounds__(128) tsn_ema_step_lanes_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                                 T* __restrict__ xn_out, int B, int D,
+                                                                 const long long* count, float* mean, float* var,
+                                                                 const float* __restrict__ gamma,
+                                                                 const float* __restrict__ beta, float eps,
+                                                                 const float* __restrict__ p,
+                                                                 const float* __restrict__ q,
+                                                                 const float* __restrict__ g,
+                                                                 const float* __restrict__ omega, const float* h_in,
+                                                                 float* h_out, int silu, int use_norm) {
+  constexpr int N = LN * 4;
+  const int sub = threadIdx.x % LN;
+  const int d = blockIdx.x * (128 / LN) + threadIdx.x / LN;
+  const bool live = d < D;  // dead lanes stay for the shuffles
+  const int b0 = blockIdx.y * BB;
+  float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), pv = qv, gv = qv;
+  float om = 0.f, gam = 1.f, bet = 0.f;
+  if (live) {
+    qv = __ldg(reinterpret_cast<const float4*>(q + (size_t)d * N) + sub);
+    pv = __ldg(reinterpret_cast<const float4*>(p + (size_t)d * N) + sub);
+    gv = __ldg(reinterpret_cast<const float4*>(g + (size_t)d * N) + sub);
+    om = __ldg(omega + d);
+    if (use_norm) {
+      gam = __ldg(gamma + d);
+      bet = __ldg(beta + d);
+    }
+  }
+  float4 hv[BB];
+  float xv[BB], mu[BB], vr[BB], coef[BB];
+#pragma unroll
+  for (int j = 0; j < BB; ++j) {
+    const int b = b0 + j;
+    const bool ok = live && b < B;
+    const size_t gid = (size_t)b * D + d;
+    hv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    xv[j] = mu[j] = 0.f;
+    vr[j] = coef[j] = 1.f;
+    if (ok) {
+      if (h_in) hv[j] = *(reinterpret_cast<const float4*>(h_in + gid * N) + sub);
+      xv[j] = Elem<T>::ld(x + gid);
+      if (use_norm) {
+        mu[j] = mean[gid];
+        vr[j] = var[gid];
+        coef[j] = __frcp_rn((float)(count[b] + 1));
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < BB; ++j) {
+    const int b = b0 + j;
+    const bool ok = live && b < B;
+    const size_t gid = (size_t)b * D + d;
+    float xin = xv[j];
+    float m1 = 0.f, m2 = 0.f;
+    if (use_norm) {
+      const float d1 = xin - mu[j];
+      m1 = fmaf(coef[j], d1, mu[j]);
+      const float d2 = fmaf(d1, xin - m1, -vr[j]);
+      m2 = fmaf(coef[j], d2, vr[j]);
+      xin = fmaf((xin - m1) * rsqrtf(m2 + eps), gam, bet);
+    }
+    float4 hn = hv[j];
+    hn.x = fmaf(qv.x, hn.x, pv.x * xin); hn.y = fmaf(qv.y, hn.y, pv.y * xin);
+    hn.z = fmaf(qv.z, hn.z, pv.z * xin); hn.w = fmaf(qv.w, hn.w, pv.w * xin);
+    float acc = fmaf(gv.x, hn.x, fmaf(gv.y, hn.y, fmaf(gv.z, hn.z, gv.w * hn.w)));
+#pragma unroll
+    for (int o = 1; o < LN; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (ok) {
+      *(reinterpret_cast<float4*>(h_out + gid * N) + sub) = hn;
+      if (sub == 0) {
+        float v = fmaf(om, xin, acc);
+        if (silu) v = siluf_(v);
+        Elem<T>::st(y + gid, v);
+        if (use_norm) {
+          mean[gid] = m1;
+          var[gid] = m2;
+          if (xn_out) Elem<T>::st(xn_out + gid, xin);
+        }
+      }
+    }
+  }
+}
+
+// Launches the lane-split step when the pole count allows it (N = 4, 8, 16 or 32, states 16-byte
+// aligned); returns false otherwise.
+template <typename T>
+static bool launch_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, const long long* count, float* mean,
+                              float* var, const float* gamma, const float* beta, float eps, const float* p,
+                              const float* q, const float* g, const float* omega, const float* h_in, float* h_out,
+                              int silu, int use_norm, mega_stream_t stream) {
+  if (N != 4 && N != 8 && N != 16 && N != 32) return false;
+  if (!aligned_to(h_out, 16) || (h_in && !aligned_to(h_in, 16)) || !aligned_to(p, 16) || !aligned_to(q, 16) ||
+      !aligned_to(g, 16))
+    return false;
+  constexpr int BB = 4;
+  const int ln = N / 4;
+  dim3 grid((unsigned)((D + 128 / ln - 1) / (128 / ln)), (unsigned)((B + BB - 1) / BB));
+  if (grid.y > 65535) return false;
+#define MEGA_STEP_LANES(LNV)                                                                              \
+  launch(tsn_ema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, xn_out, B, D, count, mean, var, \
+         gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm)
+  if (ln == 1) MEGA_STEP_LANES(1);
+  else if (ln == 2) MEGA_STEP_LANES(2);
+  else if (ln == 4) MEGA_STEP_LANES(4);
+  else MEGA_STEP_LANES(8);
+#undef MEGA_STEP_LANES
+  return true;
+}
+
+bool step_lanes_try(int dtype, const void* x, void* y, void* xn_out, int B, int D, int N, const long long* count,
+                    float* mean, float* var, const float* gamma, const float* beta, float eps, const float* p,
+                    const float* q, const float* g, const float* omega, const float* h_in, float* h_out, int silu,
+                    void* stream) {
+  const int use_norm = count != nullptr;
+  switch (dtype) {
+    case MEGA_F32:
+      return launch_step_lanes<float>((const float*)x, (float*)y, (float*)xn_out, B, D, N, count, mean, var, gamma,
+                                      beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream);
+    case MEGA_BF16:
+      return launch_step_lanes<__nv_bfloat16>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (__nv_bfloat16*)xn_out, B,
+                                              D, N, count, mean, var, gamma, beta, eps, p, q, g, omega, h_in, h_out,
+                                              silu, use_norm, stream);
+    case MEGA_F16:
+      return launch_step_lanes<__half>((const __half*)x, (__half*)y, (__half*)xn_out, B, D, N, count, mean, var,
+                                       gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream);
+    default:
+      return false;
+  }
+}
+
 // One thread per sequence bumps the counts after the element kernel has read them.
 __global__ void tsn_count_step_kernel(long long* count, int B) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -209,10 +346,13 @@ extern "C" MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, 
   const int np = next_pow2_ndim(N);
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
   const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
-  MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, launch(tsn_ema_step_kernel<T, NP>, grid, 128, 0, stream,
-                                                         (const T*)x, (T*)y, (T*)xn_out, B, D, N,
-                                                         (long long*)count, mean, var, gamma, beta, (float)eps,
-                                                         p, q, gamma_hat, omega, h, silu, use_norm)));
+  if (!step_lanes_try(dtype, x, y, xn_out, B, D, N, (const long long*)count, mean, var, gamma, beta, (float)eps, p, q,
+                      gamma_hat, omega, h, h, silu, stream)) {
+    MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, launch(tsn_ema_step_kernel<T, NP>, grid, 128, 0, stream,
+                                                           (const T*)x, (T*)y, (T*)xn_out, B, D, N,
+                                                           (long long*)count, mean, var, gamma, beta, (float)eps,
+                                                           p, q, gamma_hat, omega, h, silu, use_norm)));
+  }
   if (use_norm) launch(tsn_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
   return check_launch("tsn_ema_step");
 }
