@@ -53,6 +53,8 @@ SIGNATURES = {
     "mega_cema_coeffs_bwd": [c_p] * 7 + [c_i, c_i] + [c_p] * 5,
     "mega_attention_softmax_fwd": [c_p, c_p, c_i, c_l, c_l, c_i, c_i, c_p],
     "mega_attention_softmax_bwd": [c_p, c_p, c_p, c_i, c_l, c_l, c_i, c_i, c_p],
+    "mega_attention_dropkey_softmax_fwd": [c_p, c_p, c_i, c_l, c_l, c_i, c_i, c_d, ctypes.c_uint64, ctypes.c_uint64,
+                                           c_p],
     "mega_tsn_cema_fwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
                           c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
     "mega_set_option": [c_i, c_i],

@@ -647,6 +647,21 @@ def attention_softmax_fwd(x, causal=True):
     return y
 
 
+def attention_dropkey_softmax_fwd(x, dropout, causal=True, seed=0, offset=0):
+    """attention_softmax_fwd with DropKey: every kept score is masked with probability ``dropout``
+    before the softmax (no rescaling).  The mask is a function of (seed, offset, row, column)."""
+    _cuda(x)
+    xc = x.contiguous()
+    outer, inner = xc.shape[-2], xc.shape[-1]
+    batch = xc.numel() // (outer * inner)
+    y = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_attention_dropkey_softmax_fwd(
+            xc.data_ptr(), y.data_ptr(), _dt(xc), batch, outer, inner, 1 if causal else 0, float(dropout),
+            int(seed) & 0xFFFFFFFFFFFFFFFF, int(offset) & 0xFFFFFFFFFFFFFFFF, _stream()), "attention_dropkey_softmax_fwd")
+    return y
+
+
 def attention_softmax_bwd(dy, y, causal=True):
     """Gradient of attention_softmax_fwd with respect to the scores."""
     _cuda(dy, y)

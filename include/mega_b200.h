@@ -390,15 +390,27 @@ MEGA_API int mega_cema_coeffs_bwd(const float* alpha, const float* delta, const 
  * Attention-weight softmax of the Mega block.  x, y (and dy, dx) are contiguous (batch, outer, inner)
  * score tensors; softmax over `inner`; with `causal` row r keeps its first inner - outer + r + 1
  * columns and the rest of the row is 0; a row whose kept scores are all -inf is all zeros.
- * inner <= 8192.  DropKey (the reference's stochastic training option) is not implemented.
+ * inner <= 8192.
  * Replaces: attention_softmax_fwd / attention_softmax_bwd with dropout = 0
  * (fairseq/csrc/ops/attention_softmax.cc:6-18, fairseq/csrc/softmax.cuh:90-153; called from
  * fairseq/modules/attention_softmax.py:11-40).
+ *
+ * mega_attention_dropkey_softmax_fwd: the same with DropKey, the reference's training option
+ * (fairseq/csrc/softmax.cuh:155-232): each kept score is set to -inf with probability `dropout`
+ * (0 <= dropout < 1) before the softmax, without rescaling; a row that loses every score is all
+ * zeros.  The backward is mega_attention_softmax_bwd (dropped columns have y = 0).  Column c of
+ * row i (i over batch x outer) is dropped when word c % 4 of Philox4x32-10 with counter
+ * (c / 4, i, offset low, offset high) and key (seed low, seed high) is below dropout * 2^32: the mask
+ * is a function of (seed, offset, i, c) only.  The reference draws from curand's Philox stream
+ * indexed by its own thread layout, so the masks are equal in distribution, not bit for bit.
  */
 MEGA_API int mega_attention_softmax_fwd(const void* x, void* y, int dtype, int64_t batch, int64_t outer, int inner,
                                int causal, mega_stream_t stream);
 MEGA_API int mega_attention_softmax_bwd(const void* dy, const void* y, void* dx, int dtype, int64_t batch,
                                int64_t outer, int inner, int causal, mega_stream_t stream);
+MEGA_API int mega_attention_dropkey_softmax_fwd(const void* x, void* y, int dtype, int64_t batch, int64_t outer,
+                                       int inner, int causal, double dropout, uint64_t seed, uint64_t offset,
+                                       mega_stream_t stream);
 
 #ifdef __cplusplus
 }

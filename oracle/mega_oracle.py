@@ -510,3 +510,46 @@ def attention_softmax(x, use_causal_mask=True):
     e = torch.where(dead.expand_as(e), torch.zeros_like(e), e)
     d = e.sum(-1, keepdim=True)
     return torch.where(d == 0, torch.zeros_like(e), e / torch.where(d == 0, torch.ones_like(d), d))
+
+
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3",
+    SC'11) on numpy uint64 arrays holding 32-bit words; returns the four output words."""
+    import numpy as np
+    m32 = np.uint64(0xFFFFFFFF)
+    c0, c1, c2, c3 = [np.asarray(c, dtype=np.uint64) & m32 for c in np.broadcast_arrays(c0, c1, c2, c3)]
+    k0, k1 = np.uint64(k0) & m32, np.uint64(k1) & m32
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        hi0, lo0 = p0 >> np.uint64(32), p0 & m32
+        hi1, lo1 = p1 >> np.uint64(32), p1 & m32
+        c0, c1, c2, c3 = hi1 ^ c1 ^ k0, lo1, hi0 ^ c3 ^ k1, lo0
+        k0 = (k0 + np.uint64(0x9E3779B9)) & m32
+        k1 = (k1 + np.uint64(0xBB67AE85)) & m32
+    return c0, c1, c2, c3
+
+
+def dropkey_mask(rows, inner, dropout, seed, offset=0):
+    """The DropKey mask of the CUDA kernel (True = score dropped), shape (rows, inner): column c of
+    row i is dropped when word c % 4 of Philox4x32-10(counter (c // 4, i, offset lo, offset hi),
+    key (seed lo, seed hi)) is below dropout * 2^32.  The reference (fairseq/csrc/softmax.cuh:
+    155-186) drops with the same probability from curand's Philox stream in its own thread
+    order; only the distribution is shared."""
+    import numpy as np
+    groups = (inner + 3) // 4
+    cg = np.arange(groups, dtype=np.uint64).reshape(1, groups)
+    ri = np.arange(rows, dtype=np.uint64).reshape(rows, 1)
+    w = philox4x32_10(cg, ri, np.uint64(offset & 0xFFFFFFFF), np.uint64((offset >> 32) & 0xFFFFFFFF),
+                      seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    bits = np.stack(w, axis=-1).reshape(rows, groups * 4)[:, :inner]
+    return torch.from_numpy(bits < np.uint64(int(dropout * 4294967296.0)))
+
+
+def attention_dropkey_softmax(x, dropout, use_causal_mask, seed, offset=0):
+    """fairseq/csrc/softmax.cuh:155-232 (AttentionDropKeySoftmaxFwdKernel) with the mask of
+    ``dropkey_mask``: dropped scores become -inf before the softmax, nothing is rescaled."""
+    outer, inner = x.shape[-2], x.shape[-1]
+    rows = x.numel() // inner
+    drop = dropkey_mask(rows, inner, dropout, seed, offset).view(x.shape)
+    return attention_softmax(x.double().masked_fill(drop, float("-inf")), use_causal_mask)

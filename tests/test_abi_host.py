@@ -90,6 +90,9 @@ def test_argument_rejection_training_and_complex_entry_points():
     assert lib.mega_cema_coeffs(one, one, one, one, 7, 4, 16, one, one, one, None) == 2
     assert lib.mega_gate_qk(one, 4, one, one, one, 8, one, 8, 0, 2, 8, 1e-5, None) == 4  # pitch below the row length
     assert lib.mega_ema_coeffs_bwd(one, one, one, one, one, one, 0, 16, one, one, one, one, None) == 3
+    # DropKey softmax: probability in [0, 1)
+    assert lib.mega_attention_dropkey_softmax_fwd(one, one, 0, 1, 1, 8, 1, 1.0, 1, 0, None) == 7
+    assert lib.mega_attention_dropkey_softmax_fwd(None, one, 0, 1, 1, 8, 1, 0.1, 1, 0, None) == 1
 
 
 def test_ops_refuse_cpu_tensors():

@@ -92,3 +92,17 @@ def test_fft_path_vs_recurrence_long():
     a = O.ema_forward_fft(x, *prm)
     b = O.ema_forward_recurrence(x, *prm)
     assert rel_l2(a, b) < 2e-6
+
+
+def test_philox_known_answers():
+    """Philox4x32-10 known-answer vectors published with the generator (Random123 kat_vectors):
+    the DropKey mask of the attention softmax is built on it."""
+    from oracle import mega_oracle as O
+    ones = 0xFFFFFFFF
+    assert [int(v) for v in O.philox4x32_10(0, 0, 0, 0, 0, 0)] == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert [int(v) for v in O.philox4x32_10(ones, ones, ones, ones, ones, ones)] == [0x408f276d, 0x41c83b0e,
+                                                                                      0xa20bc7c6, 0x6d5451fd]
+    assert [int(v) for v in O.philox4x32_10(0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344, 0xa4093822,
+                                            0x299f31d0)] == [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+    m = O.dropkey_mask(64, 1000, 0.3, 99, 1)
+    assert m.shape == (64, 1000) and abs(m.float().mean().item() - 0.3) < 0.01
