@@ -2,7 +2,8 @@
 // activations with contiguous channels and no padding mask.
 //
 // Work split.  A CTA owns kCg column groups (8 channels = 16 bytes each; kCg = 8, 7, 4 or 2) of 8
-// sequences and walks time in steps of 32 positions.  Warp w owns column group w.  For one
+// sequences and walks time in steps of 32 positions.  Warp w owns column group w (or, with two
+// warps per column group, four of its eight channels).  For one
 // channel the 8 sequences x 2 consecutive 16-position chunks of a step form the 16 rows of
 // warp-level MMAs (row g = sequence g, chunk 0; row g + 8 = sequence g, chunk 1), so every carry
 // between chunks stays inside one thread and no cross-lane scan is needed.  The 56-channel tile
@@ -37,10 +38,12 @@ namespace {
 
 constexpr int kSeq = 8;    // sequences per CTA
 constexpr int kStep = 32;  // positions per step (2 chunks of 16)
-constexpr int kStages = 4;
 
 template <int kCg>
 struct Cfg {
+  // Ring depth: a tile is fetched kStages - 1 steps before it is used.  Deeper rings were measured
+  // and do not pay: a fifth stage leaves the SM too little L1 for the few spilled registers.
+  static constexpr int kStages = 4;
   static constexpr int kCh = kCg * 8;                       // channels per CTA
   static constexpr int kRow = kCg * 16;                     // bytes per tile row
   static constexpr int kStageBytes = kSeq * kStep * kRow;   // 32 KiB (kCg = 8) / 28 KiB (kCg = 7)
@@ -52,7 +55,7 @@ struct Cfg {
   static constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [kCh][2] f32
   static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
   static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages]
-  static constexpr int kSmemBytes = kOffBar + 128 + 1024;           // + alignment slack
+  static constexpr int kSmemBytes = kOffBar + 2 * kStages * 8 + 1024;  // + alignment slack
 };
 
 // d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
@@ -87,6 +90,9 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -125,13 +131,18 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
   return (uint32_t)(row * (kCg * 16) + (cg << 4));
 }
 
-template <bool kNorm, int kCg, bool kSilu>
-__global__ void __launch_bounds__(kCg * 32, 1)
+// kWs = warps per column group: 1 (a warp owns the 8 channels of its 16-byte column) or 2 (a warp
+// owns 4 of them: half the per-thread state and tile registers, so more warps fit an SM).
+template <bool kNorm, int kCg, bool kSilu, int kWs>
+__global__ void __launch_bounds__(kCg * kWs * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        StreamArgs a) {
   using C = Cfg<kCg>;
   constexpr int kCh = C::kCh;
-  constexpr int kThreads = kCg * 32;
+  constexpr int kThreads = kCg * kWs * 32;
+  constexpr int kStages = C::kStages;
+  constexpr int kE = 8 / kWs;   // channels per warp
+  constexpr int kVw = kE / 2;   // 32-bit words (channel pairs) per tile vector of this warp
   constexpr int kStageBytes = C::kStageBytes;
   constexpr int kOffStages = C::kOffStages, kOffT = C::kOffT, kOffP = C::kOffP, kOffG = C::kOffG;
   constexpr int kOffA = C::kOffA, kOffWB = C::kOffWB, kOffKp = C::kOffKp, kOffBar = C::kOffBar;
@@ -148,7 +159,9 @@ __global__ void __launch_bounds__(kCg * 32, 1)
 
   const uint32_t sm_s = smem_u32(sm);
   const int tid = threadIdx.x;
-  const int lane = tid & 31, warp = tid >> 5;
+  const int lane = tid & 31;
+  const int warp = (tid >> 5) / kWs;  // column group
+  const int hf = (tid >> 5) % kWs;    // which part of the column's channels
   const int g = lane >> 2, q = lane & 3;
   const int d0 = blockIdx.x * kCh;
   const int b0 = blockIdx.y * kSeq;
@@ -160,7 +173,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
     prefetch_tensormap(&tmy);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&done[s], kCg);
+      mbar_init(&done[s], kCg * kWs);
     }
     mbar_fence_init();
   }
@@ -245,12 +258,13 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   // ---- running state of this thread: sequence b0 + g, channels 8*warp + e ----------------------
   const int bseq = b0 + g;
   const bool seq_ok = bseq < a.B;
-  float hc[8][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
-  float mu_run[8], m2_run[8], s1_run[8];  // running mean, sum of squared deviations, sum of x
+  float hc[kE][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
+  float mu_run[kE], m2_run[kE], s1_run[kE];  // running mean, sum of squared deviations, sum of x
   float nbase = 1.f;
+  const int cbase = warp * 8 + hf * kE;  // first channel of this warp inside the tile
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const int d = d0 + warp * 8 + e;
+  for (int e = 0; e < kE; ++e) {
+    const int d = d0 + cbase + e;
     const bool ok = seq_ok && d < a.D;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -271,10 +285,21 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   if (kNorm && seq_ok) nbase = (float)a.prev_count[bseq] + 1.f;
   const float ut0 = (2 * q <= g) ? 1.f : 0.f, ut1 = (2 * q + 1 <= g) ? 1.f : 0.f;
   const float eps = a.eps;
-  // position offsets of the 8 vectors this thread touches: j = 0..3 chunk 0, j = 4..7 chunk 1
-  int toff[8];
+  // position offsets of the 8 vectors this thread touches: j = 0..3 chunk 0, j = 4..7 chunk 1.
+  // Rows of sequences g and g + 1 lie a multiple of 128 bytes apart, so the two sequences of a
+  // quarter warp would hit the same banks: lanes with odd g therefore access the two positions of
+  // each pair (t, t + 1) in the other order (slot j holds logical vector j ^ 1 there).
+  // (Both LSU savings, this one and the all-ones MMAs below, are for the two-warps-per-column form;
+  // with one warp per column the kernel is latency-bound and they cost 1 % instead.)
+  constexpr bool kLeanLsu = kWs > 1;
+  const bool odd = kLeanLsu && (g & 1) != 0;
+  int toff[8];   // logical: vector j is position toff[j]
+  int soff[8];   // access order: slot j touches position soff[j]
 #pragma unroll
-  for (int j = 0; j < 8; ++j) toff[j] = (j >> 2) * 16 + 2 * q + (j & 1) + ((j >> 1) & 1) * 8;
+  for (int j = 0; j < 8; ++j) {
+    toff[j] = (j >> 2) * 16 + 2 * q + (j & 1) + ((j >> 1) & 1) * 8;
+    soff[j] = (j >> 2) * 16 + 2 * q + ((j & 1) ^ (odd ? 1 : 0)) + ((j >> 1) & 1) * 8;
+  }
 
   __syncthreads();  // matrices visible
 
@@ -284,9 +309,17 @@ __global__ void __launch_bounds__(kCg * 32, 1)
     unsigned char* stage = sm + kOffStages + s * kStageBytes;
     const uint32_t stage_s = sm_s + kOffStages + s * kStageBytes;
     const bool ok = mbar_wait(&full[s], ph);
-    uint4 v[8];
+    uint32_t v[8][kVw];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = lds128(stage_s + vec_off<kCg>(g, toff[j], warp));
+    for (int j = 0; j < 8; ++j) {
+      if (kWs == 1) {
+        const uint4 t4 = lds128(stage_s + vec_off<kCg>(g, soff[j], warp));
+        v[j][0] = t4.x; v[j][1] = t4.y; v[j][kVw - 2] = t4.z; v[j][kVw - 1] = t4.w;
+      } else {
+        const uint2 t2 = lds64(stage_s + vec_off<kCg>(g, soff[j], warp) + hf * 8);
+        v[j][0] = t2.x; v[j][1] = t2.y;
+      }
+    }
     float invn[8];
     float inv_end = 0.f, n_end = 1.f;
     const bool tail = (i + 1) * kStep > L;
@@ -298,16 +331,16 @@ __global__ void __launch_bounds__(kCg * 32, 1)
       inv_end = rcp_fast(n_end);
     }
 #pragma unroll
-    for (int pp = 0; pp < 4; ++pp) {
+    for (int pp = 0; pp < kVw; ++pp) {
       float yv[2][8];
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         const int e = 2 * pp + h2;
-        const int ch = warp * 8 + e;
+        const int ch = cbase + e;
         float xf[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t w32 = pp == 0 ? v[j].x : pp == 1 ? v[j].y : pp == 2 ? v[j].z : v[j].w;
+          const uint32_t w32 = odd ? v[j ^ 1][pp] : v[j][pp];
           xf[j] = __uint_as_float(h2 == 0 ? (w32 << 16) : (w32 & 0xffff0000u));
         }
         float xn[8];
@@ -319,17 +352,27 @@ __global__ void __launch_bounds__(kCg * 32, 1)
           // 0/1 upper-triangular matrix per half.  The total of a half is its last prefix, held
           // by the lane with q = 3; a shuffle hands it to the row's other lanes, and the carries
           // (running total + totals of the halves before) are added afterwards in fp32.
-          const int src3 = lane | 3;
           float k1[4];  // carry of the sum of x for (row g, first half), (g, second), (g + 8, first), (g + 8, second)
           {  // sum of x: exact (bf16 inputs, fp32 accumulation)
-            float D0[4], D1[4];
+            float D0[4], D1[4], E0[4], E1[4];
             mma_tf32(D0, xf[0], xf[4], xf[1], xf[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(D1, xf[2], xf[6], xf[3], xf[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
+            // totals of the halves: the same rows against an all-ones matrix put the total into every
+            // column, i.e. into every lane of the row (a shuffle goes through the LSU data pipe, which
+            // the two-warps-per-column form loads to 60 %)
+            if (kLeanLsu) {
+              mma_tf32(E0, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E1, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            } else {  // the total of a half is its last prefix, held by the lane with q = 3
+              const int src3 = lane | 3;
+              E0[0] = __shfl_sync(0xffffffffu, D0[1], src3); E1[0] = __shfl_sync(0xffffffffu, D1[1], src3);
+              E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
+            }
             k1[0] = s1_run[e];
-            k1[1] = k1[0] + __shfl_sync(0xffffffffu, D0[1], src3);
-            k1[2] = k1[1] + __shfl_sync(0xffffffffu, D1[1], src3);
-            k1[3] = k1[2] + __shfl_sync(0xffffffffu, D0[3], src3);
-            tot1 = k1[3] + __shfl_sync(0xffffffffu, D1[3], src3);
+            k1[1] = k1[0] + E0[0];
+            k1[2] = k1[1] + E1[0];
+            k1[3] = k1[2] + E0[2];
+            tot1 = k1[3] + E1[2];
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
@@ -350,11 +393,18 @@ __global__ void __launch_bounds__(kCg * 32, 1)
               sq[2 * jp] = lo * lo;
               sq[2 * jp + 1] = hi * hi;
             }
-            float D0[4], D1[4];
+            float D0[4], D1[4], E0[4], E1[4];
             mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
-            const float ea = __shfl_sync(0xffffffffu, D0[1], src3), fa = __shfl_sync(0xffffffffu, D1[1], src3);
-            const float eb = __shfl_sync(0xffffffffu, D0[3], src3), fb = __shfl_sync(0xffffffffu, D1[3], src3);
+            if (kLeanLsu) {
+              mma_tf32(E0, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E1, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+            } else {
+              const int src3 = lane | 3;
+              E0[0] = __shfl_sync(0xffffffffu, D0[1], src3); E1[0] = __shfl_sync(0xffffffffu, D1[1], src3);
+              E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
+            }
+            const float ea = E0[0], fa = E1[0], eb = E0[2], fb = E1[2];
             k2[0] = m2_run[e];
             k2[1] = k2[0] + ea;
             k2[2] = k2[1] + fa;
@@ -440,13 +490,19 @@ __global__ void __launch_bounds__(kCg * 32, 1)
         }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t o = pack_bf16(yv[0][j], yv[1][j]);
-        if (pp == 0) v[j].x = o; else if (pp == 1) v[j].y = o; else if (pp == 2) v[j].z = o; else v[j].w = o;
+      for (int j = 0; j < 8; j += 2) {
+        const uint32_t o0 = pack_bf16(yv[0][j], yv[1][j]), o1 = pack_bf16(yv[0][j + 1], yv[1][j + 1]);
+        v[j][pp] = odd ? o1 : o0;
+        v[j + 1][pp] = odd ? o0 : o1;
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sts128(stage_s + vec_off<kCg>(g, toff[j], warp), v[j]);
+    for (int j = 0; j < 8; ++j) {
+      if (kWs == 1)
+        sts128(stage_s + vec_off<kCg>(g, soff[j], warp), make_uint4(v[j][0], v[j][1], v[j][kVw - 2], v[j][kVw - 1]));
+      else
+        sts64(stage_s + vec_off<kCg>(g, soff[j], warp) + hf * 8, make_uint2(v[j][0], v[j][1]));
+    }
     fence_proxy_async();
     __syncwarp();
     if (!ok) break;
@@ -469,20 +525,20 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   // ---- final statistics and states -------------------------------------------------------------
   if (seq_ok && q == 0) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int d = d0 + warp * 8 + e;
+    for (int e = 0; e < kE; ++e) {
+      const int d = d0 + cbase + e;
       if (kNorm && d < a.D) {
         const float n = (float)a.prev_count[bseq] + (float)L;
         a.mean_out[(size_t)bseq * a.D + d] = mu_run[e];
         a.var_out[(size_t)bseq * a.D + d] = fmaxf(m2_run[e] / n, 0.f);
       }
     }
-    if (kNorm && blockIdx.x == 0 && warp == 0) a.count_out[bseq] = a.prev_count[bseq] + L;
+    if (kNorm && blockIdx.x == 0 && warp == 0 && hf == 0) a.count_out[bseq] = a.prev_count[bseq] + L;
   }
   if (seq_ok && a.h_out) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int d = d0 + warp * 8 + e;
+    for (int e = 0; e < kE; ++e) {
+      const int d = d0 + cbase + e;
       if (d < a.D) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -494,7 +550,7 @@ __global__ void __launch_bounds__(kCg * 32, 1)
   }
 }
 
-template <bool kNorm, int kCg, bool kSilu>
+template <bool kNorm, int kCg, bool kSilu, int kWs = 1>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s) {
   using C = Cfg<kCg>;
@@ -502,7 +558,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   CUtensorMap tx, ty;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
   if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, sw)) return false;
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -513,7 +569,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
     return false;
   }
   dim3 grid((a.D + C::kCh - 1) / C::kCh, (a.B + kSeq - 1) / kSeq);
-  launch(kern, grid, dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, a);
+  launch(kern, grid, dim3(kCg * kWs * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, a);
   return true;
 }
 
@@ -534,6 +590,9 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   // waves).  Problems too small to give every SM a wide tile: 32 or 16 channels per CTA, so
   // that the few (8 sequences x 8 channels) strips there are spread over the SMs; a strip is
   // a serial chain along the sequence, so its speed depends on how few warps share its SM.
+  // With the normalisation (three quarters of a step's instructions) such problems take the
+  // 16-channel tile with two warps per column: a warp then walks 4 channels per step, e.g.
+  // B = 16, L = 4096, D = 1024: 0.29 -> 0.17 ms; B = 8, L = 8192, D = 1024: 0.55 -> 0.30 ms.
   const long long seq_groups = (a_in.B + kSeq - 1) / kSeq;
   auto ctas = [&](int ch) -> long long { return ((a_in.D + ch - 1) / ch) * seq_groups; };
   auto waves_cost = [&](int ch) -> double {
@@ -541,12 +600,14 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     return (double)waves * ch;  // time ~ waves x work per CTA
   };
   int tile = g_options[OPT_MMA_TILE].load();
-  if (tile != 2 && tile != 4 && tile != 7 && tile != 8) {
+  if (tile != 2 && tile != 4 && tile != 7 && tile != 8 && tile != 22) {
     if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
+    else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
   }
 #define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
-  (tile == 7   ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
+  (tile == 22  ? launch_variant<NORM, 2, SILU, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)     \
+   : tile == 7 ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
    : tile == 8 ? launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
    : tile == 4 ? launch_variant<NORM, 4, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
                : launch_variant<NORM, 2, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))

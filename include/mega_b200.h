@@ -75,7 +75,8 @@ MEGA_API uint64_t mega_launch_count(void);
  */
 #define MEGA_OPT_DISABLE_STREAM 0
 #define MEGA_OPT_DISABLE_MMA 1 /* non-zero: skip the tensor-core kernels */
-#define MEGA_OPT_MMA_TILE 2    /* 2, 4, 7, 8: force 16-, 32-, 56-, 64-channel tensor-core tiles; 0: automatic */
+#define MEGA_OPT_MMA_TILE 2    /* 2, 4, 7, 8: force 16-, 32-, 56-, 64-channel tensor-core tiles; 22: 16 channels
+                                  with two warps per 16-byte column; 0: automatic */
 MEGA_API int mega_set_option(int key, int value);
 /*
  * Debug aid (synchronises the device): reads the device-side error word that a kernel raises

@@ -151,7 +151,7 @@ def test_streamed_path_matches_generic(dtype, bsz, length, dim):
 @pytest.mark.parametrize("bsz,length,dim,ndim", [(4, 32, 64, 16), (9, 100, 72, 16), (8, 1024, 128, 16),
                                                   (16, 257, 200, 16), (5, 64, 8, 2), (8, 96, 136, 5)])
 @pytest.mark.parametrize("with_state", [False, True])
-@pytest.mark.parametrize("tile", [8, 7, 4, 2])
+@pytest.mark.parametrize("tile", [8, 7, 4, 2, 22])
 def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
     """bf16, no padding: the tensor-core kernels (fused TimestepNorm -> EMA and EMA alone) against
     the oracle, and against the streamed SIMT kernels (a test switch disables the MMA path)."""
@@ -173,7 +173,7 @@ def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
     before = M.launch_count()
     for disable in (0, 1):
         _lib.set_option(1, disable)
-        _lib.set_option(2, tile)   # 64-, 56-, 32- or 16-channel tiles
+        _lib.set_option(2, tile)   # 64-, 56-, 32- or 16-channel tiles; 22: 16 channels with two warps per 16-byte column
         try:
             fused = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
                                           p, q, g, prm[4].cuda(), None, h_in=None if h0 is None else h0.cuda(),
