@@ -36,7 +36,7 @@ WORKLOADS = {
     "tiny": (4, 2048, 256, "bf16"),
 }
 # side workloads (BASELINE configs 0, 2 and the decode half of config 4): own JSON line, N=1 only
-AUX_WORKLOADS = ("c0", "c2", "decode", "cema", "train")
+AUX_WORKLOADS = ("c0", "c2", "decode", "cema", "train", "c4n", "c1n")
 NDIM = 16
 FALLBACK_HBM_GBS = 6650.0
 
@@ -509,6 +509,19 @@ def run_aux(args):
             norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
             ms = timed(lambda: M.timestep_norm_ema(norm, ema, x), steps, warm)
             tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 2, "cema: TimestepNorm+MultiHeadComplexEMA causal fwd bf16 L=32768 B=16 D=2048", "bf16"
+        elif args.workload in ("c4n", "c1n"):
+            # configs 4 and 1 as the Mega block calls the pair: the normalised activations are a second
+            # output (they feed the value projection), so the compulsory traffic is 3 x D x 2 B per token
+            L, B, D = (32768, 64, 2048) if args.workload == "c4n" else (4096, 16, 1024)
+            x = torch.empty(B, L, D, dtype=torch.bfloat16, device=dev)
+            for b in range(B):
+                x[b] = torch.randn(L, D, device=dev, dtype=torch.bfloat16)
+            ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+            norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+            ms = timed(lambda: M.timestep_norm_ema(norm, ema, x, None, None, 'silu', return_normed=True), steps, warm)
+            tokens, bytes_alg, dt = B * L, 3.0 * B * L * D * 2, "bf16"
+            name = "%s: TimestepNorm+MultiHeadEMA(+SiLU) fwd returning the normalised activations too, bf16 L=%d B=%d D=%d" % (
+                args.workload, L, B, D)
         elif args.workload == "c0":
             L, B, D = 1024, 8, 512
             x = torch.randn(L, B, D, generator=gen).to(dev)           # time-major, viewed as (B, D, L)

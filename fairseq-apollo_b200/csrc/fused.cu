@@ -389,20 +389,9 @@ extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype,
     sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = a.silu;
+    // (the tensor-core kernel writes the normalised activations too when xn_out is given)
     if (mma_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream))
       return check_launch("tsn_ema_fwd(mma)");
-    if (xn_out != nullptr && xn_out != y && xn_out != x) {
-      // The tensor-core kernel has no second output: when the normalised activations are wanted
-      // too, it produces y and the streamed TimestepNorm kernel produces xn (x is read twice,
-      // still cheaper than the SIMT fused kernel).  Both write the same final statistics.
-      StreamArgs sn = sa;
-      sn.N = 0; sn.p = sn.q = sn.g = sn.omega = nullptr; sn.h_in = nullptr; sn.h_out = nullptr; sn.silu = 0;
-      if (mma_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream)) {
-        if (stream_cl_try(dtype, x, xn_out, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, false, sn, (cudaStream_t)stream))
-          return check_launch("tsn_ema_fwd(mma+norm)");
-        // could not stream the norm: fall through and let the generic path rewrite everything
-      }
-    }
     if (stream_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, true, sa, (cudaStream_t)stream))
       return check_launch("tsn_ema_fwd(stream)");
   }

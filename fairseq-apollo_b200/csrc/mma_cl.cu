@@ -39,23 +39,27 @@ namespace {
 constexpr int kSeq = 8;    // sequences per CTA
 constexpr int kStep = 32;  // positions per step (2 chunks of 16)
 
-template <int kCg>
+// kXn: the kernel also writes the normalised activations (the Mega block feeds them to its value
+// projection): two more tile buffers, filled from registers and stored by TMA like the outputs, at
+// the price of one stage of the ring.
+template <int kCg, bool kXn = false>
 struct Cfg {
   // Ring depth: a tile is fetched kStages - 1 steps before it is used.  Deeper rings were measured
   // and do not pay: a fifth stage leaves the SM too little L1 for the few spilled registers.
-  static constexpr int kStages = 4;
+  static constexpr int kStages = kXn ? 3 : 4;
   static constexpr int kCh = kCg * 8;                       // channels per CTA
   static constexpr int kRow = kCg * 16;                     // bytes per tile row
   static constexpr int kStageBytes = kSeq * kStep * kRow;   // 32 KiB (kCg = 8) / 28 KiB (kCg = 7)
   static constexpr int kOffStages = 0;
-  static constexpr int kOffT = kOffStages + kStages * kStageBytes;  // [kCh][2][32] u32
+  static constexpr int kOffXn = kOffStages + kStages * kStageBytes;  // kXn: [2][stage] normalised tiles
+  static constexpr int kOffT = kOffXn + (kXn ? 2 * kStageBytes : 0);  // [kCh][2][32] u32
   static constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [kCh][32] uint4
   static constexpr int kOffG = kOffP + kCh * 4 * 32 * 4;            // [kCh][32] uint4
   static constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [kCh][16] f32  (q^16)
   static constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [kCh][2] f32
   static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
-  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages]
-  static constexpr int kSmemBytes = kOffBar + 2 * kStages * 8 + 1024;  // + alignment slack
+  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages], xfree[2]
+  static constexpr int kSmemBytes = kOffBar + (2 * kStages + 2) * 8 + 1024;  // + alignment slack
 };
 
 // d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
@@ -133,11 +137,12 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 
 // kWs = warps per column group: 1 (a warp owns the 8 channels of its 16-byte column) or 2 (a warp
 // owns 4 of them: half the per-thread state and tile registers, so more warps fit an SM).
-template <bool kNorm, int kCg, bool kSilu, int kWs>
+template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn>
 __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
-                       StreamArgs a) {
-  using C = Cfg<kCg>;
+                       const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
+  static_assert(!kXn || kNorm, "the normalised copy exists only with the normalisation");
+  using C = Cfg<kCg, kXn>;
   constexpr int kCh = C::kCh;
   constexpr int kThreads = kCg * kWs * 32;
   constexpr int kStages = C::kStages;
@@ -156,6 +161,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   float* Kp = reinterpret_cast<float*>(sm + kOffKp);
   uint64_t* full = reinterpret_cast<uint64_t*>(sm + kOffBar);
   uint64_t* done = full + kStages;  // one arrival per warp once its slice of the stage is written
+  uint64_t* xfree = done + kStages;  // kXn: buffer k of the normalised tiles has been read by its store
 
   const uint32_t sm_s = smem_u32(sm);
   const int tid = threadIdx.x;
@@ -174,6 +180,10 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&done[s], kCg * kWs);
+    }
+    if (kXn) {
+      mbar_init(&xfree[0], 1);
+      mbar_init(&xfree[1], 1);
     }
     mbar_fence_init();
   }
@@ -331,8 +341,10 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
       inv_end = rcp_fast(n_end);
     }
 #pragma unroll
+    uint32_t vx[kXn ? 8 : 1][kXn ? kVw : 1];  // kXn: words of the normalised tile
     for (int pp = 0; pp < kVw; ++pp) {
       float yv[2][8];
+      float xq[kXn ? 2 : 1][8];
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         const int e = 2 * pp + h2;
@@ -446,6 +458,10 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) xn[j] = xf[j];
         }
+        if (kXn) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xq[h2][j] = xn[j];
+        }
         // A fragment of xn: a0 (row g: t = 2q, 2q+1), a1 (row g+8), a2 (row g: t = 2q+8, 2q+9), a3 (row g+8)
         const uint32_t xa0 = pack_bf16(xn[0], xn[1]), xa2 = pack_bf16(xn[2], xn[3]);
         const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
@@ -494,6 +510,23 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
         const uint32_t o0 = pack_bf16(yv[0][j], yv[1][j]), o1 = pack_bf16(yv[0][j + 1], yv[1][j + 1]);
         v[j][pp] = odd ? o1 : o0;
         v[j + 1][pp] = odd ? o0 : o1;
+        if (kXn) {
+          const uint32_t n0 = pack_bf16(xq[0][j], xq[1][j]), n1 = pack_bf16(xq[0][j + 1], xq[1][j + 1]);
+          vx[j][pp] = odd ? n1 : n0;
+          vx[j + 1][pp] = odd ? n0 : n1;
+        }
+      }
+    }
+    if (kXn) {
+      // the store that read this buffer two steps ago must have drained it
+      if (i >= 2 && !mbar_wait(&xfree[i & 1], (uint32_t)(((i >> 1) - 1) & 1))) break;
+      const uint32_t xb = sm_s + C::kOffXn + (i & 1) * kStageBytes;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (kWs == 1)
+          sts128(xb + vec_off<kCg>(g, soff[j], warp), make_uint4(vx[j][0], vx[j][1], vx[j][kVw - 2], vx[j][kVw - 1]));
+        else
+          sts64(xb + vec_off<kCg>(g, soff[j], warp) + hf * 8, make_uint2(vx[j][0], vx[j][1]));
       }
     }
 #pragma unroll
@@ -511,9 +544,14 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     if (tid == 0) {
       if (!mbar_wait(&done[s], ph)) break;
       tma_store_3d(&tmy, d0, i * kStep, b0, stage);
+      if (kXn) tma_store_3d(&tmn, d0, i * kStep, b0, sm + C::kOffXn + (i & 1) * kStageBytes);
       bulk_commit();
+      if (kXn) {
+        bulk_wait_read<1>();  // the stores of the step before have drained their stage and buffer
+        if (i >= 1) mbar_arrive(&xfree[(i - 1) & 1]);
+      }
       if (i + kStages - 1 < nsteps) {
-        bulk_wait_read<1>();  // the store issued one step ago has drained its stage
+        if (!kXn) bulk_wait_read<1>();  // the store issued one step ago has drained its stage
         const int s2 = (i + kStages - 1) % kStages;
         mbar_expect_tx(&full[s2], kStageBytes);
         tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i + kStages - 1) * kStep, b0, &full[s2]);
@@ -550,15 +588,22 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   }
 }
 
-template <bool kNorm, int kCg, bool kSilu, int kWs = 1>
+// xn (with its strides nsb, nsl) is the optional second output; kXn selects the kernel form.
+template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
-                           long long ysl, const StreamArgs& a, cudaStream_t s) {
-  using C = Cfg<kCg>;
+                           long long ysl, const StreamArgs& a, cudaStream_t s, void* xn = nullptr,
+                           long long nsb = 0, long long nsl = 0) {
+  using C = Cfg<kCg, kXn>;
   const CUtensorMapSwizzle sw = kCg == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
-  CUtensorMap tx, ty;
+  CUtensorMap tx, ty, tn;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
   if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, sw)) return false;
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs>;
+  if (kXn) {
+    if (!make_tensor_map_3d(&tn, dtype, xn, a.D, a.L, a.B, nsl, nsb, C::kCh, kStep, kSeq, sw)) return false;
+  } else {
+    tn = ty;
+  }
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -569,19 +614,22 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
     return false;
   }
   dim3 grid((a.D + C::kCh - 1) / C::kCh, (a.B + kSeq - 1) / kSeq);
-  launch(kern, grid, dim3(kCg * kWs * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, a);
+  launch(kern, grid, dim3(kCg * kWs * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, tn, a);
   return true;
 }
 
 }  // namespace
 
-// Envelope: bf16, channel stride 1, no padding mask, ndim <= 16, no normalised-copy output,
+// Envelope: bf16, channel stride 1, no padding mask, ndim <= 16, a normalised-copy output (strided
+// like y) only together with the normalisation and distinct from x and y,
 // B >= 4 (rows of the MMAs are sequences), L < 2^24, and L a multiple of 32 when a state is
 // exported.  Returns false, launching nothing, outside of it.
 bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
                 long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a_in, cudaStream_t s) {
   if (g_options[OPT_DISABLE_MMA].load() != 0) return false;
-  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || xn != nullptr || a_in.mask != nullptr) return false;
+  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || a_in.mask != nullptr) return false;
+  const bool want_xn = xn != nullptr;  // second output: the normalised activations, strided like y
+  if (want_xn && (!norm || xn == y || xn == x)) return false;
   if (a_in.N > 16 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
   if (a_in.h_out && (a_in.L % kStep) != 0) return false;
   if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
@@ -604,6 +652,16 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
+  }
+  if (want_xn) {
+    // with the second output: 56-channel tiles for large problems (the 64-channel tile has no
+    // room for the two extra buffers), the 16-channel two-warp tile otherwise
+    tile = (tile == 7 || tile == 8) ? 7 : 22;
+    if (tile == 7)
+      return a_in.silu ? launch_variant<true, 7, true, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
+                       : launch_variant<true, 7, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
+    return a_in.silu ? launch_variant<true, 2, true, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
+                     : launch_variant<true, 2, false, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
   }
 #define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
   (tile == 22  ? launch_variant<NORM, 2, SILU, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)     \

@@ -42,7 +42,8 @@ def test_fused_grid(bsz, length, dim, dtype, masked):
     assert torch.equal(res["count"].cpu(), cnt)
     assert rel_l2(res["y"].float(), y) < TOL[dtype]
     assert rel_l2(res["xn"].float(), xn) < TOL[dtype]
-    assert rel_l2(res["mean"], mean) < 1e-5 and rel_l2(res["var"], var) < 1e-5
+    # bf16 without a mask runs on the tensor-core kernel, whose second moment goes through tf32 products
+    assert rel_l2(res["mean"], mean) < 1e-5 and rel_l2(res["var"], var) < (1e-5 if dtype == torch.float32 else 1e-3)
     if mask is not None:
         assert (res["xn"].cpu()[mask] == 0).all()
 
@@ -171,6 +172,8 @@ def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
     p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
     outs = []
     before = M.launch_count()
+    xn_ref = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[0]
+    ysilu_ref = O.ema_forward_recurrence(xn_ref.transpose(1, 2), *prm, None, h=h0, silu=True).transpose(1, 2)
     for disable in (0, 1):
         _lib.set_option(1, disable)
         _lib.set_option(2, tile)   # 64-, 56-, 32- or 16-channel tiles; 22: 16 channels with two warps per 16-byte column
@@ -180,10 +183,21 @@ def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
                                           want_state=want_state)
             ema = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), None,
                                     None if h0 is None else h0.cuda(), want_state=want_state, silu=True)
+            # the same call with the normalised activations as a second output (the form the Mega
+            # block uses: the tensor-core kernel writes both tiles)
+            both = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                         p, q, g, prm[4].cuda(), None, h_in=None if h0 is None else h0.cuda(),
+                                         want_state=want_state, want_normed=True, silu=True)
         finally:
             _lib.set_option(1, 0)
             _lib.set_option(2, 0)
         outs.append((fused, ema))
+        assert rel_l2(both["xn"].float(), xn_ref) < 1e-2, disable
+        assert rel_l2(both["y"].float(), ysilu_ref) < 1e-2, disable
+        assert torch.equal(both["count"].cpu(), fused["count"].cpu())
+        assert rel_l2(both["mean"], fused["mean"]) < 1e-6 and rel_l2(both["var"], fused["var"]) < 1e-6
+        if want_state:
+            assert rel_l2(both["h"], fused["h"]) < 1e-6
     xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[:4]
     yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, None, h=h0, return_state=True)
     eref, ehref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, None, h=h0, return_state=True, silu=True)
@@ -221,3 +235,53 @@ def test_tensor_core_path_offset_data(offset, scale):
                                 p, q, g, prm[4].cuda())
     assert rel_l2(res["y"].float(), yref) < 1e-2
     assert rel_l2(res["mean"], mean) < 1e-4 and rel_l2(res["var"], var) < 2e-3
+
+
+def test_config4_full_size_properties():
+    """The bench workload at full size (B=64, L=32768, D=2048, bf16; 8 GiB in, 8 GiB out), checked
+    through properties that do not need an oracle pass over 4e9 elements:
+    (1) half of the batch run alone (same tile shape) gives bit for bit the rows of the full-batch call;
+    (2) two half-length calls with the carried statistics and EMA state give the full call
+        within the bf16 tolerance;
+    (3) 3 sequences x 8 channels over the whole length against the float64 oracle."""
+    M, O = _mods()
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2 ** 30:
+        pytest.skip("needs ~26 GiB of device memory")
+    bsz, length, dim, ndim = 64, 32768, 2048, 16
+    gen = torch.Generator().manual_seed(1238)
+    params = make_ema_params(gen, dim, ndim)
+    norm = M.TimestepNorm(dim, prior_count=2).cuda().eval()
+    move = M.MultiHeadEMA(dim, ndim=ndim).cuda().eval()
+    with torch.no_grad():
+        for dst, src in zip((move.alpha, move.delta, move.beta, move.gamma, move.omega), params):
+            dst.copy_(src)
+        torch.manual_seed(1238)
+        x = torch.empty(bsz, length, dim, device="cuda", dtype=torch.bfloat16)
+        for b in range(bsz):
+            x[b] = (torch.randn(length, dim, device="cuda") * 1.2 + 0.1).to(torch.bfloat16)
+        y = M.timestep_norm_ema(norm, move, x)
+        assert torch.isfinite(y[::7, ::101]).all()
+        # (1) batch shards are independent and deterministic
+        ys = M.timestep_norm_ema(norm, move, x[16:48])
+        assert torch.equal(ys, y[16:48])
+        del ys
+        # (2) chunked == full
+        st = {}
+        half = length // 2
+        y0 = M.timestep_norm_ema(norm, move, x[:, :half], None, st)
+        y1 = M.timestep_norm_ema(norm, move, x[:, half:], None, st)
+        assert rel_l2(y0[:8].float(), y[:8, :half].float()) < 1e-2
+        assert rel_l2(y1[:8].float(), y[:8, half:].float()) < 1e-2
+        assert rel_l2(y1[-8:, -4096:].float(), y[-8:, -4096:].float()) < 1e-2
+        del y0, y1
+        # (3) a sample of rows against the oracle over the whole length
+        bs, ds = [0, 31, 63], [0, 1, 777, 1024, 1531, 2045, 2046, 2047]
+        xs = x[bs][:, :, ds].float().cpu()
+        ysam = y[bs][:, :, ds].float().cpu()
+    pc = torch.full((len(bs),), 2, dtype=torch.int64)
+    xn, _, _, _ = O.timestep_norm(xs, pc, torch.zeros(len(bs), len(ds)), torch.ones(len(bs), len(ds)),
+                                  torch.ones(len(ds)), torch.zeros(len(ds)), None, acc_dtype=torch.float64)
+    sub = [p[ds] for p in params]
+    ref = O.ema_forward_recurrence(xn.transpose(1, 2), *sub).transpose(1, 2)
+    assert rel_l2(ysam, ref) < 1e-2
