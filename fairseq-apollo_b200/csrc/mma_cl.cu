@@ -137,11 +137,13 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 
 // kWs = warps per column group: 1 (a warp owns the 8 channels of its 16-byte column) or 2 (a warp
 // owns 4 of them: half the per-thread state and tile registers, so more warps fit an SM).
-template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn>
+// kEma = false: TimestepNorm alone (y = the normalised activations; no pole matrices, no states).
+template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true>
 __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
   static_assert(!kXn || kNorm, "the normalised copy exists only with the normalisation");
+  static_assert(kEma || (kNorm && !kXn && !kSilu), "without the EMA the kernel is the plain normalisation");
   using C = Cfg<kCg, kXn>;
   constexpr int kCh = C::kCh;
   constexpr int kThreads = kCg * kWs * 32;
@@ -200,7 +202,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     const int ch = it >> 4, l = it & 15;
     const int d = d0 + ch;
     float acc = 0.f, a16 = 0.f;
-    if (d < a.D) {
+    if (kEma && d < a.D) {
       for (int n = 0; n < a.N; ++n) {
         const float pn = __ldg(a.p + (size_t)d * a.N + n), qn = __ldg(a.q + (size_t)d * a.N + n),
                     gn = __ldg(a.g + (size_t)d * a.N + n);
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   }
   __syncthreads();
   // ---- phase 2: fragment-ordered T, P, G --------------------------------------------------
-  for (int it = tid; it < kCh * 32; it += kThreads) {
+  for (int it = tid; kEma && it < kCh * 32; it += kThreads) {
     const int ch = it >> 5, ln = it & 31;
     const int gg = ln >> 2, qq = ln & 3;
     const int d = d0 + ch;
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
-      hc[e][k] = (ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+      hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
     }
     mu_run[e] = 0.f;
     m2_run[e] = 0.f;
@@ -462,6 +464,11 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) xq[h2][j] = xn[j];
         }
+        if (!kEma) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) yv[h2][j] = xn[j];
+          continue;
+        }
         // A fragment of xn: a0 (row g: t = 2q, 2q+1), a1 (row g+8), a2 (row g: t = 2q+8, 2q+9), a3 (row g+8)
         const uint32_t xa0 = pack_bf16(xn[0], xn[1]), xa2 = pack_bf16(xn[2], xn[3]);
         const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
@@ -573,7 +580,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     }
     if (kNorm && blockIdx.x == 0 && warp == 0 && hf == 0) a.count_out[bseq] = a.prev_count[bseq] + L;
   }
-  if (seq_ok && a.h_out) {
+  if (kEma && seq_ok && a.h_out) {
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
       const int d = d0 + cbase + e;
@@ -589,7 +596,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 }
 
 // xn (with its strides nsb, nsl) is the optional second output; kXn selects the kernel form.
-template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false>
+template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s, void* xn = nullptr,
                            long long nsb = 0, long long nsl = 0) {
@@ -603,7 +610,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   } else {
     tn = ty;
   }
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -630,7 +637,9 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || a_in.mask != nullptr) return false;
   const bool want_xn = xn != nullptr;  // second output: the normalised activations, strided like y
   if (want_xn && (!norm || xn == y || xn == x)) return false;
-  if (a_in.N > 16 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
+  const bool ema = a_in.N > 0;  // N = 0: TimestepNorm alone
+  if (!ema && (!norm || want_xn || a_in.silu || a_in.h_in || a_in.h_out)) return false;
+  if (a_in.N > 16 || a_in.N < 0 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
   if (a_in.h_out && (a_in.L % kStep) != 0) return false;
   if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
   // Tile width.  Large problems: 64 channels, or 56 when that fills the 148 SMs in fewer or
@@ -652,6 +661,12 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
+  }
+  if (!ema) {
+    if (tile == 2 || tile == 4) tile = 22;
+    return tile == 22  ? launch_variant<true, 2, false, 2, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+           : tile == 7 ? launch_variant<true, 7, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                       : launch_variant<true, 8, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
   }
   if (want_xn) {
     // with the second output: 56-channel tiles for large problems (the 64-channel tile has no

@@ -364,6 +364,9 @@ static int tsn_fwd_common(const void* x, void* y, int dtype, int B, int L, int D
       sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
       sa.mask = pad_mask;
       sa.cummean = cummean; sa.cumrstd = cumrstd;
+      // bf16 without a mask and without the saves for backward: the tensor-core kernel's prefix sums
+      if (!cummean && mma_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream))
+        return check_launch("timestep_norm_fwd(mma)");
       if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, true, false, sa, (cudaStream_t)stream))
         return check_launch("timestep_norm_fwd(stream)");
     }

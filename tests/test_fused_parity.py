@@ -188,10 +188,15 @@ def test_tensor_core_path(bsz, length, dim, ndim, with_state, tile):
             both = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
                                          p, q, g, prm[4].cuda(), None, h_in=None if h0 is None else h0.cuda(),
                                          want_state=want_state, want_normed=True, silu=True)
+            # TimestepNorm alone (the same kernel without the pole matrices)
+            tsn_only = M.ops.timestep_norm_fwd(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda())
         finally:
             _lib.set_option(1, 0)
             _lib.set_option(2, 0)
         outs.append((fused, ema))
+        assert rel_l2(tsn_only[0].float(), xn_ref) < 1e-2, disable
+        assert torch.equal(tsn_only[1].cpu(), fused["count"].cpu())
+        assert rel_l2(tsn_only[2], fused["mean"]) < 1e-5 and rel_l2(tsn_only[3], fused["var"]) < 1e-3
         assert rel_l2(both["xn"].float(), xn_ref) < 1e-2, disable
         assert rel_l2(both["y"].float(), ysilu_ref) < 1e-2, disable
         assert torch.equal(both["count"].cpu(), fused["count"].cpu())
