@@ -647,6 +647,8 @@ extern "C" int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
     sa.cplx = 1;
+    if (mma_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream))
+      return check_launch("tsn_cema_fwd(mma)");
     if (stream_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, true, sa, (cudaStream_t)stream))
       return check_launch("tsn_cema_fwd(stream)");
   }

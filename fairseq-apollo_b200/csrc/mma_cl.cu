@@ -42,8 +42,10 @@ constexpr int kStep = 32;  // positions per step (2 chunks of 16)
 // kXn: the kernel also writes the normalised activations (the Mega block feeds them to its value
 // projection): two more tile buffers, filled from registers and stored by TMA like the outputs, at
 // the price of one stage of the ring.
-template <int kCg, bool kXn = false>
+// kCplx: complex poles (MultiHeadComplexEMA): P, G and q^16 hold real and imaginary parts.
+template <int kCg, bool kXn = false, bool kCplx = false>
 struct Cfg {
+  static constexpr int kCm = kCplx ? 2 : 1;
   // Ring depth: a tile is fetched kStages - 1 steps before it is used.  Deeper rings were measured
   // and do not pay: a fifth stage leaves the SM too little L1 for the few spilled registers.
   static constexpr int kStages = kXn ? 3 : 4;
@@ -53,10 +55,10 @@ struct Cfg {
   static constexpr int kOffStages = 0;
   static constexpr int kOffXn = kOffStages + kStages * kStageBytes;  // kXn: [2][stage] normalised tiles
   static constexpr int kOffT = kOffXn + (kXn ? 2 * kStageBytes : 0);  // [kCh][2][32] u32
-  static constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [kCh][32] uint4
-  static constexpr int kOffG = kOffP + kCh * 4 * 32 * 4;            // [kCh][32] uint4
-  static constexpr int kOffA = kOffG + kCh * 4 * 32 * 4;            // [kCh][16] f32  (q^16)
-  static constexpr int kOffWB = kOffA + kCh * 16 * 4;               // [kCh][2] f32
+  static constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [kCh][kCm][32] uint4
+  static constexpr int kOffG = kOffP + kCm * kCh * 4 * 32 * 4;      // [kCh][kCm][32] uint4
+  static constexpr int kOffA = kOffG + kCm * kCh * 4 * 32 * 4;      // [kCh][16] f32 (q^16; kCplx: float2)
+  static constexpr int kOffWB = kOffA + kCm * kCh * 16 * 4;         // [kCh][2] f32
   static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
   static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages], xfree[2]
   static constexpr int kSmemBytes = kOffBar + (2 * kStages + 2) * 8 + 1024;  // + alignment slack
@@ -120,6 +122,16 @@ __device__ __forceinline__ float rcp_fast(float v) {
 __device__ __forceinline__ float qpow(float logq, bool qpos, int l) {
   return l == 0 ? 1.0f : (qpos ? __expf((float)l * logq) : 0.0f);
 }
+// (qr + i qi)^l
+__device__ __forceinline__ float2 cpow(float qr, float qi, int l) {
+  if (l == 0) return make_float2(1.f, 0.f);
+  const float rho = hypotf(qr, qi);
+  if (!(rho > 0.f)) return make_float2(0.f, 0.f);
+  const float mag = __expf((float)l * __logf(rho));
+  float sn, cs;
+  sincosf((float)l * atan2f(qi, qr), &sn, &cs);
+  return make_float2(mag * cs, mag * sn);
+}
 __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
@@ -138,14 +150,16 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 // kWs = warps per column group: 1 (a warp owns the 8 channels of its 16-byte column) or 2 (a warp
 // owns 4 of them: half the per-thread state and tile registers, so more warps fit an SM).
 // kEma = false: TimestepNorm alone (y = the normalised activations; no pole matrices, no states).
-template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true>
+template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false>
 __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
   static_assert(!kXn || kNorm, "the normalised copy exists only with the normalisation");
   static_assert(kEma || (kNorm && !kXn && !kSilu), "without the EMA the kernel is the plain normalisation");
-  using C = Cfg<kCg, kXn>;
+  static_assert(!kCplx || kEma, "complex poles need the EMA");
+  using C = Cfg<kCg, kXn, kCplx>;
   constexpr int kCh = C::kCh;
+  constexpr int kCm = C::kCm;
   constexpr int kThreads = kCg * kWs * 32;
   constexpr int kStages = C::kStages;
   constexpr int kE = 8 / kWs;   // channels per warp
@@ -201,20 +215,37 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   for (int it = tid; it < kCh * 16; it += kThreads) {
     const int ch = it >> 4, l = it & 15;
     const int d = d0 + ch;
-    float acc = 0.f, a16 = 0.f;
+    float acc = 0.f, a16 = 0.f, a16i = 0.f;
     if (kEma && d < a.D) {
       for (int n = 0; n < a.N; ++n) {
-        const float pn = __ldg(a.p + (size_t)d * a.N + n), qn = __ldg(a.q + (size_t)d * a.N + n),
-                    gn = __ldg(a.g + (size_t)d * a.N + n);
-        const bool qpos = qn > 0.f;
-        const float lq = qpos ? __logf(qn) : 0.f;
-        acc = fmaf(pn * gn, qpow(lq, qpos, l), acc);
-        if (n == l) a16 = qpow(lq, qpos, 16);
+        const size_t c = (size_t)d * a.N + n;
+        const float pn = __ldg(a.p + c);
+        if (kCplx) {  // k[l] = sum_n p Re(gamma q^l)
+          const float qr = __ldg(a.q + 2 * c), qi = __ldg(a.q + 2 * c + 1);
+          const float2 ql = cpow(qr, qi, l);
+          acc = fmaf(pn, __ldg(a.g + 2 * c) * ql.x - __ldg(a.g + 2 * c + 1) * ql.y, acc);
+          if (n == l) {
+            const float2 q16 = cpow(qr, qi, 16);
+            a16 = q16.x;
+            a16i = q16.y;
+          }
+        } else {
+          const float qn = __ldg(a.q + c), gn = __ldg(a.g + c);
+          const bool qpos = qn > 0.f;
+          const float lq = qpos ? __logf(qn) : 0.f;
+          acc = fmaf(pn * gn, qpow(lq, qpos, l), acc);
+          if (n == l) a16 = qpow(lq, qpos, 16);
+        }
       }
       if (l == 0) acc += __ldg(a.omega + d);
     }
     Kp[it] = acc;
-    Ac[it] = a16;  // entry (ch, pole l); poles >= N stay 0
+    if (kCplx) {
+      Ac[2 * it] = a16;
+      Ac[2 * it + 1] = a16i;
+    } else {
+      Ac[it] = a16;  // entry (ch, pole l); poles >= N stay 0
+    }
     if (l < 2) {
       float v = (l == 0) ? 1.f : 0.f;
       if (kNorm && d < a.D) v = (l == 0) ? __ldg(a.gamma + d) : __ldg(a.beta + d);
@@ -231,6 +262,51 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
     auto tap = [&](int l) -> float { return (l >= 0 && l < 16) ? Kp[ch * 16 + l] : 0.f; };
     Tc[(ch * 2 + 0) * 32 + ln] = bf16_bits(tap(gg - 2 * qq)) | (bf16_bits(tap(gg - 2 * qq - 1)) << 16);
     Tc[(ch * 2 + 1) * 32 + ln] = bf16_bits(tap(8 + gg - 2 * qq)) | (bf16_bits(tap(8 + gg - 2 * qq - 1)) << 16);
+    if (kCplx) {
+      // the same fragments with complex powers: P gives Re and Im of the local states, G takes
+      // Re(gamma q^(t'+1)) against Re h and -Im(gamma q^(t'+1)) against Im h
+      uint32_t prr[4], pri[4], grr[4], gri[4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const int n = 8 * nb + gg;
+        float pn = 0.f, qr = 0.f, qi = 0.f;
+        if (d < a.D && n < a.N) {
+          const size_t c = (size_t)d * a.N + n;
+          pn = __ldg(a.p + c);
+          qr = __ldg(a.q + 2 * c);
+          qi = __ldg(a.q + 2 * c + 1);
+        }
+        const float2 e0 = cpow(qr, qi, 15 - 2 * qq), e1 = cpow(qr, qi, 14 - 2 * qq);
+        const float2 e2 = cpow(qr, qi, 7 - 2 * qq), e3 = cpow(qr, qi, 6 - 2 * qq);
+        prr[nb * 2 + 0] = bf16_bits(pn * e0.x) | (bf16_bits(pn * e1.x) << 16);
+        pri[nb * 2 + 0] = bf16_bits(pn * e0.y) | (bf16_bits(pn * e1.y) << 16);
+        prr[nb * 2 + 1] = bf16_bits(pn * e2.x) | (bf16_bits(pn * e3.x) << 16);
+        pri[nb * 2 + 1] = bf16_bits(pn * e2.y) | (bf16_bits(pn * e3.y) << 16);
+        const int tp = 8 * nb + gg;
+        float cr[4], ci[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int pole = 2 * qq + (k & 1) + ((k >> 1) << 3);
+          cr[k] = ci[k] = 0.f;
+          if (d < a.D && pole < a.N) {
+            const size_t c = (size_t)d * a.N + pole;
+            const float2 w = cpow(__ldg(a.q + 2 * c), __ldg(a.q + 2 * c + 1), tp + 1);
+            const float gre = __ldg(a.g + 2 * c), gim = __ldg(a.g + 2 * c + 1);
+            cr[k] = gre * w.x - gim * w.y;
+            ci[k] = -(gre * w.y + gim * w.x);
+          }
+        }
+        grr[nb * 2 + 0] = bf16_bits(cr[0]) | (bf16_bits(cr[1]) << 16);
+        grr[nb * 2 + 1] = bf16_bits(cr[2]) | (bf16_bits(cr[3]) << 16);
+        gri[nb * 2 + 0] = bf16_bits(ci[0]) | (bf16_bits(ci[1]) << 16);
+        gri[nb * 2 + 1] = bf16_bits(ci[2]) | (bf16_bits(ci[3]) << 16);
+      }
+      Pc[(ch * 2 + 0) * 32 + ln] = make_uint4(prr[0], prr[1], prr[2], prr[3]);
+      Pc[(ch * 2 + 1) * 32 + ln] = make_uint4(pri[0], pri[1], pri[2], pri[3]);
+      Gc[(ch * 2 + 0) * 32 + ln] = make_uint4(grr[0], grr[1], grr[2], grr[3]);
+      Gc[(ch * 2 + 1) * 32 + ln] = make_uint4(gri[0], gri[1], gri[2], gri[3]);
+      continue;
+    }
     uint32_t pr[4], gr[4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
@@ -271,6 +347,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   const int bseq = b0 + g;
   const bool seq_ok = bseq < a.B;
   float hc[kE][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
+  float hci[kCplx ? kE : 1][4];  // kCplx: their imaginary parts
   float mu_run[kE], m2_run[kE], s1_run[kE];  // running mean, sum of squared deviations, sum of x
   float nbase = 1.f;
   const int cbase = warp * 8 + hf * kE;  // first channel of this warp inside the tile
@@ -281,7 +358,14 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
-      hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+      if (kCplx) {
+        const bool have = ok && a.h_in && pole < a.N;
+        const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
+        hc[e][k] = have ? __ldg(a.h_in + c) : 0.f;
+        hci[e][k] = have ? __ldg(a.h_in + c + 1) : 0.f;
+      } else {
+        hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+      }
     }
     mu_run[e] = 0.f;
     m2_run[e] = 0.f;
@@ -474,37 +558,76 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
         const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
         const uint2 tr = make_uint2(lds32(sm_s + kOffT + ((ch * 2 + 0) * 32 + lane) * 4),
                                     lds32(sm_s + kOffT + ((ch * 2 + 1) * 32 + lane) * 4));
-        const uint4 pr = lds128(sm_s + kOffP + (ch * 32 + lane) * 16);
-        const uint4 gr = lds128(sm_s + kOffG + (ch * 32 + lane) * 16);
-        const uint2 aq0u = lds64(sm_s + kOffA + (ch * 16 + 2 * q) * 4);
-        const uint2 aq1u = lds64(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 4);
-        const float2 aq0 = make_float2(__uint_as_float(aq0u.x), __uint_as_float(aq0u.y));
-        const float2 aq1 = make_float2(__uint_as_float(aq1u.x), __uint_as_float(aq1u.y));
-        // local state contributions of the two chunks
-        float H0[4], H1[4];
-        mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y, 0.f, 0.f, 0.f, 0.f);  // poles 2q, 2q+1
-        mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
         float W0[4], W1[4];  // Toeplitz term of the outputs (positions 0..7 and 8..15 of each chunk)
         mma_bf16(W0, xa0, xa1, xa2, xa3, tr.x, 0u, 0.f, 0.f, 0.f, 0.f);
         mma_bf16(W1, xa0, xa1, xa2, xa3, tr.y, tr.x, 0.f, 0.f, 0.f, 0.f);
-        // states entering chunk 0 (= carried) and chunk 1, and the new carry
-        const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
-        float hs1[4];
-        hs1[0] = fmaf(aq0.x, hs0[0], H0[0]);
-        hs1[1] = fmaf(aq0.y, hs0[1], H0[1]);
-        hs1[2] = fmaf(aq1.x, hs0[2], H1[0]);
-        hs1[3] = fmaf(aq1.y, hs0[3], H1[1]);
-        hc[e][0] = fmaf(aq0.x, hs1[0], H0[2]);
-        hc[e][1] = fmaf(aq0.y, hs1[1], H0[3]);
-        hc[e][2] = fmaf(aq1.x, hs1[2], H1[2]);
-        hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
-        const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
-        const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
-        // outputs: the carried-state term accumulates onto the Toeplitz term, which does not
-        // wait for the states (W0, W1 are issued alongside H0, H1 above)
         float Y0[4], Y1[4];
-        mma_bf16(Y0, ha0, ha1, ha2, ha3, gr.x, gr.y, W0[0], W0[1], W0[2], W0[3]);
-        mma_bf16(Y1, ha0, ha1, ha2, ha3, gr.z, gr.w, W1[0], W1[1], W1[2], W1[3]);
+        if (kCplx) {
+          const uint4 prr = lds128(sm_s + kOffP + ((ch * 2 + 0) * 32 + lane) * 16);
+          const uint4 pri = lds128(sm_s + kOffP + ((ch * 2 + 1) * 32 + lane) * 16);
+          const uint4 grr = lds128(sm_s + kOffG + ((ch * 2 + 0) * 32 + lane) * 16);
+          const uint4 gri = lds128(sm_s + kOffG + ((ch * 2 + 1) * 32 + lane) * 16);
+          // q^16 of poles 2q, 2q+1 and 8+2q, 9+2q as (re, im) pairs
+          const uint4 a0u = lds128(sm_s + kOffA + (ch * 16 + 2 * q) * 8);
+          const uint4 a1u = lds128(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 8);
+          const float ar[4] = {__uint_as_float(a0u.x), __uint_as_float(a0u.z), __uint_as_float(a1u.x), __uint_as_float(a1u.z)};
+          const float ai[4] = {__uint_as_float(a0u.y), __uint_as_float(a0u.w), __uint_as_float(a1u.y), __uint_as_float(a1u.w)};
+          float Hr0[4], Hr1[4], Hi0[4], Hi1[4];
+          mma_bf16(Hr0, xa0, xa1, xa2, xa3, prr.x, prr.y, 0.f, 0.f, 0.f, 0.f);
+          mma_bf16(Hr1, xa0, xa1, xa2, xa3, prr.z, prr.w, 0.f, 0.f, 0.f, 0.f);
+          mma_bf16(Hi0, xa0, xa1, xa2, xa3, pri.x, pri.y, 0.f, 0.f, 0.f, 0.f);
+          mma_bf16(Hi1, xa0, xa1, xa2, xa3, pri.z, pri.w, 0.f, 0.f, 0.f, 0.f);
+          // local contributions per pole k: chunk 0 (row g) and chunk 1 (row g + 8)
+          const float l0r[4] = {Hr0[0], Hr0[1], Hr1[0], Hr1[1]}, l0i[4] = {Hi0[0], Hi0[1], Hi1[0], Hi1[1]};
+          const float l1r[4] = {Hr0[2], Hr0[3], Hr1[2], Hr1[3]}, l1i[4] = {Hi0[2], Hi0[3], Hi1[2], Hi1[3]};
+          float s0r[4], s0i[4], s1r[4], s1i[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            s0r[k] = hc[e][k];
+            s0i[k] = hci[e][k];
+            s1r[k] = fmaf(ar[k], s0r[k], fmaf(-ai[k], s0i[k], l0r[k]));
+            s1i[k] = fmaf(ar[k], s0i[k], fmaf(ai[k], s0r[k], l0i[k]));
+            hc[e][k] = fmaf(ar[k], s1r[k], fmaf(-ai[k], s1i[k], l1r[k]));
+            hci[e][k] = fmaf(ar[k], s1i[k], fmaf(ai[k], s1r[k], l1i[k]));
+          }
+          const uint32_t hr0 = pack_bf16(s0r[0], s0r[1]), hr1 = pack_bf16(s1r[0], s1r[1]);
+          const uint32_t hr2 = pack_bf16(s0r[2], s0r[3]), hr3 = pack_bf16(s1r[2], s1r[3]);
+          const uint32_t hi0 = pack_bf16(s0i[0], s0i[1]), hi1 = pack_bf16(s1i[0], s1i[1]);
+          const uint32_t hi2 = pack_bf16(s0i[2], s0i[3]), hi3 = pack_bf16(s1i[2], s1i[3]);
+          float Z0[4], Z1[4];
+          mma_bf16(Z0, hr0, hr1, hr2, hr3, grr.x, grr.y, W0[0], W0[1], W0[2], W0[3]);
+          mma_bf16(Z1, hr0, hr1, hr2, hr3, grr.z, grr.w, W1[0], W1[1], W1[2], W1[3]);
+          mma_bf16(Y0, hi0, hi1, hi2, hi3, gri.x, gri.y, Z0[0], Z0[1], Z0[2], Z0[3]);
+          mma_bf16(Y1, hi0, hi1, hi2, hi3, gri.z, gri.w, Z1[0], Z1[1], Z1[2], Z1[3]);
+        } else {
+          const uint4 pr = lds128(sm_s + kOffP + (ch * 32 + lane) * 16);
+          const uint4 gr = lds128(sm_s + kOffG + (ch * 32 + lane) * 16);
+          const uint2 aq0u = lds64(sm_s + kOffA + (ch * 16 + 2 * q) * 4);
+          const uint2 aq1u = lds64(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 4);
+          const float2 aq0 = make_float2(__uint_as_float(aq0u.x), __uint_as_float(aq0u.y));
+          const float2 aq1 = make_float2(__uint_as_float(aq1u.x), __uint_as_float(aq1u.y));
+          // local state contributions of the two chunks
+          float H0[4], H1[4];
+          mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y, 0.f, 0.f, 0.f, 0.f);  // poles 2q, 2q+1
+          mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
+          // states entering chunk 0 (= carried) and chunk 1, and the new carry
+          const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
+          float hs1[4];
+          hs1[0] = fmaf(aq0.x, hs0[0], H0[0]);
+          hs1[1] = fmaf(aq0.y, hs0[1], H0[1]);
+          hs1[2] = fmaf(aq1.x, hs0[2], H1[0]);
+          hs1[3] = fmaf(aq1.y, hs0[3], H1[1]);
+          hc[e][0] = fmaf(aq0.x, hs1[0], H0[2]);
+          hc[e][1] = fmaf(aq0.y, hs1[1], H0[3]);
+          hc[e][2] = fmaf(aq1.x, hs1[2], H1[2]);
+          hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
+          const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
+          const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
+          // outputs: the carried-state term accumulates onto the Toeplitz term, which does not
+          // wait for the states (W0, W1 are issued alongside H0, H1 above)
+          mma_bf16(Y0, ha0, ha1, ha2, ha3, gr.x, gr.y, W0[0], W0[1], W0[2], W0[3]);
+          mma_bf16(Y1, ha0, ha1, ha2, ha3, gr.z, gr.w, W1[0], W1[1], W1[2], W1[3]);
+        }
         yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
         if (kSilu) {
@@ -588,7 +711,15 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
-          if (pole < a.N) a.h_out[((size_t)bseq * a.D + d) * a.N + pole] = hc[e][k];
+          if (pole < a.N) {
+            if (kCplx) {
+              const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
+              a.h_out[c] = hc[e][k];
+              a.h_out[c + 1] = hci[e][k];
+            } else {
+              a.h_out[((size_t)bseq * a.D + d) * a.N + pole] = hc[e][k];
+            }
+          }
         }
       }
     }
@@ -596,11 +727,11 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 }
 
 // xn (with its strides nsb, nsl) is the optional second output; kXn selects the kernel form.
-template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true>
+template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true, bool kCplx = false>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s, void* xn = nullptr,
                            long long nsb = 0, long long nsl = 0) {
-  using C = Cfg<kCg, kXn>;
+  using C = Cfg<kCg, kXn, kCplx>;
   const CUtensorMapSwizzle sw = kCg == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUtensorMap tx, ty, tn;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
@@ -610,7 +741,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   } else {
     tn = ty;
   }
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma, kCplx>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -661,6 +792,16 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
+  }
+  if (a_in.cplx) {
+    // complex poles (fused TimestepNorm -> MultiHeadComplexEMA): the matrices of a channel take
+    // 2.4 KB, so the 16-channel tile with two warps per column (three CTAs per SM) serves all sizes
+    if (!norm || !ema) return false;
+    if (want_xn)
+      return a_in.silu ? launch_variant<true, 2, true, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
+                       : launch_variant<true, 2, false, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
+    return a_in.silu ? launch_variant<true, 2, true, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                     : launch_variant<true, 2, false, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
   }
   if (!ema) {
     if (tile == 2 || tile == 4) tile = 22;

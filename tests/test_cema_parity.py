@@ -144,3 +144,52 @@ def test_fused_timestep_norm_complex_ema(bsz, length, dim, ndim, dtype):
             parts.append(M.timestep_norm_ema(norm, move, x[:, i:i + step].cuda(), mask[:, i:i + step].cuda(), st, 'silu'))
         assert rel_l2(torch.cat(parts, 1).float(), y_ref) < TOL[dtype]
         assert move._get_input_buffer(st)["prev_state"].dtype == torch.complex64
+
+
+@pytest.mark.parametrize("bsz,length,dim,ndim", [(4, 32, 64, 16), (8, 96, 64, 16), (9, 100, 72, 16), (16, 257, 200, 5),
+                                                 (8, 1024, 136, 16)])
+@pytest.mark.parametrize("normed", [False, True])
+@pytest.mark.parametrize("silu", [False, True])
+def test_complex_tensor_core_path(bsz, length, dim, ndim, normed, silu):
+    """bf16, no padding: fused TimestepNorm -> complex EMA on the tensor-core kernel (complex P, G
+    and q^16 fragments) against the oracle and against the streamed kernel (a test switch disables
+    the tensor-core path); full pass, then 32-step chunks with the carried complex state."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(bsz * 131 + length + dim)
+    torch.manual_seed(bsz * 131 + length + dim)
+    move = M.MultiHeadComplexEMA(dim, ndim=ndim).cuda().eval()
+    norm = M.TimestepNorm(dim, prior_count=2).cuda().eval()
+    with torch.no_grad():
+        move.gamma[:, :, 1].normal_(0, 1)
+        norm.weight.normal_(0, 0.1)
+        norm.bias.normal_(0, 0.1)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.2).to(torch.bfloat16)
+    prm = [getattr(move, k).detach().cpu() for k in ("alpha", "delta", "theta", "gamma", "omega")]
+    xn_ref = O.timestep_norm(x.float(), torch.full((bsz,), 2, dtype=torch.int64), torch.zeros(bsz, dim),
+                             torch.ones(bsz, dim), norm.weight.detach().cpu() + 1.0, norm.bias.detach().cpu(), None)[0]
+    y_ref = O.cema_forward_recurrence(xn_ref.transpose(1, 2), *prm, None, silu=silu).transpose(1, 2)
+    act = 'silu' if silu else None
+    outs = []
+    before = M.launch_count()
+    with torch.no_grad():
+        for disable in (0, 1):
+            _lib.set_option(1, disable)
+            try:
+                res = M.timestep_norm_ema(norm, move, x.cuda(), None, None, act, return_normed=normed)
+                st, parts = {}, []
+                for i in range(0, length, 32):
+                    parts.append(M.timestep_norm_ema(norm, move, x[:, i:i + 32].cuda(), None, st, act))
+            finally:
+                _lib.set_option(1, 0)
+            y = res[0] if normed else res
+            assert rel_l2(y.float(), y_ref) < 1e-2, disable
+            if normed:
+                assert rel_l2(res[1].float(), xn_ref) < 1e-2, disable
+            assert rel_l2(torch.cat(parts, 1).float(), y_ref) < 1e-2, disable
+            outs.append((y, move._get_input_buffer(st)["prev_state"]))
+    assert rel_l2(outs[0][0].float(), outs[1][0].float()) < 1e-2
+    assert outs[0][1].dtype == torch.complex64
+    if length % 32 == 0:   # the final carried states of the two implementations
+        assert rel_l2(torch.view_as_real(outs[0][1]), torch.view_as_real(outs[1][1])) < 1e-2
+    assert _lib.device_error() == 0
