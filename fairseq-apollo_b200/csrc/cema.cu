@@ -577,6 +577,8 @@ extern "C" int mega_cema_fwd(const void* x, void* y, int dtype, int B, int D, in
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
     sa.cplx = 1;
+    if (mma_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, sa, (cudaStream_t)stream))
+      return check_launch("cema_fwd(mma)");
     if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, true, sa, (cudaStream_t)stream))
       return check_launch("cema_fwd(stream)");
   }

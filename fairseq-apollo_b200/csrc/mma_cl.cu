@@ -796,7 +796,10 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   if (a_in.cplx) {
     // complex poles (fused TimestepNorm -> MultiHeadComplexEMA): the matrices of a channel take
     // 2.4 KB, so the 16-channel tile with two warps per column (three CTAs per SM) serves all sizes
-    if (!norm || !ema) return false;
+    if (!ema) return false;
+    if (!norm)  // the complex layer alone
+      return a_in.silu ? launch_variant<false, 2, true, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                       : launch_variant<false, 2, false, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
     if (want_xn)
       return a_in.silu ? launch_variant<true, 2, true, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
                        : launch_variant<true, 2, false, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);

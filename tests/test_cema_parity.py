@@ -190,6 +190,15 @@ def test_complex_tensor_core_path(bsz, length, dim, ndim, normed, silu):
             outs.append((y, move._get_input_buffer(st)["prev_state"]))
     assert rel_l2(outs[0][0].float(), outs[1][0].float()) < 1e-2
     assert outs[0][1].dtype == torch.complex64
+    if not normed:   # the complex layer alone (no normalisation) on the same kernel
+        e_ref = O.cema_forward_recurrence(x.float().transpose(1, 2), *prm, None, silu=silu)
+        with torch.no_grad():
+            e = move(x.cuda().transpose(1, 2), None, None, act)
+            st2, parts2 = {}, []
+            for i in range(0, length, 32):
+                parts2.append(move(x[:, i:i + 32].cuda().transpose(1, 2), None, st2, act))
+        assert rel_l2(e.float(), e_ref) < 1e-2
+        assert rel_l2(torch.cat(parts2, -1).float(), e_ref) < 1e-2
     if length % 32 == 0:   # the final carried states of the two implementations
         assert rel_l2(torch.view_as_real(outs[0][1]), torch.view_as_real(outs[1][1])) < 1e-2
     assert _lib.device_error() == 0
