@@ -33,6 +33,8 @@ SIGNATURES = {
                          c_p, c_p, c_p, c_p, c_i, c_p, c_u, c_p],
     "mega_tsn_ema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
                           c_p, c_u, c_p],
+    "mega_tsn_cema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
+                           c_p, c_u, c_p],
     "mega_gate_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],

@@ -216,13 +216,19 @@ __global__ void __launch_bounds__(128) cema_step_kernel(const T* x, T* y, int B,
 // The same step with LN = N / 2 lanes per (batch, channel): a lane owns two complex poles (one
 // 16-byte state vector), so a warp moves whole contiguous state rows, and a thread walks BB
 // batch entries with its coefficients in registers.  h_in may be NULL and may alias h_out.
+// With use_norm the TimestepNorm update of the token runs first (redundantly in the LN lanes;
+// lane 0 stores the statistics), as in the real layer's step kernel.
 template <typename T, int LN, int BB>
-__global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restrict__ x, T* __restrict__ y, int B,
-                                                              int D, const float* __restrict__ p,
+__global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                              T* __restrict__ xn_out, int B, int D,
+                                                              const long long* count, float* mean, float* var,
+                                                              const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta, float eps,
+                                                              const float* __restrict__ p,
                                                               const float* __restrict__ q,
                                                               const float* __restrict__ g,
                                                               const float* __restrict__ omega, const float* h_in,
-                                                              float* h_out, int silu) {
+                                                              float* h_out, int silu, int use_norm) {
   constexpr int N = LN * 2;
   const int sub = threadIdx.x % LN;
   const int d = blockIdx.x * (128 / LN) + threadIdx.x / LN;
@@ -230,35 +236,54 @@ __global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restric
   const int b0 = blockIdx.y * BB;
   float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), gv = qv;
   float2 pv = make_float2(0.f, 0.f);
-  float om = 0.f;
+  float om = 0.f, gam = 1.f, bet = 0.f;
   if (live) {
     qv = __ldg(reinterpret_cast<const float4*>(q + (size_t)d * N * 2) + sub);
     gv = __ldg(reinterpret_cast<const float4*>(g + (size_t)d * N * 2) + sub);
     pv = __ldg(reinterpret_cast<const float2*>(p + (size_t)d * N) + sub);
     om = __ldg(omega + d);
+    if (use_norm) {
+      gam = __ldg(gamma + d);
+      bet = __ldg(beta + d);
+    }
   }
   float4 hv[BB];
-  float xv[BB];
+  float xv[BB], mu[BB], vr[BB], coef[BB];
 #pragma unroll
   for (int j = 0; j < BB; ++j) {
     const int b = b0 + j;
     const size_t gid = (size_t)b * D + d;
     hv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    xv[j] = 0.f;
+    xv[j] = mu[j] = 0.f;
+    vr[j] = coef[j] = 1.f;
     if (live && b < B) {
       if (h_in) hv[j] = *(reinterpret_cast<const float4*>(h_in + gid * N * 2) + sub);
       xv[j] = Elem<T>::ld(x + gid);
+      if (use_norm) {
+        mu[j] = mean[gid];
+        vr[j] = var[gid];
+        coef[j] = __frcp_rn((float)(count[b] + 1));
+      }
     }
   }
 #pragma unroll
   for (int j = 0; j < BB; ++j) {
     const int b = b0 + j;
     const size_t gid = (size_t)b * D + d;
+    float xin = xv[j];
+    float m1 = 0.f, m2 = 0.f;
+    if (use_norm) {
+      const float d1 = xin - mu[j];
+      m1 = fmaf(coef[j], d1, mu[j]);
+      const float d2 = fmaf(d1, xin - m1, -vr[j]);
+      m2 = fmaf(coef[j], d2, vr[j]);
+      xin = fmaf((xin - m1) * rsqrtf(m2 + eps), gam, bet);
+    }
     const float4 h = hv[j];
     float4 hn;
-    hn.x = fmaf(qv.x, h.x, fmaf(-qv.y, h.y, pv.x * xv[j]));
+    hn.x = fmaf(qv.x, h.x, fmaf(-qv.y, h.y, pv.x * xin));
     hn.y = fmaf(qv.y, h.x, qv.x * h.y);
-    hn.z = fmaf(qv.z, h.z, fmaf(-qv.w, h.w, pv.y * xv[j]));
+    hn.z = fmaf(qv.z, h.z, fmaf(-qv.w, h.w, pv.y * xin));
     hn.w = fmaf(qv.w, h.z, qv.z * h.w);
     float acc = (gv.x * hn.x - gv.y * hn.y) + (gv.z * hn.z - gv.w * hn.w);
 #pragma unroll
@@ -266,18 +291,31 @@ __global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restric
     if (live && b < B) {
       *(reinterpret_cast<float4*>(h_out + gid * N * 2) + sub) = hn;
       if (sub == 0) {
-        float v = fmaf(om, xv[j], acc);
+        float v = fmaf(om, xin, acc);
         if (silu) v = siluf_(v);
         Elem<T>::st(y + gid, v);
+        if (use_norm) {
+          mean[gid] = m1;
+          var[gid] = m2;
+          if (xn_out) Elem<T>::st(xn_out + gid, xin);
+        }
       }
     }
   }
 }
 
+// One thread per sequence bumps the counts after the element kernel has read them.
+__global__ void cema_count_step_kernel(long long* count, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) count[b] += 1;
+}
+
 template <typename T>
-static bool launch_cema_step_lanes(const T* x, T* y, int B, int D, int N, const float* p, const float* q,
-                                   const float* g, const float* omega, const float* h_in, float* h_out, int silu,
-                                   void* stream) {
+static bool launch_cema_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, const long long* count,
+                                   float* mean, float* var, const float* gamma, const float* beta, float eps,
+                                   const float* p, const float* q, const float* g, const float* omega,
+                                   const float* h_in, float* h_out, int silu, void* stream) {
+  const int use_norm = count != nullptr;
   if (N != 2 && N != 4 && N != 8 && N != 16 && N != 32) return false;
   if (!aligned_to(h_out, 16) || (h_in && !aligned_to(h_in, 16)) || !aligned_to(p, 8) || !aligned_to(q, 16) ||
       !aligned_to(g, 16))
@@ -287,7 +325,8 @@ static bool launch_cema_step_lanes(const T* x, T* y, int B, int D, int N, const 
   dim3 grid((unsigned)((D + 128 / ln - 1) / (128 / ln)), (unsigned)((B + BB - 1) / BB));
   if (grid.y > 65535) return false;
 #define MEGA_CEMA_STEP_LANES(LNV) \
-  launch(cema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, B, D, p, q, g, omega, h_in, h_out, silu)
+  launch(cema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, xn_out, B, D, count, mean, var, gamma, \
+         beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm)
   if (ln == 1) MEGA_CEMA_STEP_LANES(1);
   else if (ln == 2) MEGA_CEMA_STEP_LANES(2);
   else if (ln == 4) MEGA_CEMA_STEP_LANES(4);
@@ -617,12 +656,32 @@ extern "C" int mega_cema_step(const void* x, void* y, int dtype, int B, int D, c
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
   const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
   bool lanes = false;
-  MEGA_DISPATCH_DTYPE(dtype, lanes = launch_cema_step_lanes<T>((const T*)x, (T*)y, B, D, N, p, q, gamma_hat, omega,
-                                                              h_in, h_out, silu, stream));
+  MEGA_DISPATCH_DTYPE(dtype, lanes = launch_cema_step_lanes<T>((const T*)x, (T*)y, (T*)nullptr, B, D, N, nullptr,
+                                                              nullptr, nullptr, nullptr, nullptr, 0.f, p, q,
+                                                              gamma_hat, omega, h_in, h_out, silu, stream));
   if (lanes) return check_launch("cema_step(lanes)");
   MEGA_DISPATCH_DTYPE(dtype, launch(cema_step_kernel<T>, grid, 128, 0, stream, (const T*)x, (T*)y, B, D, N, p, q,
                                     gamma_hat, omega, h_in, h_out, (flags & MEGA_EMA_SILU) ? 1 : 0));
   return check_launch("cema_step");
+}
+
+extern "C" int mega_tsn_cema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D, int64_t* count,
+                                  float* mean, float* var, const float* gamma, const float* beta, double eps,
+                                  const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                                  float* h, unsigned flags, mega_stream_t stream) {
+  if (!x || !y || !count || !mean || !var || !gamma || !beta || !p || !q || !gamma_hat || !omega || !h)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  bool lanes = false;
+  MEGA_DISPATCH_DTYPE(dtype, lanes = launch_cema_step_lanes<T>((const T*)x, (T*)y, (T*)xn_out, B, D, N,
+                                                              (const long long*)count, mean, var, gamma, beta,
+                                                              (float)eps, p, q, gamma_hat, omega, h, h, silu, stream));
+  if (!lanes) return MEGA_ERR_UNSUPPORTED;  // pole counts other than 2, 4, 8, 16, 32, or unaligned states
+  launch(cema_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
+  return check_launch("tsn_cema_step");
 }
 
 extern "C" int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D, int64_t xsb,

@@ -33,7 +33,7 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
         mx = move(xn.transpose(1, 2), padding_mask, incremental_state, activation).transpose(1, 2)
         return (mx, xn) if return_normed else mx
     if (incremental_state is not None and x.size(1) == 1 and padding_mask is None and x.is_contiguous()
-            and not move.complex):
+            and (not move.complex or move.ndim in (2, 4, 8, 16, 32))):
         return _decode_step(norm, move, x, incremental_state, activation, return_normed)
     prev_count, prev_mean, prev_var, nstate = norm.initial_statistics(x.size(0), incremental_state)
     p, q, g = move.coeffs()
@@ -73,13 +73,18 @@ def sequence_norm_ema(norm: SequenceNorm, move: MultiHeadEMA, x: Tensor, padding
 def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):
     """fp32, contiguous copies of everything the decode kernel reads, cached until a parameter
     is modified (checked through the tensors' version counters)."""
-    tensors = (norm.weight, norm.bias, move.alpha, move.delta, move.beta, move.gamma, move.omega)
+    third = move.theta if move.complex else move.beta
+    tensors = (norm.weight, norm.bias, move.alpha, move.delta, third, move.gamma, move.omega)
     key = tuple((t.data_ptr(), t._version) for t in tensors)
     cache = getattr(move, "_decode_cache", None)
     if cache is None or cache[0] != key:
-        p, q, g = ops.ema_coeffs(move.alpha, move.delta, move.beta, move.gamma)
+        if move.complex:   # q, g complex64 (K, N): the kernel reads them as interleaved (re, im) floats
+            p, q, g = ops.cema_coeffs(move.alpha, move.delta, move.theta, move.gamma)
+            p, q, g = p.reshape(p.shape[0], -1).contiguous(), q.reshape(q.shape[0], -1).contiguous(), g.contiguous()
+        else:
+            p, q, g = ops.ema_coeffs(move.alpha, move.delta, move.beta, move.gamma)
         cache = (key, (norm.weight.detach().float() + 1.0).contiguous(), norm.bias.detach().float().contiguous(),
-                 p, q, g, move.omega.detach().float().contiguous())
+                 p, q, g, move.omega.detach().float().reshape(-1).contiguous())
         move._decode_cache = cache
     return cache[1:]
 
@@ -99,15 +104,17 @@ def _decode_step(norm, move, x, incremental_state, activation, return_normed):
             nstate[k] = t.float().contiguous()
     estate = move._get_input_buffer(incremental_state)
     h = estate.get('prev_state')
+    sdtype = torch.complex64 if move.complex else torch.float32
     if h is None:
-        h = torch.zeros(bsz, dim, move.ndim, device=x.device, dtype=torch.float32)
-    elif h.dtype != torch.float32 or not h.is_contiguous():
-        h = h.float().contiguous()
+        h = torch.zeros(bsz, dim, move.ndim, device=x.device, dtype=sdtype)
+    elif h.dtype != sdtype or not h.is_contiguous():
+        h = h.to(sdtype).contiguous()
     estate['prev_state'] = h
     move._set_input_buffer(incremental_state, estate)
     y = torch.empty_like(x)
     xn = torch.empty_like(x) if return_normed else None
-    ops.tsn_ema_step_(x.view(bsz, dim), y.view(bsz, dim), nstate['prev_count'], nstate['prev_mean'],
-                      nstate['prev_var'], gamma, beta, norm.eps, p, q, g, omega, h,
-                      silu=activation == 'silu', xn_out=None if xn is None else xn.view(bsz, dim))
+    step = ops.tsn_cema_step_ if move.complex else ops.tsn_ema_step_
+    step(x.view(bsz, dim), y.view(bsz, dim), nstate['prev_count'], nstate['prev_mean'],
+         nstate['prev_var'], gamma, beta, norm.eps, p, q, g, omega, h,
+         silu=activation == 'silu', xn_out=None if xn is None else xn.view(bsz, dim))
     return (y, xn) if return_normed else y

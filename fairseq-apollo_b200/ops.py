@@ -298,6 +298,18 @@ def tsn_ema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, s
     return y
 
 
+def tsn_cema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None):
+    """tsn_ema_step_ for the complex layer: q, g (K, N, 2) and h (B, D, N, 2) are fp32 views of the
+    complex64 tensors; everything is updated in place, nothing is converted or allocated."""
+    bsz, dim = x.shape
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().mega_tsn_cema_step(
+            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, count.data_ptr(), mean.data_ptr(),
+            var.data_ptr(), gamma.data_ptr(), beta.data_ptr(), float(eps), p.data_ptr(), q.data_ptr(), g.data_ptr(),
+            omega.data_ptr(), p.shape[1], h.data_ptr(), EMA_SILU if silu else 0, _stream()), "tsn_cema_step")
+    return y
+
+
 # --------------------------------------------------------------------------- gates
 def _rows(t):
     """View t (..., cols) as `rows` rows of `cols` elements with one row pitch; copies only

@@ -372,6 +372,20 @@ MEGA_API int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, 
                       unsigned flags, mega_stream_t stream);
 
 /*
+ * mega_tsn_cema_step: single-token decode step of TimestepNorm -> MultiHeadComplexEMA, all running
+ * state updated IN PLACE like mega_tsn_ema_step: count (B) int64, mean/var (B,D) fp32, h (B,D,N,2)
+ * fp32 complex pole states (16-byte aligned).  N must be 2, 4, 8, 16 or 32 (MEGA_ERR_UNSUPPORTED
+ * otherwise: run the two operators in turn).  Queues two launches (elements, then counts).
+ * Replaces: the L == 1 case of TimestepNorm.forward + BaseMovingLayer.forward with an incremental
+ * state and the complex layer (norm_layer/timestep_norm.py:100-139, base_moving_average.py:144-160,
+ * complex_exponential_moving_average.py:79-109).
+ */
+MEGA_API int mega_tsn_cema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D, int64_t* count,
+                       float* mean, float* var, const float* gamma, const float* beta, double eps,
+                       const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                       float* h, unsigned flags, mega_stream_t stream);
+
+/*
  * mega_cema_bwd / mega_cema_coeffs_bwd: gradients of mega_cema_fwd (no SiLU flag, no carried state;
  * truncation as in the forward), same argument conventions as mega_ema_bwd; dq and dgamma_hat are (K, N, 2) with
  * the gradients of the real and imaginary parts, dtheta is (K).

@@ -202,3 +202,32 @@ def test_complex_tensor_core_path(bsz, length, dim, ndim, normed, silu):
     if length % 32 == 0:   # the final carried states of the two implementations
         assert rel_l2(torch.view_as_real(outs[0][1]), torch.view_as_real(outs[1][1])) < 1e-2
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("ndim", [16, 3])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_complex_single_token_decode(ndim, dtype):
+    """TimestepNorm -> complex EMA token by token with the incremental state (the fused decode
+    step for ndim 16, the two operators in turn for ndim 3) equals the full-length call."""
+    M, O = _mods()
+    gen = torch.Generator().manual_seed(ndim)
+    torch.manual_seed(ndim)
+    bsz, length, dim = 5, 37, 72
+    move = M.MultiHeadComplexEMA(dim, ndim=ndim).cuda().eval()
+    norm = M.TimestepNorm(dim, prior_count=2).cuda().eval()
+    with torch.no_grad():
+        move.gamma[:, :, 1].normal_(0, 1)
+        norm.weight.normal_(0, 0.1)
+        norm.bias.normal_(0, 0.1)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.3 + 0.2).to(dtype).cuda()
+    with torch.no_grad():
+        full, xn_full = M.timestep_norm_ema(norm, move, x, None, None, 'silu', return_normed=True)
+        st, ys, xns = {}, [], []
+        for t in range(length):
+            y, xn = M.timestep_norm_ema(norm, move, x[:, t:t + 1].contiguous(), None, st, 'silu', return_normed=True)
+            ys.append(y)
+            xns.append(xn)
+    assert rel_l2(torch.cat(ys, 1).float(), full.float()) < TOL[dtype]
+    assert rel_l2(torch.cat(xns, 1).float(), xn_full.float()) < TOL[dtype]
+    assert move._get_input_buffer(st)["prev_state"].dtype == torch.complex64
+    assert int(norm._get_input_buffer(st)["prev_count"][0]) == 2 + length
