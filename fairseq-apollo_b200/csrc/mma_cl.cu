@@ -789,7 +789,10 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   };
   int tile = g_options[OPT_MMA_TILE].load();
   if (tile != 2 && tile != 4 && tile != 7 && tile != 8 && tile != 22) {
-    if (ctas(64) >= 148 || ctas(56) >= 148) tile = waves_cost(56) < waves_cost(64) ? 7 : 8;
+    // (the EMA alone is closer to the memory bound and prefers the 128-byte rows of the 64-channel
+    // tile: 1.71 against 2.02 ms at B = 64, L = 16384, D = 2048, unless 56 channels save a wave)
+    if (ctas(64) >= 148 || ctas(56) >= 148)
+      tile = waves_cost(56) * (norm ? 1.0 : 1.15) < waves_cost(64) ? 7 : 8;
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
   }
