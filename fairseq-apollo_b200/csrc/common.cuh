@@ -30,6 +30,11 @@ bool step_lanes_try(int dtype, const void* x, void* y, void* xn_out, int B, int 
 template <typename... KArgs, typename... Args>
 static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
                           Args... args) {
+  // Above the default 48 KB the dynamic shared-memory size is an opt-in attribute of the kernel ON
+  // THE CURRENT DEVICE; setting it at every such launch (microseconds, these launches run for
+  // hundreds) keeps a process that drives several GPUs correct.
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   kernel<<<grid, block, smem, (cudaStream_t)stream>>>(static_cast<KArgs>(args)...);
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
