@@ -26,6 +26,12 @@
 //                  h_local = P xn          (P[n][t] = p q^(15-t));  h_next = q^16 h + h_local.
 // The per-channel matrices T, P, G are built once per CTA, in MMA fragment order, in shared
 // memory.  Tiles move by TMA (128-byte swizzle), are transformed in place and stored by TMA.
+//
+// Forms of the kernel (template parameters): with or without the normalisation; with or without
+// the EMA (TimestepNorm alone); SiLU epilogue; one or two warps per 16-byte column; a second
+// output with the normalised activations (what the Mega block feeds its value projection);
+// complex poles (MultiHeadComplexEMA: P yields Re and Im of the local states, the carry is a
+// complex multiply by q^16, G takes Re(gamma q^(t+1)) against Re h and -Im(...) against Im h).
 #include <mutex>
 
 #include "common.cuh"
