@@ -20,6 +20,7 @@ bounded sample.  `--impl reference` prints that CPU measurement as its own line.
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -36,9 +37,16 @@ WORKLOADS = {
     "tiny": (4, 2048, 256, "bf16"),
 }
 # side workloads (BASELINE configs 0, 2 and the decode half of config 4): own JSON line, N=1 only
-AUX_WORKLOADS = ("c0", "c2", "decode", "cema", "train", "c4n", "c1n")
+AUX_WORKLOADS = ("c0", "c2", "c3", "decode", "cema", "train", "c4n", "c1n")
+# side workloads measured after the headline run and reported under its "aux" key (N = 1 only)
+AUX_IN_HEADLINE = ("c0", "c1", "c2", "c3", "c4n", "cema", "train", "decode")
 NDIM = 16
 FALLBACK_HBM_GBS = 6650.0
+CPU_DETAIL = {
+    "reference+port": "TimestepNorm: the reference's own compiled CPU operator (oracle/_ref); EMA: the oracle's "
+                      "port of the reference's torch.fft flow (the reference's Python cannot travel)",
+    "port": "TimestepNorm and EMA through the oracle's port of the reference's CPU flow",
+}
 
 
 def make_ema_params(gen, dim, ndim):
@@ -231,9 +239,9 @@ def run_reference(args, B, L, D, dtype_name):
         "data": "synthetic",
         "config": {"workload": workload_name(args, B, L, D, dtype_name), "ndim": NDIM,
                    "path": "reference CPU path: TimestepNorm C++ op + torch.fft convolution"},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores,
-                         "kind": "reference" if kind.startswith("reference") else "port", "sample": sample,
-                         "detail": kind},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample,
+                         "detail": CPU_DETAIL[kind]},
+        "reference_scope": "one host's CPU cores, rank 0 only: the number does not grow with --gpus",
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -262,8 +270,8 @@ NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = 1036.28e6 / (32 * 4096)
 
 
 def workload_name(args, B, L, D, dtype_name):
-    return "%s: TimestepNorm+MultiHeadEMA causal fwd, B=%d L=%d D=%d %s (per rank)" % (
-        args.workload, B, L, D, dtype_name)
+    return "%s: TimestepNorm+MultiHeadEMA causal fwd, B=%d L=%d D=%d %s per rank (%s scaling)" % (
+        args.workload, B, L, D, dtype_name, args.scaling)
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -313,6 +321,8 @@ def run_ours(args, B, L, D, dtype_name):
     vo = torch.empty(Bl, D, device=dev)
     from fairseq_apollo_b200 import _lib
     lib = _lib.lib()
+    if args.tile:
+        _lib.set_option(2, args.tile)
     stream = torch.cuda.current_stream()
 
     def step(xi=x, yi=y, bl=Bl):
@@ -355,12 +365,25 @@ def run_ours(args, B, L, D, dtype_name):
     value = job_throughput(Bl * L, world, args.steps, total_ms)
 
     # ---- end-to-end through host buffers: pinned host x -> device -> kernel -> pinned host y
-    # The per-rank batch streams through in slices on three streams (H2D, compute, D2H).
+    # The per-rank batch streams through in slices on three streams (H2D, compute, D2H).  The host
+    # side holds the whole per-rank batch (input and output) in pinned memory; if the host cannot
+    # pin that much, one pinned slice stands in for every slice (same bytes moved, said in the note).
     sl = max(1, min(Bl, args.e2e_slice))
     nsl = (Bl + sl - 1) // sl
-    hx = torch.empty(sl, L, D, dtype=dtype).pin_memory()
-    hy = torch.empty(sl, L, D, dtype=dtype).pin_memory()
-    hx.copy_(x[:sl].cpu())
+    whole_host_batch = True
+    try:
+        hx_all = torch.empty(nsl * sl, L, D, dtype=dtype).pin_memory()
+        hy_all = torch.empty(nsl * sl, L, D, dtype=dtype).pin_memory()
+        for i in range(nsl):
+            n = min(sl, Bl - i * sl)
+            hx_all[i * sl:i * sl + n].copy_(x[i * sl:i * sl + n])
+    except Exception:  # noqa: BLE001 - not enough pinnable host memory
+        whole_host_batch = False
+        hx_all = torch.empty(sl, L, D, dtype=dtype).pin_memory()
+        hy_all = torch.empty(sl, L, D, dtype=dtype).pin_memory()
+        hx_all.copy_(x[:sl].cpu())
+    hxs = [hx_all[i * sl:(i + 1) * sl] if whole_host_batch else hx_all for i in range(nsl)]
+    hys = [hy_all[i * sl:(i + 1) * sl] if whole_host_batch else hy_all for i in range(nsl)]
     dx = [torch.empty(sl, L, D, dtype=dtype, device=dev) for _ in range(2)]
     dy = [torch.empty(sl, L, D, dtype=dtype, device=dev) for _ in range(2)]
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -375,7 +398,7 @@ def run_ours(args, B, L, D, dtype_name):
             with torch.cuda.stream(s_in):
                 if i >= 2:
                     s_in.wait_event(ev_k[i - 2])          # buffer k consumed by the kernel
-                dx[k].copy_(hx, non_blocking=True)
+                dx[k].copy_(hxs[i], non_blocking=True)
                 ev_in[i].record(s_in)
             stream.wait_event(ev_in[i])
             if i >= 2:
@@ -388,7 +411,7 @@ def run_ours(args, B, L, D, dtype_name):
             ev_k[i].record(stream)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_k[i])
-                hy.copy_(dy[k], non_blocking=True)
+                hys[i].copy_(dy[k], non_blocking=True)
                 ev_out[i].record(s_out)
         stream.wait_stream(s_out)
         stream.wait_stream(s_in)
@@ -409,12 +432,40 @@ def run_ours(args, B, L, D, dtype_name):
     e2e_val = e2e_tokens / (float(em.item()) * 1e-3)
     bytes_dir = nsl * sl * L * D * es
 
-    # ---- one verification gather (outside every timed region): checksum of a small slice
-    chk = y[0, :64].float().sum().reshape(1)
+    # ---- verification (outside every timed region): the first sequence's first 4096 positions
+    # through the streamed SIMT kernel (a different implementation of the same entry point) against
+    # the timed kernel's output, and the end-to-end output in host memory against the device one;
+    # every rank's result is gathered to rank 0 (the only collective of the run besides timing).
+    step()
+    torch.cuda.synchronize()
+    vl = min(L, 4096)
+    xv, yv = x[:1, :vl].contiguous(), torch.empty(1, vl, D, dtype=dtype, device=dev)
+    _lib.set_option(1, 1)
+    try:
+        step(xv, yv, 1)
+    finally:
+        _lib.set_option(1, 0)
+    ref = yv.float()
+    rel = float((y[:1, :vl].float() - ref).norm() / ref.norm())
+    e2e_same = True
+    if whole_host_batch:
+        e2e_same = bool(torch.equal(hy_all[:min(sl, Bl)].to(dev), y[:min(sl, Bl)]))
+    chk = torch.tensor([rel, 1.0 if e2e_same else 0.0], device=dev, dtype=torch.float64)
+    outs = [chk]
     if world > 1:
         outs = [torch.empty_like(chk) for _ in range(world)]
         dist.all_gather(outs, chk)
+    verify = {"max_rel_l2_vs_simt_kernel": max(float(o[0]) for o in outs), "tolerance": 1e-2,
+              "e2e_host_output_equals_device_output": all(float(o[1]) == 1.0 for o in outs)}
+    verify["ok"] = verify["max_rel_l2_vs_simt_kernel"] < 1e-2 and verify["e2e_host_output_equals_device_output"]
+    del hx_all, hy_all, hxs, hys, dx, dy
 
+    aux = None
+    kernel_name = _lib.last_kernel()
+    if rank == 0 and world == 1 and not args.no_aux:
+        del x, y
+        torch.cuda.empty_cache()
+        aux = aux_summary(5, 3)
     if rank == 0:
         peak, peak_kind = hbm_peak()
         kern_ms = sum(per_step) / len(per_step)
@@ -426,7 +477,7 @@ def run_ours(args, B, L, D, dtype_name):
             cstep, kind, cores = cpu_reference_step_factory(D, L, sample_b, sample_d)
             sec = time_cpu(cstep, 3, 1)
             cpu = {"value": sample_b * L * (sample_d / D) / sec, "unit": "tokens/s", "cores": cores,
-                   "kind": "reference" if kind.startswith("reference") else "port", "detail": kind,
+                   "kind": kind, "detail": CPU_DETAIL[kind],
                    "sample": "B=%d, L=%d, %d of %d channels, 3 timed passes (tokens scaled by the channel fraction)"
                              % (sample_b, L, sample_d, D)}
         line = {
@@ -441,27 +492,36 @@ def run_ours(args, B, L, D, dtype_name):
                          "frac": achieved / peak,
                          "traffic": (NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 * Bl * L
                                      if (D == 2048 and dtype_name == "bf16") else None),
+                         "traffic_note": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
+                                         "kernel at B=32, L=4096, D=2048, scaled by the tokens of a launch",
                          "peak_kind": peak_kind,
-                         "kernel": "tsn_ema fused forward", "algorithmic_bytes_per_launch": alg_bytes,
+                         "kernel": kernel_name, "algorithmic_bytes_per_launch": alg_bytes,
                          "kernel_ms": kern_ms},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": bytes_dir * world,
                     "d2h_bytes_per_step": bytes_dir * world, "steps": e2e_steps,
-                    "note": "pinned host slices of %d sequences streamed on 3 streams" % sl},
+                    "note": ("the whole per-rank batch lives in pinned host memory (input and output); slices of %d "
+                             "sequences stream H2D -> kernel -> D2H on 3 streams" % sl) if whole_host_batch else
+                            ("host could not pin the whole batch: one pinned slice of %d sequences is sent and "
+                             "received %d times per step (same bytes over PCIe)" % (sl, nsl))},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "verify": verify,
+            "aux": aux,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_aux(args):
-    """Configs 0 and 2 and the 1024-step decode loop: CUDA-event timing of the module calls."""
+def aux_workload(workload, steps, warm):
+    """One side workload (configs 0, 1, 2, the decode loop, the complex layer, a training step, the
+    two-output form): CUDA-event timing of the module calls on GPU 0; returns the JSON line as a dict."""
     import torch
     import fairseq_apollo_b200 as M
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    from fairseq_apollo_b200 import _lib
+    args = argparse.Namespace(workload=workload)
+    dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator().manual_seed(1234)
     peak, peak_kind = hbm_peak()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -479,8 +539,9 @@ def run_aux(args):
         ts = sorted(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(steps))
         return ts[len(ts) // 2]
 
-    steps, warm = max(args.steps, 5), max(args.warmup, 3)
+    steps, warm = max(steps, 5), max(warm, 3)
     l0 = M.launch_count()
+    kernel = None
     if args.workload == "train":
         # forward + backward of TimestepNorm -> EMA on the config-1 shape through the modules' autograd
         # Functions; compulsory traffic: x read twice, y written, dy read, dx written = 5 passes
@@ -509,6 +570,40 @@ def run_aux(args):
             norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
             ms = timed(lambda: M.timestep_norm_ema(norm, ema, x), steps, warm)
             tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 2, "cema: TimestepNorm+MultiHeadComplexEMA causal fwd bf16 L=32768 B=16 D=2048", "bf16"
+        elif args.workload == "c3":
+            # BASELINE config 3: one Mega decoder block (this package's MovingAverageGatedAttention on the fused
+            # kernels, projections on cuBLAS) + the normalised feed-forward network, bf16, random init;
+            # token ids uniform over a 32k vocabulary into a random embedding scaled by sqrt(D)
+            L, B, D, Z, H, FF, C = 8192, 8, 1024, 256, 2048, 2048, 1024
+            emb = (torch.randn(32000, D, generator=gen) * D ** -0.5).to(dev).bfloat16()
+            ids = torch.randint(0, 32000, (B, L), generator=gen).to(dev)
+            x = (emb[ids] * math.sqrt(D)).contiguous()
+            blk = M.MovingAverageGatedAttention(D, Z, H, NDIM, chunk_size=C, moving_layer='ema', moving_act='silu',
+                                                rel_pos_bias='rotary', efficient_attn=True).to(dev).bfloat16().eval()
+            ln = torch.nn.LayerNorm(D).to(dev).bfloat16()
+            fc1, fc2 = torch.nn.Linear(D, FF).to(dev).bfloat16(), torch.nn.Linear(FF, D, bias=False).to(dev).bfloat16()
+
+            def layer():
+                h = blk(x)[0]
+                return h + fc2(torch.nn.functional.silu(fc1(ln(h))))
+            ms = timed(layer, steps, warm)
+            ms_ema = timed(lambda: M.timestep_norm_ema(blk.norm, blk.move, x, None, None, 'silu', return_normed=True),
+                           steps, warm)
+            ms_blk = timed(lambda: blk(x), steps, warm)
+            extra = {"ms_layer": ms, "ms_block": ms_blk, "ms_fused_norm_ema_part": ms_ema,
+                     "share_of_layer_in_fused_norm_ema": ms_ema / ms,
+                     "note": "projections, attention GEMMs and the feed-forward network are cuBLAS (library GEMMs); "
+                             "the norm -> EMA -> SiLU, the gates and the attention softmax are this library's kernels"}
+            # compulsory traffic of the norm -> EMA part only (x in, mx and xn out); the layer as a whole is GEMM-bound
+            tokens, bytes_alg, dt = B * L, 3.0 * B * L * D * 2 * (ms / ms_ema), "bf16"
+            name = "c3: Mega decoder block + NFFN fwd bf16 L=8192 B=8 D=1024 z=256 h=2048 ffn=2048 chunk=1024"
+        elif args.workload == "c1":
+            L, B, D = 4096, 16, 1024
+            x = torch.randn(B, L, D, generator=gen).to(dev).bfloat16()
+            ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+            norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+            ms = timed(lambda: M.timestep_norm_ema(norm, ema, x), steps, warm)
+            tokens, bytes_alg, name, dt = B * L, 2.0 * B * L * D * 2, "c1: TimestepNorm+MultiHeadEMA causal fwd bf16 L=4096 B=16 D=1024", "bf16"
         elif args.workload in ("c4n", "c1n"):
             # configs 4 and 1 as the Mega block calls the pair: the normalised activations are a second
             # output (they feed the value projection), so the compulsory traffic is 3 x D x 2 B per token
@@ -569,20 +664,53 @@ def run_aux(args):
             def replay():
                 for _ in range(T):
                     gr.replay()
+            kernel = _lib.last_kernel()
             ms = timed(replay, 3, 1) / T
             extra = {"module_call_us_per_step": ms_module * 1e3, "graph_replay_us_per_step": ms * 1e3}
             tokens, bytes_alg, name, dt = B, 2.0 * B * D * NDIM * 4 + 2.0 * B * D * 2, "decode: TimestepNorm+EMA single-token step, B=64 D=2048 ndim=16, state fp32", "bf16"
     launches = M.launch_count() - l0
-    if args.workload != "decode":
+    if args.workload not in ("decode", "c3"):
         extra = None
-    line = {"extra": extra, "metric": "mega_ema_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+    if args.workload != "decode":
+        kernel = _lib.last_kernel()
+    torch.cuda.synchronize()
+    del flush
+    line = {"extra": extra, "kernel": kernel, "metric": "mega_ema_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
             "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": dt, "data": "synthetic",
             "config": {"workload": name, "ndim": NDIM, "l2": "256 MiB scratch written between timed calls"},
             "roofline": {"bound": "hbm", "achieved": bytes_alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": bytes_alg / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": peak_kind},
             "gpu_launches": int(launches)}
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def run_aux(args):
+    import torch
+    torch.cuda.set_device(0)
+    print(json.dumps(aux_workload(args.workload, args.steps, args.warmup)), flush=True)
+
+
+def aux_summary(steps, warm):
+    """The side workloads, measured in this process after the headline run: one entry each with the
+    time per step, tokens/s, the fraction of the HBM peak (algorithmic bytes) and the kernel family
+    that ran.  A workload that fails is reported with its error, not dropped."""
+    import gc
+    import torch
+    out = {}
+    for w in AUX_IN_HEADLINE:
+        try:
+            r = aux_workload(w, steps, warm)
+            out[w] = {"ms": r["ms_per_step"], "tokens_per_s": r["value"], "roofline_frac": r["roofline"]["frac"],
+                      "achieved_gbs": r["roofline"]["achieved"], "kernel": r.get("kernel"),
+                      "workload": r["config"]["workload"]}
+            if r.get("extra"):
+                out[w].update(r["extra"])
+        except Exception as exc:  # noqa: BLE001 - reported in the line
+            out[w] = {"error": str(exc).splitlines()[0][:200]}
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -592,12 +720,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS))
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong (default): the workload's batch is sharded over the ranks, as BASELINE config 4 "
+                         "defines the multi-GPU run (B=64 -> 32/16/8 per GPU); weak: every rank runs the full batch")
+    ap.add_argument("--no-aux", action="store_true", help="skip the side workloads reported under 'aux'")
     ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
     ap.add_argument("--length", type=int, default=0, help="override the sequence length (profiling aid)")
     ap.add_argument("--e2e-slice", type=int, default=8)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tile", type=int, default=0, help="force a tensor-core tile form (tuning aid; 0 = automatic)")
     args = ap.parse_args()
     if args.workload in AUX_WORKLOADS:
         return run_aux(args)

@@ -31,9 +31,9 @@ SIGNATURES = {
                          c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
     "mega_sqn_ema_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_d, c_p, c_p, c_p,
                          c_p, c_p, c_p, c_p, c_i, c_p, c_u, c_p],
-    "mega_tsn_ema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
+    "mega_tsn_ema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
                           c_p, c_u, c_p],
-    "mega_tsn_cema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
+    "mega_tsn_cema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,
                            c_p, c_u, c_p],
     "mega_gate_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
@@ -67,6 +67,7 @@ OTHER = {
     "mega_last_cuda_error": ([], ctypes.c_char_p),
     "mega_abi_version": ([], c_i),
     "mega_launch_count": ([], ctypes.c_uint64),
+    "mega_debug_last_kernel": ([], ctypes.c_char_p),
 }
 
 _lib = None
@@ -108,6 +109,11 @@ def check(status, what):
 
 def launch_count():
     return int(lib().mega_launch_count())
+
+
+def last_kernel():
+    """Kernel family of the most recent launch of this process (test aid)."""
+    return lib().mega_debug_last_kernel().decode()
 
 
 def set_option(key, value):

@@ -9,6 +9,7 @@ namespace mega {
 std::atomic<uint64_t> g_launches{0};
 thread_local char g_cuda_err[256] = "";
 std::atomic<int> g_options[8];
+std::atomic<const char*> g_last_kernel{"none"};
 
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
@@ -37,6 +38,8 @@ extern "C" const char* mega_status_string(int status) {
 extern "C" const char* mega_last_cuda_error(void) { return mega::g_cuda_err; }
 extern "C" int mega_abi_version(void) { return MEGA_ABI_VERSION; }
 extern "C" uint64_t mega_launch_count(void) { return mega::g_launches.load(); }
+
+extern "C" MEGA_API const char* mega_debug_last_kernel(void) { return mega::g_last_kernel.load(); }
 
 extern "C" MEGA_API int mega_set_option(int key, int value) {
   if (key < 0 || key >= 8) return MEGA_ERR_SHAPE;

@@ -228,7 +228,8 @@ __global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restric
                                                               const float* __restrict__ q,
                                                               const float* __restrict__ g,
                                                               const float* __restrict__ omega, const float* h_in,
-                                                              float* h_out, int silu, int use_norm) {
+                                                              float* h_out, int silu, int use_norm,
+                                                              long long* count_next) {
   constexpr int N = LN * 2;
   const int sub = threadIdx.x % LN;
   const int d = blockIdx.x * (128 / LN) + threadIdx.x / LN;
@@ -302,6 +303,12 @@ __global__ void __launch_bounds__(128) cema_step_lanes_kernel(const T* __restric
       }
     }
   }
+  // the counts after this step go to a second array (never the one every CTA is reading)
+  if (count_next && d == 0 && sub == 0) {
+#pragma unroll
+    for (int j = 0; j < BB; ++j)
+      if (b0 + j < B) count_next[b0 + j] = count[b0 + j] + 1;
+  }
 }
 
 // One thread per sequence bumps the counts after the element kernel has read them.
@@ -314,7 +321,8 @@ template <typename T>
 static bool launch_cema_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, const long long* count,
                                    float* mean, float* var, const float* gamma, const float* beta, float eps,
                                    const float* p, const float* q, const float* g, const float* omega,
-                                   const float* h_in, float* h_out, int silu, void* stream) {
+                                   const float* h_in, float* h_out, int silu, void* stream,
+                                   long long* count_next = nullptr) {
   const int use_norm = count != nullptr;
   if (N != 2 && N != 4 && N != 8 && N != 16 && N != 32) return false;
   if (!aligned_to(h_out, 16) || (h_in && !aligned_to(h_in, 16)) || !aligned_to(p, 8) || !aligned_to(q, 16) ||
@@ -326,7 +334,7 @@ static bool launch_cema_step_lanes(const T* x, T* y, T* xn_out, int B, int D, in
   if (grid.y > 65535) return false;
 #define MEGA_CEMA_STEP_LANES(LNV) \
   launch(cema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, xn_out, B, D, count, mean, var, gamma, \
-         beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm)
+         beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, count_next)
   if (ln == 1) MEGA_CEMA_STEP_LANES(1);
   else if (ln == 2) MEGA_CEMA_STEP_LANES(2);
   else if (ln == 4) MEGA_CEMA_STEP_LANES(4);
@@ -666,7 +674,8 @@ extern "C" int mega_cema_step(const void* x, void* y, int dtype, int B, int D, c
 }
 
 extern "C" int mega_tsn_cema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D, int64_t* count,
-                                  float* mean, float* var, const float* gamma, const float* beta, double eps,
+                                  int64_t* count_next, float* mean, float* var, const float* gamma,
+                                  const float* beta, double eps,
                                   const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
                                   float* h, unsigned flags, mega_stream_t stream) {
   if (!x || !y || !count || !mean || !var || !gamma || !beta || !p || !q || !gamma_hat || !omega || !h)
@@ -676,11 +685,14 @@ extern "C" int mega_tsn_cema_step(const void* x, void* y, void* xn_out, int dtyp
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
   const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
   bool lanes = false;
+  // a distinct count_next array takes the bumped counts from the element kernel itself
+  long long* next = (count_next && count_next != count) ? (long long*)count_next : nullptr;
   MEGA_DISPATCH_DTYPE(dtype, lanes = launch_cema_step_lanes<T>((const T*)x, (T*)y, (T*)xn_out, B, D, N,
                                                               (const long long*)count, mean, var, gamma, beta,
-                                                              (float)eps, p, q, gamma_hat, omega, h, h, silu, stream));
+                                                              (float)eps, p, q, gamma_hat, omega, h, h, silu, stream,
+                                                              next));
   if (!lanes) return MEGA_ERR_UNSUPPORTED;  // pole counts other than 2, 4, 8, 16, 32, or unaligned states
-  launch(cema_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
+  if (!next) launch(cema_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
   return check_launch("tsn_cema_step");
 }
 

@@ -16,7 +16,10 @@ namespace mega {
 extern std::atomic<uint64_t> g_launches;
 extern thread_local char g_cuda_err[256];
 extern std::atomic<int> g_options[8];
-enum { OPT_DISABLE_STREAM = 0, OPT_DISABLE_MMA = 1, OPT_MMA_TILE = 2 };
+enum { OPT_DISABLE_STREAM = 0, OPT_DISABLE_MMA = 1, OPT_MMA_TILE = 2, OPT_WAIT_LIMIT = 3, OPT_WITHHOLD_LOAD = 4 };
+// Name of the kernel family of the most recent launch (test aid): launch() sets "other", the
+// launchers of the named families overwrite it right after.
+extern std::atomic<const char*> g_last_kernel;
 int check_launch(const char* what);
 
 // Single-token step with N / 4 lanes per (sequence, channel) (csrc/fused.cu): TimestepNorm update
@@ -25,7 +28,7 @@ int check_launch(const char* what);
 bool step_lanes_try(int dtype, const void* x, void* y, void* xn_out, int B, int D, int N, const long long* count,
                     float* mean, float* var, const float* gamma, const float* beta, float eps, const float* p,
                     const float* q, const float* g, const float* omega, const float* h_in, float* h_out, int silu,
-                    void* stream);
+                    void* stream, long long* count_next = nullptr);
 
 template <typename... KArgs, typename... Args>
 static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream,
@@ -37,6 +40,7 @@ static inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   kernel<<<grid, block, smem, (cudaStream_t)stream>>>(static_cast<KArgs>(args)...);
   g_launches.fetch_add(1, std::memory_order_relaxed);
+  g_last_kernel.store("other", std::memory_order_relaxed);
 }
 
 // ---- element I/O ------------------------------------------------------------

@@ -200,7 +200,8 @@ __global__ void __launch_bounds__(128) tsn_ema_step_lanes_kernel(const T* __rest
                                                                  const float* __restrict__ q,
                                                                  const float* __restrict__ g,
                                                                  const float* __restrict__ omega, const float* h_in,
-                                                                 float* h_out, int silu, int use_norm) {
+                                                                 float* h_out, int silu, int use_norm,
+                                                                 long long* count_next) {
   constexpr int N = LN * 4;
   const int sub = threadIdx.x % LN;
   const int d = blockIdx.x * (128 / LN) + threadIdx.x / LN;
@@ -272,6 +273,12 @@ __global__ void __launch_bounds__(128) tsn_ema_step_lanes_kernel(const T* __rest
       }
     }
   }
+  // the counts after this step go to a second array (never the one every CTA is reading)
+  if (count_next && d == 0 && sub == 0) {
+#pragma unroll
+    for (int j = 0; j < BB; ++j)
+      if (b0 + j < B) count_next[b0 + j] = count[b0 + j] + 1;
+  }
 }
 
 // Launches the lane-split step when the pole count allows it (N = 4, 8, 16 or 32, states 16-byte
@@ -280,7 +287,7 @@ template <typename T>
 static bool launch_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, const long long* count, float* mean,
                               float* var, const float* gamma, const float* beta, float eps, const float* p,
                               const float* q, const float* g, const float* omega, const float* h_in, float* h_out,
-                              int silu, int use_norm, mega_stream_t stream) {
+                              int silu, int use_norm, mega_stream_t stream, long long* count_next) {
   if (N != 4 && N != 8 && N != 16 && N != 32) return false;
   if (!aligned_to(h_out, 16) || (h_in && !aligned_to(h_in, 16)) || !aligned_to(p, 16) || !aligned_to(q, 16) ||
       !aligned_to(g, 16))
@@ -291,7 +298,7 @@ static bool launch_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, 
   if (grid.y > 65535) return false;
 #define MEGA_STEP_LANES(LNV)                                                                              \
   launch(tsn_ema_step_lanes_kernel<T, LNV, BB>, grid, 128, 0, stream, x, y, xn_out, B, D, count, mean, var, \
-         gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm)
+         gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, count_next)
   if (ln == 1) MEGA_STEP_LANES(1);
   else if (ln == 2) MEGA_STEP_LANES(2);
   else if (ln == 4) MEGA_STEP_LANES(4);
@@ -303,19 +310,20 @@ static bool launch_step_lanes(const T* x, T* y, T* xn_out, int B, int D, int N, 
 bool step_lanes_try(int dtype, const void* x, void* y, void* xn_out, int B, int D, int N, const long long* count,
                     float* mean, float* var, const float* gamma, const float* beta, float eps, const float* p,
                     const float* q, const float* g, const float* omega, const float* h_in, float* h_out, int silu,
-                    void* stream) {
+                    void* stream, long long* count_next) {
   const int use_norm = count != nullptr;
   switch (dtype) {
     case MEGA_F32:
       return launch_step_lanes<float>((const float*)x, (float*)y, (float*)xn_out, B, D, N, count, mean, var, gamma,
-                                      beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream);
+                                      beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream, count_next);
     case MEGA_BF16:
       return launch_step_lanes<__nv_bfloat16>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (__nv_bfloat16*)xn_out, B,
                                               D, N, count, mean, var, gamma, beta, eps, p, q, g, omega, h_in, h_out,
-                                              silu, use_norm, stream);
+                                              silu, use_norm, stream, count_next);
     case MEGA_F16:
       return launch_step_lanes<__half>((const __half*)x, (__half*)y, (__half*)xn_out, B, D, N, count, mean, var,
-                                       gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream);
+                                       gamma, beta, eps, p, q, g, omega, h_in, h_out, silu, use_norm, stream,
+                                       count_next);
     default:
       return false;
   }
@@ -327,13 +335,19 @@ __global__ void tsn_count_step_kernel(long long* count, int B) {
   if (b < B) count[b] += 1;
 }
 
+__global__ void tsn_count_next_kernel(const long long* count, long long* next, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) next[b] = count[b] + 1;
+}
+
 }  // namespace mega
 
 using namespace mega;
 
 extern "C" MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D,
-                                          int64_t* count, float* mean, float* var, const float* gamma,
-                                          const float* beta, double eps, const float* p, const float* q,
+                                          int64_t* count, int64_t* count_next, float* mean, float* var,
+                                          const float* gamma, const float* beta, double eps, const float* p,
+                                          const float* q,
                                           const float* gamma_hat, const float* omega, int N, float* h,
                                           unsigned flags, mega_stream_t stream) {
   if (!x || !y || !p || !q || !gamma_hat || !omega || !h) return MEGA_ERR_NULL;
@@ -346,14 +360,23 @@ extern "C" MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, 
   const int np = next_pow2_ndim(N);
   const unsigned grid = (unsigned)(((long long)B * D + 127) / 128);
   const int silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
-  if (!step_lanes_try(dtype, x, y, xn_out, B, D, N, (const long long*)count, mean, var, gamma, beta, (float)eps, p, q,
-                      gamma_hat, omega, h, h, silu, stream)) {
+  // a distinct count_next array takes the bumped counts from the element kernel itself
+  long long* next = (use_norm && count_next && count_next != count) ? (long long*)count_next : nullptr;
+  if (step_lanes_try(dtype, x, y, xn_out, B, D, N, (const long long*)count, mean, var, gamma, beta, (float)eps, p, q,
+                     gamma_hat, omega, h, h, silu, stream, next)) {
+    if (next) return check_launch("tsn_ema_step");
+  } else {
     MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(np, launch(tsn_ema_step_kernel<T, NP>, grid, 128, 0, stream,
                                                            (const T*)x, (T*)y, (T*)xn_out, B, D, N,
                                                            (long long*)count, mean, var, gamma, beta, (float)eps,
                                                            p, q, gamma_hat, omega, h, silu, use_norm)));
   }
-  if (use_norm) launch(tsn_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
+  if (use_norm) {
+    if (next)  // generic kernel: the second array is filled by a copy-and-increment launch
+      launch(tsn_count_next_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (const long long*)count, next, B);
+    else
+      launch(tsn_count_step_kernel, (unsigned)((B + 127) / 128), 128, 0, stream, (long long*)count, B);
+  }
   return check_launch("tsn_ema_step");
 }
 

@@ -33,6 +33,9 @@
 // complex poles (MultiHeadComplexEMA: P yields Re and Im of the local states, the carry is a
 // complex multiply by q^16, G takes Re(gamma q^(t+1)) against Re h and -Im(...) against Im h).
 #include <mutex>
+#include <string>
+#include <type_traits>
+#include <utility>
 
 #include "common.cuh"
 #include "stream_cl.cuh"
@@ -49,12 +52,19 @@ constexpr int kStep = 32;  // positions per step (2 chunks of 16)
 // projection): two more tile buffers, filled from registers and stored by TMA like the outputs, at
 // the price of one stage of the ring.
 // kCplx: complex poles (MultiHeadComplexEMA): P, G and q^16 hold real and imaginary parts.
-template <int kCg, bool kXn = false, bool kCplx = false>
+// kWp: pipeline depth along the sequence (see the kernel): kWp groups of warps work on kWp
+// consecutive steps of the same strip at once and hand the running quantities over through
+// per-warp mailboxes in shared memory.
+template <int kCg, bool kXn = false, bool kCplx = false, int kWs = 1, int kWp = 1>
 struct Cfg {
   static constexpr int kCm = kCplx ? 2 : 1;
-  // Ring depth: a tile is fetched kStages - 1 steps before it is used.  Deeper rings were measured
-  // and do not pay: a fifth stage leaves the SM too little L1 for the few spilled registers.
-  static constexpr int kStages = kXn ? 3 : 4;
+  // Ring depth: a tile is fetched kStages - kWp steps before it is used.  Without the pipeline
+  // deeper rings were measured and do not pay: a fifth stage leaves the SM too little L1 for the
+  // few spilled registers.  With it a tile is small (narrow tiles only) and the ring holds three
+  // rounds of the pipeline.
+  static constexpr int kStages = kWp > 1 ? 3 * kWp : (kXn ? 3 : 4);
+  static constexpr int kWarps = kCg * kWs * kWp;
+  static constexpr int kE = 8 / kWs;  // channels per warp
   static constexpr int kCh = kCg * 8;                       // channels per CTA
   static constexpr int kRow = kCg * 16;                     // bytes per tile row
   static constexpr int kStageBytes = kSeq * kStep * kRow;   // 32 KiB (kCg = 8) / 28 KiB (kCg = 7)
@@ -66,8 +76,15 @@ struct Cfg {
   static constexpr int kOffA = kOffG + kCm * kCh * 4 * 32 * 4;      // [kCh][16] f32 (q^16; kCplx: float2)
   static constexpr int kOffWB = kOffA + kCm * kCh * 16 * 4;         // [kCh][2] f32
   static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
-  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages], xfree[2]
-  static constexpr int kSmemBytes = kOffBar + (2 * kStages + 2) * 8 + 1024;  // + alignment slack
+  static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages], xfree[2], abort word
+  // mailboxes (kWp > 1): per warp, per kind (0: statistics, 1: pole states), per channel: 32 lanes x
+  // 16 bytes of data, and one mbarrier whose phases count the steps that have been posted
+  static constexpr int kOffMail = (kOffBar + (2 * kStages + 2) * 8 + 16 + 15) / 16 * 16;
+  static constexpr int kMailWarp = 2 * kE * 32 * 16;
+  static constexpr int kOffFlag = kOffMail + (kWp > 1 ? kWarps * kMailWarp : 0);
+  static constexpr int kFlagWarp = 2 * kE * 8;  // one mbarrier per kind and channel: "this step's value is posted"
+  static constexpr int kSmemBytes = kOffFlag + (kWp > 1 ? kWarps * kFlagWarp : 0) + 1024;  // + alignment slack
+  static_assert(kSmemBytes <= 227 * 1024, "tile does not fit the shared memory of an SM");
 };
 
 // d = a * b + c (c read-only, so a zero or shared accumulator input needs no copy)
@@ -87,27 +104,113 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], float a0, float a1, floa
         "r"(__float_as_uint(a3)), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)), "f"(c0), "f"(c1),
         "f"(c2), "f"(c3));
 }
-// shared-memory accesses by 32-bit shared address (keeps them LDS/STS rather than generic)
+// shared-memory accesses by 32-bit shared address (keeps them LDS/STS rather than generic).  `off`
+// must be a compile-time constant after inlining: it becomes the immediate of the instruction, so
+// that a thread keeps one base register per array instead of computing every address.
+template <int kOff = 0>
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(kOff));
   return v;
 }
+template <int kOff = 0>
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(kOff));
   return v;
 }
+template <int kOff = 0>
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(kOff));
   return v;
 }
+template <int kOff = 0>
 __device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
-  asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+  asm volatile("st.shared.v2.u32 [%0+%1], {%2,%3};" ::"r"(addr), "n"(kOff), "r"(v.x), "r"(v.y) : "memory");
 }
+template <int kOff = 0>
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  asm volatile("st.shared.v4.u32 [%0+%1], {%2,%3,%4,%5};" ::"r"(addr), "n"(kOff), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// Compile-time loop: f(std::integral_constant<int, 0>{}), ..., so that the body can use its index
+// in constant expressions (instruction immediates).
+template <int... Is, typename F>
+__device__ __forceinline__ void static_for_impl(std::integer_sequence<int, Is...>, F&& f) {
+  (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(std::make_integer_sequence<int, N>{}, f);
+}
+// The abort word in shared memory, and the hand-off between the warps of a pipeline.  A warp posts a
+// value for its successor by writing the data to its mailbox and arriving (every lane, release
+// semantics) on the mailbox's mbarrier; the successor waits for the phase of that step and reads
+// the data (each lane only reads what the same lane of the other warp wrote).  A waiting warp is
+// suspended by the hardware inside mbarrier.try_wait instead of spinning on a flag.
+__device__ __forceinline__ uint32_t ld_volatile_s(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_s(uint32_t addr, uint32_t v) {
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+template <int kOff = 0>
+__device__ __forceinline__ void mbar_arrive_s(uint32_t addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0+%1];" ::"r"(addr), "n"(kOff) : "memory");
+}
+template <int kOff = 0>
+__device__ __forceinline__ bool mbar_try_s(uint32_t addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1+%2], %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(addr), "n"(kOff), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait for a phase of an mbarrier (out of line: the caller tries once inline and comes here
+// only when it has to wait).  Gives up when the CTA's abort word is set (another waiter has given
+// up) or after `limit` SM cycles; then it raises the device error word, sets the abort word and
+// returns false.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t abort_addr, long long limit) {
+  const long long start = clock64();
+  while (true) {
+    if (mbar_try_s(addr, parity)) return true;
+    if (ld_volatile_s(abort_addr) != 0) return false;
+    if (clock64() - start > limit) {
+      g_device_error = 2;
+      st_volatile_s(abort_addr, 1u);
+      return false;
+    }
+  }
+}
+// mbar_wait with the caller's cycle limit and the CTA's abort word (same give-up rule as poll_flag).
+__device__ __forceinline__ bool mbar_wait_lim(uint64_t* bar, uint32_t parity, uint32_t abort_addr, long long limit) {
+  const uint32_t addr = smem_u32(bar);
+  uint32_t ok = 0;
+  long long start = 0;
+  for (int spins = 0;; ++spins) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (spins == 0) start = clock64();
+    if (ld_volatile_s(abort_addr) != 0) return false;
+    if (clock64() - start > limit) {
+      g_device_error = 1;
+      st_volatile_s(abort_addr, 1u);
+      return false;
+    }
+  }
 }
 // two fp32 -> packed bf16x2 (lo in the low half)
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -156,17 +259,28 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 // kWs = warps per column group: 1 (a warp owns the 8 channels of its 16-byte column) or 2 (a warp
 // owns 4 of them: half the per-thread state and tile registers, so more warps fit an SM).
 // kEma = false: TimestepNorm alone (y = the normalised activations; no pole matrices, no states).
-template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false>
-__global__ void __launch_bounds__(kCg * kWs * 32, 1)
+// kWp = pipeline depth along the sequence.  A strip (8 sequences x the channels of a warp) is a
+// serial chain over the steps, so a problem with few strips leaves the SMs short of warps.  With
+// kWp > 1 the CTA holds kWp groups of warps; group w takes the steps i = w, w + kWp, ... of every
+// strip and the running quantities (sum and squared deviations of TimestepNorm, pole states) travel
+// from the warp of step i to the warp of step i + 1 through a mailbox in shared memory, per channel
+// and as soon as they are known: the statistics right after the prefix sums of a channel (the sums
+// of squares are taken about a centre the warp already holds, its own latest mean, and moved to the
+// incoming mean afterwards), the pole states right after the local-state product.  The warps of
+// consecutive steps thus run a few hundred cycles apart instead of a whole step.
+template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false, int kWp = 1>
+__global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
   static_assert(!kXn || kNorm, "the normalised copy exists only with the normalisation");
   static_assert(kEma || (kNorm && !kXn && !kSilu), "without the EMA the kernel is the plain normalisation");
   static_assert(!kCplx || kEma, "complex poles need the EMA");
-  using C = Cfg<kCg, kXn, kCplx>;
+  static_assert(kWp == 1 || (!kXn && !kCplx && kEma), "the pipelined form covers the real EMA without the second output");
+  using C = Cfg<kCg, kXn, kCplx, kWs, kWp>;
   constexpr int kCh = C::kCh;
   constexpr int kCm = C::kCm;
-  constexpr int kThreads = kCg * kWs * 32;
+  constexpr int kThreads = kCg * kWs * kWp * 32;
+  constexpr int kGroup = kCg * kWs;  // warps of one pipeline group
   constexpr int kStages = C::kStages;
   constexpr int kE = 8 / kWs;   // channels per warp
   constexpr int kVw = kE / 2;   // 32-bit words (channel pairs) per tile vector of this warp
@@ -186,10 +300,21 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   uint64_t* xfree = done + kStages;  // kXn: buffer k of the normalised tiles has been read by its store
 
   const uint32_t sm_s = smem_u32(sm);
+  const uint32_t abort_s = sm_s + kOffBar + (2 * kStages + 2) * 8;  // set when a bounded wait gave up
   const int tid = threadIdx.x;
   const int lane = tid & 31;
-  const int warp = (tid >> 5) / kWs;  // column group
-  const int hf = (tid >> 5) % kWs;    // which part of the column's channels
+  const int wp = (tid >> 5) / kGroup;            // pipeline group: takes the steps i = wp (mod kWp)
+  const int wig = (tid >> 5) % kGroup;           // warp inside its group
+  const int warp = wig / kWs;  // column group
+  const int hf = wig % kWs;    // which part of the column's channels
+  const bool issuer = tid == wp * kGroup * 32;  // moves the tiles of this group's steps
+  const long long wait_limit = a.wait_limit;
+  // mailboxes: this warp writes its own, and reads that of the same strip's warp one group before
+  const uint32_t mail_out = sm_s + C::kOffMail + (uint32_t)(tid >> 5) * C::kMailWarp + lane * 16;
+  const uint32_t flag_out = sm_s + C::kOffFlag + (uint32_t)(tid >> 5) * C::kFlagWarp;
+  const int wprev = ((wp + kWp - 1) % kWp) * kGroup + wig;
+  const uint32_t mail_in = sm_s + C::kOffMail + (uint32_t)wprev * C::kMailWarp + lane * 16;
+  const uint32_t flag_in = sm_s + C::kOffFlag + (uint32_t)wprev * C::kFlagWarp;
   const int g = lane >> 2, q = lane & 3;
   const int d0 = blockIdx.x * kCh;
   const int b0 = blockIdx.y * kSeq;
@@ -207,13 +332,18 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
       mbar_init(&xfree[0], 1);
       mbar_init(&xfree[1], 1);
     }
+    st_volatile_s(abort_s, 0u);
+    if (kWp > 1) {  // hand-off barriers: all 32 lanes of the posting warp arrive
+      for (int k = 0; k < C::kWarps * 2 * C::kE; ++k)
+        mbar_init(reinterpret_cast<uint64_t*>(sm + C::kOffFlag) + k, 32);
+    }
     mbar_fence_init();
   }
   __syncthreads();
   if (tid == 0) {
-    for (int s = 0; s < kStages - 1 && s < nsteps; ++s) {
+    for (int s = 0; s < kStages - kWp && s < nsteps; ++s) {
       mbar_expect_tx(&full[s], kStageBytes);
-      tma_load_3d(sm + kOffStages + s * kStageBytes, &tmx, d0, s * kStep, b0, &full[s]);
+      if (s != a.withhold_step) tma_load_3d(sm + kOffStages + s * kStageBytes, &tmx, d0, s * kStep, b0, &full[s]);
     }
   }
 
@@ -352,38 +482,65 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   // ---- running state of this thread: sequence b0 + g, channels 8*warp + e ----------------------
   const int bseq = b0 + g;
   const bool seq_ok = bseq < a.B;
+  // kWp == 1: the running quantities live in registers from step to step.  kWp > 1: they arrive
+  // through the mailbox at every step; a warp only keeps its latest mean per channel (mu_run), the
+  // centre of its next sums of squares.
   float hc[kE][4];   // pole states: poles 2q, 2q+1, 8+2q, 9+2q of channel e
   float hci[kCplx ? kE : 1][4];  // kCplx: their imaginary parts
   float mu_run[kE], m2_run[kE], s1_run[kE];  // running mean, sum of squared deviations, sum of x
   float nbase = 1.f;
   const int cbase = warp * 8 + hf * kE;  // first channel of this warp inside the tile
-#pragma unroll
-  for (int e = 0; e < kE; ++e) {
+  static_for<kE>([&](auto e_c) {
+    constexpr int e = decltype(e_c)::value;
     const int d = d0 + cbase + e;
     const bool ok = seq_ok && d < a.D;
+    if constexpr (kWp > 1) {
+      mu_run[e] = (kNorm && ok) ? a.prev_mean[(size_t)bseq * a.D + d] : 0.f;
+      // The warps of the last group put the call's initial statistics and pole states into their
+      // mailboxes, where step 0 (first group) looks for what "step -1" left (it does not wait: the
+      // barrier before the loop orders these writes).
+      if (wp == kWp - 1) {
+        float c0 = 0.f, vv = 0.f;
+        if (kNorm && ok) {
+          c0 = (float)a.prev_count[bseq];
+          vv = a.prev_var[(size_t)bseq * a.D + d];
+        }
+        sts128<e * 512>(mail_out, make_uint4(__float_as_uint(c0 * mu_run[e]), __float_as_uint(c0 * vv),
+                                             __float_as_uint(mu_run[e]), 0u));
+        float h4[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
-      if (kCplx) {
-        const bool have = ok && a.h_in && pole < a.N;
-        const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
-        hc[e][k] = have ? __ldg(a.h_in + c) : 0.f;
-        hci[e][k] = have ? __ldg(a.h_in + c + 1) : 0.f;
-      } else {
-        hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+        for (int k = 0; k < 4; ++k) {
+          const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
+          h4[k] = (ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+        }
+        sts128<(kE + e) * 512>(mail_out, make_uint4(__float_as_uint(h4[0]), __float_as_uint(h4[1]),
+                                                    __float_as_uint(h4[2]), __float_as_uint(h4[3])));
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int pole = 2 * q + (k & 1) + ((k >> 1) << 3);
+        if (kCplx) {
+          const bool have = ok && a.h_in && pole < a.N;
+          const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
+          hc[e][k] = have ? __ldg(a.h_in + c) : 0.f;
+          hci[e][k] = have ? __ldg(a.h_in + c + 1) : 0.f;
+        } else {
+          hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
+        }
+      }
+      mu_run[e] = 0.f;
+      m2_run[e] = 0.f;
+      s1_run[e] = 0.f;
+      if (kNorm && ok) {
+        const float c0 = (float)a.prev_count[bseq];
+        const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
+        mu_run[e] = mu;
+        m2_run[e] = c0 * vv;
+        s1_run[e] = c0 * mu;
       }
     }
-    mu_run[e] = 0.f;
-    m2_run[e] = 0.f;
-    s1_run[e] = 0.f;
-    if (kNorm && ok) {
-      const float c0 = (float)a.prev_count[bseq];
-      const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
-      mu_run[e] = mu;
-      m2_run[e] = c0 * vv;
-      s1_run[e] = c0 * mu;
-    }
-  }
+  });
   if (kNorm && seq_ok) nbase = (float)a.prev_count[bseq] + 1.f;
   const float ut0 = (2 * q <= g) ? 1.f : 0.f, ut1 = (2 * q + 1 <= g) ? 1.f : 0.f;
   const float eps = a.eps;
@@ -396,50 +553,72 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
   constexpr bool kLeanLsu = kWs > 1;
   const bool odd = kLeanLsu && (g & 1) != 0;
   int toff[8];   // logical: vector j is position toff[j]
-  int soff[8];   // access order: slot j touches position soff[j]
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    toff[j] = (j >> 2) * 16 + 2 * q + (j & 1) + ((j >> 1) & 1) * 8;
-    soff[j] = (j >> 2) * 16 + 2 * q + ((j & 1) ^ (odd ? 1 : 0)) + ((j >> 1) & 1) * 8;
-  }
+  for (int j = 0; j < 8; ++j) toff[j] = (j >> 2) * 16 + 2 * q + (j & 1) + ((j >> 1) & 1) * 8;
+  // Tile addresses: slot j touches position 2q + p + 8 * ((j >> 1) & 1) + 16 * (j >> 2) with
+  // p = (j & 1) ^ odd.  The 128-byte swizzle only looks at the position modulo 8, i.e. at 2q + p, so
+  // two per-thread offsets (p = 0, 1) and compile-time immediates address all eight slots.
+  constexpr int kRowB = kCg == 8 ? 128 : kCg * 16;
+  uint32_t tb[2];
+#pragma unroll
+  for (int pq = 0; pq < 2; ++pq)
+    tb[pq] = vec_off<kCg>(g, 2 * q + pq, warp) + (kWs == 2 ? hf * 8 : 0);
+  const uint32_t tb0 = odd ? tb[1] : tb[0], tb1 = odd ? tb[0] : tb[1];  // slots with even / odd j
+  // base addresses of the per-channel arrays (channel e of this warp adds a compile-time multiple)
+  const uint32_t t_base = sm_s + kOffT + (cbase * 64 + lane) * 4;
+  const uint32_t p_base = sm_s + kOffP + (cbase * kCm * 32 + lane) * 16;
+  const uint32_t g_base = sm_s + kOffG + (cbase * kCm * 32 + lane) * 16;
+  const uint32_t a_base = sm_s + kOffA + (cbase * 16 + 2 * q) * 4 * kCm;
+  const uint32_t wb_base = sm_s + kOffWB + cbase * 8;
 
   __syncthreads();  // matrices visible
 
-  for (int i = 0; i < nsteps; ++i) {
+  bool live = true;  // false once a bounded wait of this thread gave up
+  for (int i = wp; i < nsteps; i += kWp) {
     const int s = i % kStages;
     const uint32_t ph = (uint32_t)((i / kStages) & 1);
     unsigned char* stage = sm + kOffStages + s * kStageBytes;
     const uint32_t stage_s = sm_s + kOffStages + s * kStageBytes;
-    const bool ok = mbar_wait(&full[s], ph);
+    if (ld_volatile_s(abort_s) != 0) live = false;  // another waiter of this CTA gave up: leave together
+    if (!__all_sync(0xffffffffu, live)) break;
+    const bool ok = mbar_wait_lim(&full[s], ph, abort_s, wait_limit);
+    // kWp > 1, first step of this warp (other than step 0): it has no mean of its own yet, so it
+    // waits for the incoming statistics before it centres its sums (`early`)
+    const bool early = kWp > 1 && i < kWp;
+    // phase of the hand-off barriers that the warp of step i - 1 completes with that step
+    const uint32_t hand_par = kWp > 1 ? (uint32_t)((((i > 0 ? i - 1 : 0) / kWp)) & 1) : 0u;
+    const uint32_t st0 = stage_s + tb0, st1 = stage_s + tb1;
     uint32_t v[8][kVw];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    static_for<8>([&](auto j_c) {
+      constexpr int j = decltype(j_c)::value;
+      constexpr int joff = (((j >> 1) & 1) * 8 + (j >> 2) * 16) * kRowB;
       if (kWs == 1) {
-        const uint4 t4 = lds128(stage_s + vec_off<kCg>(g, soff[j], warp));
+        const uint4 t4 = lds128<joff>((j & 1) ? st1 : st0);
         v[j][0] = t4.x; v[j][1] = t4.y; v[j][kVw - 2] = t4.z; v[j][kVw - 1] = t4.w;
       } else {
-        const uint2 t2 = lds64(stage_s + vec_off<kCg>(g, soff[j], warp) + hf * 8);
+        const uint2 t2 = lds64<joff>((j & 1) ? st1 : st0);
         v[j][0] = t2.x; v[j][1] = t2.y;
       }
-    }
+    });
     float invn[8];
-    float inv_end = 0.f, n_end = 1.f;
+    float inv_end = 0.f, n_end = 1.f, n_in = 0.f;
     const bool tail = (i + 1) * kStep > L;
     if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
 #pragma unroll
       for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(nb_f + (float)toff[j]);
-      n_end = nb_f - 1.f + (float)min(kStep, L - i * kStep);  // count after this step
+      n_in = nb_f - 1.f;                                      // count before this step
+      n_end = n_in + (float)min(kStep, L - i * kStep);        // count after this step
       inv_end = rcp_fast(n_end);
     }
-#pragma unroll
     uint32_t vx[kXn ? 8 : 1][kXn ? kVw : 1];  // kXn: words of the normalised tile
-    for (int pp = 0; pp < kVw; ++pp) {
+    static_for<kVw>([&](auto pp_c) {
+      constexpr int pp = decltype(pp_c)::value;
       float yv[2][8];
       float xq[kXn ? 2 : 1][8];
-#pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {
-        const int e = 2 * pp + h2;
+      static_for<2>([&](auto h2_c) {
+        constexpr int h2 = decltype(h2_c)::value;
+        constexpr int e = 2 * pp + h2;
         const int ch = cbase + e;
         float xf[8];
 #pragma unroll
@@ -449,7 +628,26 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
         }
         float xn[8];
         if (kNorm) {
-          const float cm = mu_run[e];
+          // kWp > 1: the statistics entering this step (sum of x, squared deviations about their
+          // mean, that mean) come from the call's arguments at step 0 and from the mailbox of the
+          // warp one step ahead otherwise
+          float s1_in = 0.f, m2_in = 0.f, mean_in = 0.f;
+          auto fetch_stats = [&]() {  // (step 0 finds the call's initial statistics in the mailbox)
+            if (i != 0 && !mbar_try_s<e * 8>(flag_in, hand_par)) {
+              if (!mbar_wait_slow(flag_in + e * 8, hand_par, abort_s, wait_limit)) live = false;
+            }
+            const uint4 m = lds128<e * 512>(mail_in);
+            s1_in = __uint_as_float(m.x);
+            m2_in = __uint_as_float(m.y);
+            mean_in = __uint_as_float(m.z);
+          };
+          float cm = mu_run[e];
+          if constexpr (kWp > 1) {
+            if (early) {
+              fetch_stats();
+              cm = mean_in;
+            }
+          }
           float S1[8], S2[8];
           float tot1, tot2;
           // Prefix sums inside each half (8 positions) of the two chunks: one tf32 MMA against the
@@ -472,7 +670,8 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
               E0[0] = __shfl_sync(0xffffffffu, D0[1], src3); E1[0] = __shfl_sync(0xffffffffu, D1[1], src3);
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
-            k1[0] = s1_run[e];
+            // kWp > 1: offsets of the halves only; the running total is added once it has arrived
+            k1[0] = kWp > 1 ? 0.f : s1_run[e];
             k1[1] = k1[0] + E0[0];
             k1[2] = k1[1] + E1[0];
             k1[3] = k1[2] + E0[2];
@@ -509,7 +708,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
             const float ea = E0[0], fa = E1[0], eb = E0[2], fb = E1[2];
-            k2[0] = m2_run[e];
+            k2[0] = kWp > 1 ? 0.f : m2_run[e];
             k2[1] = k2[0] + ea;
             k2[2] = k2[1] + fa;
             k2[3] = k2[2] + eb;
@@ -523,14 +722,36 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
             const float c2 = __uint_as_float(__float_as_uint(cm * cm) & 0xffffe000u);
             tot2 -= (float)(kStep - (L - i * kStep)) * c2;
           }
+          // running totals entering the step; the incoming squared deviations are about the
+          // incoming mean and move to this step's centre (sum (x-c)^2 = sum (x-m)^2 + n (m-c)^2)
+          float m2_base;
+          if constexpr (kWp > 1) {
+            if (!early) fetch_stats();
+            const float dm = mean_in - cm;
+            m2_base = fmaf(n_in * dm, dm, m2_in);
+            tot1 += s1_in;
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+              k1[jp] += s1_in;
+              k2[jp] += m2_base;
+            }
+          } else {
+            m2_base = m2_run[e];
+          }
           // running statistics after this step: the new mean, and the squared deviations moved
-          // from the old centre c to it (sum (x-c)^2 = sum (x-m)^2 + n (m-c)^2)
-          s1_run[e] = tot1;
+          // from the centre c to it
           const float mnew = tot1 * inv_end;
           const float shift = mnew - cm;
+          const float m2new = fmaf(-shift * shift, n_end, m2_base + tot2);
           mu_run[e] = mnew;
-          m2_run[e] = fmaf(-shift * shift, n_end, m2_run[e] + tot2);
-          const uint2 wbu = lds64(sm_s + kOffWB + ch * 8);
+          if constexpr (kWp > 1) {
+            sts128<e * 512>(mail_out, make_uint4(__float_as_uint(tot1), __float_as_uint(m2new), __float_as_uint(mnew), 0u));
+            mbar_arrive_s<e * 8>(flag_out);
+          } else {
+            s1_run[e] = tot1;
+            m2_run[e] = m2new;
+          }
+          const uint2 wbu = lds64<e * 8>(wb_base);
           const float2 wb = make_float2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
           {
             const f32x2 ncm2 = pack2(-cm, -cm), eps2 = pack2(eps, eps);
@@ -557,25 +778,24 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
         if (!kEma) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) yv[h2][j] = xn[j];
-          continue;
+          return;
         }
         // A fragment of xn: a0 (row g: t = 2q, 2q+1), a1 (row g+8), a2 (row g: t = 2q+8, 2q+9), a3 (row g+8)
         const uint32_t xa0 = pack_bf16(xn[0], xn[1]), xa2 = pack_bf16(xn[2], xn[3]);
         const uint32_t xa1 = pack_bf16(xn[4], xn[5]), xa3 = pack_bf16(xn[6], xn[7]);
-        const uint2 tr = make_uint2(lds32(sm_s + kOffT + ((ch * 2 + 0) * 32 + lane) * 4),
-                                    lds32(sm_s + kOffT + ((ch * 2 + 1) * 32 + lane) * 4));
+        const uint2 tr = make_uint2(lds32<e * 256>(t_base), lds32<e * 256 + 128>(t_base));
         float W0[4], W1[4];  // Toeplitz term of the outputs (positions 0..7 and 8..15 of each chunk)
         mma_bf16(W0, xa0, xa1, xa2, xa3, tr.x, 0u, 0.f, 0.f, 0.f, 0.f);
         mma_bf16(W1, xa0, xa1, xa2, xa3, tr.y, tr.x, 0.f, 0.f, 0.f, 0.f);
         float Y0[4], Y1[4];
         if (kCplx) {
-          const uint4 prr = lds128(sm_s + kOffP + ((ch * 2 + 0) * 32 + lane) * 16);
-          const uint4 pri = lds128(sm_s + kOffP + ((ch * 2 + 1) * 32 + lane) * 16);
-          const uint4 grr = lds128(sm_s + kOffG + ((ch * 2 + 0) * 32 + lane) * 16);
-          const uint4 gri = lds128(sm_s + kOffG + ((ch * 2 + 1) * 32 + lane) * 16);
+          const uint4 prr = lds128<e * 1024>(p_base);
+          const uint4 pri = lds128<e * 1024 + 512>(p_base);
+          const uint4 grr = lds128<e * 1024>(g_base);
+          const uint4 gri = lds128<e * 1024 + 512>(g_base);
           // q^16 of poles 2q, 2q+1 and 8+2q, 9+2q as (re, im) pairs
-          const uint4 a0u = lds128(sm_s + kOffA + (ch * 16 + 2 * q) * 8);
-          const uint4 a1u = lds128(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 8);
+          const uint4 a0u = lds128<e * 128>(a_base);
+          const uint4 a1u = lds128<e * 128 + 64>(a_base);
           const float ar[4] = {__uint_as_float(a0u.x), __uint_as_float(a0u.z), __uint_as_float(a1u.x), __uint_as_float(a1u.z)};
           const float ai[4] = {__uint_as_float(a0u.y), __uint_as_float(a0u.w), __uint_as_float(a1u.y), __uint_as_float(a1u.w)};
           float Hr0[4], Hr1[4], Hi0[4], Hi1[4];
@@ -606,10 +826,10 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
           mma_bf16(Y0, hi0, hi1, hi2, hi3, gri.x, gri.y, Z0[0], Z0[1], Z0[2], Z0[3]);
           mma_bf16(Y1, hi0, hi1, hi2, hi3, gri.z, gri.w, Z1[0], Z1[1], Z1[2], Z1[3]);
         } else {
-          const uint4 pr = lds128(sm_s + kOffP + (ch * 32 + lane) * 16);
-          const uint4 gr = lds128(sm_s + kOffG + (ch * 32 + lane) * 16);
-          const uint2 aq0u = lds64(sm_s + kOffA + (ch * 16 + 2 * q) * 4);
-          const uint2 aq1u = lds64(sm_s + kOffA + (ch * 16 + 8 + 2 * q) * 4);
+          const uint4 pr = lds128<e * 512>(p_base);
+          const uint4 gr = lds128<e * 512>(g_base);
+          const uint2 aq0u = lds64<e * 64>(a_base);
+          const uint2 aq1u = lds64<e * 64 + 32>(a_base);
           const float2 aq0 = make_float2(__uint_as_float(aq0u.x), __uint_as_float(aq0u.y));
           const float2 aq1 = make_float2(__uint_as_float(aq1u.x), __uint_as_float(aq1u.y));
           // local state contributions of the two chunks
@@ -617,16 +837,37 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
           mma_bf16(H0, xa0, xa1, xa2, xa3, pr.x, pr.y, 0.f, 0.f, 0.f, 0.f);  // poles 2q, 2q+1
           mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
           // states entering chunk 0 (= carried) and chunk 1, and the new carry
-          const float hs0[4] = {hc[e][0], hc[e][1], hc[e][2], hc[e][3]};
-          float hs1[4];
+          float hs0[4];
+          if constexpr (kWp > 1) {
+            // pole states entering the step: from the mailbox of the warp one step ahead (step 0
+            // finds the call's h_in there)
+            if (i != 0 && !mbar_try_s<(kE + e) * 8>(flag_in, hand_par)) {
+              if (!mbar_wait_slow(flag_in + (kE + e) * 8, hand_par, abort_s, wait_limit)) live = false;
+            }
+            const uint4 m = lds128<(kE + e) * 512>(mail_in);
+            hs0[0] = __uint_as_float(m.x); hs0[1] = __uint_as_float(m.y);
+            hs0[2] = __uint_as_float(m.z); hs0[3] = __uint_as_float(m.w);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) hs0[k] = hc[e][k];
+          }
+          float hs1[4], hn[4];
           hs1[0] = fmaf(aq0.x, hs0[0], H0[0]);
           hs1[1] = fmaf(aq0.y, hs0[1], H0[1]);
           hs1[2] = fmaf(aq1.x, hs0[2], H1[0]);
           hs1[3] = fmaf(aq1.y, hs0[3], H1[1]);
-          hc[e][0] = fmaf(aq0.x, hs1[0], H0[2]);
-          hc[e][1] = fmaf(aq0.y, hs1[1], H0[3]);
-          hc[e][2] = fmaf(aq1.x, hs1[2], H1[2]);
-          hc[e][3] = fmaf(aq1.y, hs1[3], H1[3]);
+          hn[0] = fmaf(aq0.x, hs1[0], H0[2]);
+          hn[1] = fmaf(aq0.y, hs1[1], H0[3]);
+          hn[2] = fmaf(aq1.x, hs1[2], H1[2]);
+          hn[3] = fmaf(aq1.y, hs1[3], H1[3]);
+          if constexpr (kWp > 1) {
+            sts128<(kE + e) * 512>(mail_out, make_uint4(__float_as_uint(hn[0]), __float_as_uint(hn[1]),
+                                                        __float_as_uint(hn[2]), __float_as_uint(hn[3])));
+            mbar_arrive_s<(kE + e) * 8>(flag_out);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) hc[e][k] = hn[k];
+          }
           const uint32_t ha0 = pack_bf16(hs0[0], hs0[1]), ha1 = pack_bf16(hs1[0], hs1[1]);
           const uint32_t ha2 = pack_bf16(hs0[2], hs0[3]), ha3 = pack_bf16(hs1[2], hs1[3]);
           // outputs: the carried-state term accumulates onto the Toeplitz term, which does not
@@ -640,7 +881,7 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) yv[h2][j] = silu_tanh(yv[h2][j]);
         }
-      }
+      });
 #pragma unroll
       for (int j = 0; j < 8; j += 2) {
         const uint32_t o0 = pack_bf16(yv[0][j], yv[1][j]), o1 = pack_bf16(yv[0][j + 1], yv[1][j + 1]);
@@ -652,51 +893,81 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
           vx[j + 1][pp] = odd ? n0 : n1;
         }
       }
-    }
+    });
     if (kXn) {
       // the store that read this buffer two steps ago must have drained it
-      if (i >= 2 && !mbar_wait(&xfree[i & 1], (uint32_t)(((i >> 1) - 1) & 1))) break;
+      if (i >= 2 && !mbar_wait_lim(&xfree[i & 1], (uint32_t)(((i >> 1) - 1) & 1), abort_s, wait_limit)) live = false;
       const uint32_t xb = sm_s + C::kOffXn + (i & 1) * kStageBytes;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      static_for<8>([&](auto j_c) {
+        constexpr int j = decltype(j_c)::value;
+        constexpr int joff = (((j >> 1) & 1) * 8 + (j >> 2) * 16) * kRowB;
         if (kWs == 1)
-          sts128(xb + vec_off<kCg>(g, soff[j], warp), make_uint4(vx[j][0], vx[j][1], vx[j][kVw - 2], vx[j][kVw - 1]));
+          sts128<joff>(xb + ((j & 1) ? tb1 : tb0), make_uint4(vx[j][0], vx[j][1], vx[j][kVw - 2], vx[j][kVw - 1]));
         else
-          sts64(xb + vec_off<kCg>(g, soff[j], warp) + hf * 8, make_uint2(vx[j][0], vx[j][1]));
-      }
+          sts64<joff>(xb + ((j & 1) ? tb1 : tb0), make_uint2(vx[j][0], vx[j][1]));
+      });
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    static_for<8>([&](auto j_c) {
+      constexpr int j = decltype(j_c)::value;
+      constexpr int joff = (((j >> 1) & 1) * 8 + (j >> 2) * 16) * kRowB;
       if (kWs == 1)
-        sts128(stage_s + vec_off<kCg>(g, soff[j], warp), make_uint4(v[j][0], v[j][1], v[j][kVw - 2], v[j][kVw - 1]));
+        sts128<joff>((j & 1) ? st1 : st0, make_uint4(v[j][0], v[j][1], v[j][kVw - 2], v[j][kVw - 1]));
       else
-        sts64(stage_s + vec_off<kCg>(g, soff[j], warp) + hf * 8, make_uint2(v[j][0], v[j][1]));
-    }
+        sts64<joff>((j & 1) ? st1 : st0, make_uint2(v[j][0], v[j][1]));
+    });
     fence_proxy_async();
     __syncwarp();
-    if (!ok) break;
-    if (lane == 0) mbar_arrive(&done[s]);
-    // warps run on to the next stage on their own; only the issuing thread waits for the whole tile
-    if (tid == 0) {
-      if (!mbar_wait(&done[s], ph)) break;
-      tma_store_3d(&tmy, d0, i * kStep, b0, stage);
-      if (kXn) tma_store_3d(&tmn, d0, i * kStep, b0, sm + C::kOffXn + (i & 1) * kStageBytes);
-      bulk_commit();
-      if (kXn) {
-        bulk_wait_read<1>();  // the stores of the step before have drained their stage and buffer
-        if (i >= 1) mbar_arrive(&xfree[(i - 1) & 1]);
-      }
-      if (i + kStages - 1 < nsteps) {
-        if (!kXn) bulk_wait_read<1>();  // the store issued one step ago has drained its stage
-        const int s2 = (i + kStages - 1) % kStages;
-        mbar_expect_tx(&full[s2], kStageBytes);
-        tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i + kStages - 1) * kStep, b0, &full[s2]);
+    // A wait that gave up (never expected) leaves the tile unfinished: nothing more is stored, and
+    // every warp of the CTA leaves the loop at its next step (abort word).
+    if (!ok) live = false;
+    if (__all_sync(0xffffffffu, live)) {
+      if (lane == 0) mbar_arrive(&done[s]);
+      // warps run on to their next stage on their own; only the issuing thread of this group waits
+      // for the whole tile
+      if (issuer) {
+        if (mbar_wait_lim(&done[s], ph, abort_s, wait_limit)) {
+          tma_store_3d(&tmy, d0, i * kStep, b0, stage);
+          if (kXn) tma_store_3d(&tmn, d0, i * kStep, b0, sm + C::kOffXn + (i & 1) * kStageBytes);
+          bulk_commit();
+          if (kXn) {
+            bulk_wait_read<1>();  // the stores of the step before have drained their stage and buffer
+            if (i >= 1) mbar_arrive(&xfree[(i - 1) & 1]);
+          }
+          // refill: the stage of this thread's previous store (step i - kWp) takes tile i - kWp + kStages
+          const int nt = i + kStages - kWp;
+          if (nt < nsteps) {
+            if (!kXn) bulk_wait_read<1>();  // the store issued before this one has drained its stage
+            const int s2 = nt % kStages;
+            mbar_expect_tx(&full[s2], kStageBytes);
+            if (nt != a.withhold_step)
+              tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, nt * kStep, b0, &full[s2]);
+          }
+        } else {
+          live = false;
+        }
       }
     }
   }
-  if (tid == 0) bulk_wait<0>();
+  if (issuer) bulk_wait<0>();
+  if (ld_volatile_s(abort_s) != 0) live = false;
+  if (!live) return;  // the error word is raised; the final statistics and states are not written
 
   // ---- final statistics and states -------------------------------------------------------------
+  if constexpr (kWp > 1) {
+    // held by the group of the last step, in its own mailbox
+    if (wp != (nsteps - 1) % kWp) return;
+    static_for<kE>([&](auto e_c) {
+      constexpr int e = decltype(e_c)::value;
+      if (kNorm) {
+        const uint4 m = lds128<e * 512>(mail_out);
+        m2_run[e] = __uint_as_float(m.y);
+        mu_run[e] = __uint_as_float(m.z);
+      }
+      const uint4 hm = lds128<(kE + e) * 512>(mail_out);
+      hc[e][0] = __uint_as_float(hm.x); hc[e][1] = __uint_as_float(hm.y);
+      hc[e][2] = __uint_as_float(hm.z); hc[e][3] = __uint_as_float(hm.w);
+    });
+  }
   if (seq_ok && q == 0) {
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
@@ -733,11 +1004,12 @@ __global__ void __launch_bounds__(kCg * kWs * 32, 1)
 }
 
 // xn (with its strides nsb, nsl) is the optional second output; kXn selects the kernel form.
-template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true, bool kCplx = false>
+template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true, bool kCplx = false,
+          int kWp = 1>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s, void* xn = nullptr,
                            long long nsb = 0, long long nsl = 0) {
-  using C = Cfg<kCg, kXn, kCplx>;
+  using C = Cfg<kCg, kXn, kCplx, kWs, kWp>;
   const CUtensorMapSwizzle sw = kCg == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUtensorMap tx, ty, tn;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
@@ -747,7 +1019,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   } else {
     tn = ty;
   }
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma, kCplx>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma, kCplx, kWp>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -758,7 +1030,11 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
     return false;
   }
   dim3 grid((a.D + C::kCh - 1) / C::kCh, (a.B + kSeq - 1) / kSeq);
-  launch(kern, grid, dim3(kCg * kWs * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, tn, a);
+  launch(kern, grid, dim3(kCg * kWs * kWp * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, tn, a);
+  static const std::string name = std::string("tsn_ema_mma tile=") + std::to_string(kCg) + " warps_per_column=" +
+                                  std::to_string(kWs) + " pipe=" + std::to_string(kWp) + (kNorm ? " norm" : "") +
+                                  (kEma ? " ema" : "") + (kCplx ? " complex" : "") + (kXn ? " xn" : "");
+  g_last_kernel.store(name.c_str(), std::memory_order_relaxed);
   return true;
 }
 
@@ -769,14 +1045,27 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
 // B >= 4 (rows of the MMAs are sequences), L < 2^24, and L a multiple of 32 when a state is
 // exported.  Returns false, launching nothing, outside of it.
 bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
-                long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a_in, cudaStream_t s) {
+                long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a_arg, cudaStream_t s) {
   if (g_options[OPT_DISABLE_MMA].load() != 0) return false;
+  StreamArgs a_in = a_arg;
+  {
+    const int lim = g_options[OPT_WAIT_LIMIT].load(), wh = g_options[OPT_WITHHOLD_LOAD].load();
+    a_in.wait_limit = lim > 0 ? (long long)lim : 4000000000LL;
+    a_in.withhold_step = wh > 0 ? wh : -1;
+  }
   if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || a_in.mask != nullptr) return false;
   const bool want_xn = xn != nullptr;  // second output: the normalised activations, strided like y
   if (want_xn && (!norm || xn == y || xn == x)) return false;
   const bool ema = a_in.N > 0;  // N = 0: TimestepNorm alone
   if (!ema && (!norm || want_xn || a_in.silu || a_in.h_in || a_in.h_out)) return false;
-  if (a_in.N > 16 || a_in.N < 0 || a_in.B < 4 || a_in.L >= (1 << 24) || a_in.D < 8) return false;
+  const int forced = g_options[OPT_MMA_TILE].load();
+  const bool forced_pipe = forced == 222 || forced == 224 || forced == 422 || forced == 124;
+  // fewer than 4 sequences leave most rows of the MMAs empty: only the pipelined form, which fills the SMs
+  // from the sequence length, is then worth more than the SIMT kernels
+  const bool can_pipe = ema && !want_xn && !a_in.cplx;
+  if (a_in.N > 16 || a_in.N < 0 || (a_in.B < 4 && !(forced_pipe || (forced == 0 && can_pipe))) ||
+      a_in.L >= (1 << 24) || a_in.D < 8)
+    return false;
   if (a_in.h_out && (a_in.L % kStep) != 0) return false;
   if ((a_in.B + kSeq - 1) / kSeq > 65535) return false;
   // Tile width.  Large problems: 64 channels, or 56 when that fills the 148 SMs in fewer or
@@ -794,11 +1083,19 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     return (double)waves * ch;  // time ~ waves x work per CTA
   };
   int tile = g_options[OPT_MMA_TILE].load();
-  if (tile != 2 && tile != 4 && tile != 7 && tile != 8 && tile != 22) {
+  // pipelined forms (real EMA, with or without the normalisation, no second output)
+  if ((tile == 222 || tile == 224 || tile == 422 || tile == 124) && (a_in.cplx || !ema || want_xn)) tile = 0;
+  if (tile != 2 && tile != 4 && tile != 7 && tile != 8 && tile != 22 && tile != 222 && tile != 224 && tile != 422 &&
+      tile != 124) {
     // (the EMA alone is closer to the memory bound and prefers the 128-byte rows of the 64-channel
     // tile: 1.71 against 2.02 ms at B = 64, L = 16384, D = 2048, unless 56 channels save a wave)
     if (ctas(64) >= 148 || ctas(56) >= 148)
       tile = waves_cost(56) * (norm ? 1.0 : 1.15) < waves_cost(64) ? 7 : 8;
+    else if (can_pipe && (ctas(16) <= 148 || a_in.B < 4))
+      // too few strips for the SMs: four groups of warps per 16-channel strip set, pipelined along the
+      // sequence (B = 8, L = 32768, D = 2048: 1.21 -> 1.05 ms; B = 16, L = 4096, D = 1024: 0.168 -> 0.143 ms;
+      // the EMA alone on that shape: 0.153 -> 0.102 ms)
+      tile = 224;
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
   }
@@ -832,7 +1129,11 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
                      : launch_variant<true, 2, false, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
   }
 #define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
-  (tile == 22  ? launch_variant<NORM, 2, SILU, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)     \
+  (tile == 222 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+   : tile == 224 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+   : tile == 422 ? launch_variant<NORM, 4, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+   : tile == 124 ? launch_variant<NORM, 1, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+   : tile == 22  ? launch_variant<NORM, 2, SILU, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)     \
    : tile == 7 ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
    : tile == 8 ? launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
    : tile == 4 ? launch_variant<NORM, 4, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \

@@ -293,6 +293,7 @@ static bool launch_rowres(const RowArgs& a, size_t smem, cudaStream_t s) {
   });
   if (!attr_ok) return false;
   launch(kern, dim3((unsigned)((long long)a.B * a.D)), dim3(kT), smem, (void*)s, a);
+  g_last_kernel.store("rowres", std::memory_order_relaxed);
   return true;
 }
 

@@ -376,6 +376,7 @@ static bool launch_one(const CUtensorMap& tx, const CUtensorMap& ty, const CUten
   }
   dim3 grid((a.D + kW - 1) / kW, a.B);
   launch(kern, grid, dim3(kW), (size_t)smem, (void*)s, tx, ty, tn, tm ? *tm : ty, tr ? *tr : ty, a);
+  g_last_kernel.store("stream_cl", std::memory_order_relaxed);
   return true;
 }
 

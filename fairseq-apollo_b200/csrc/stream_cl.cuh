@@ -19,6 +19,9 @@ struct StreamArgs {
   int has_xn;
   float *cummean, *cumrstd;  // training saves of the norm-only mode, (B, L, D) fp32 contiguous, or NULL
   int cplx;  // complex poles: q, g are interleaved (re, im) (K, N, 2); states (B, D, N, 2)
+  // set by the tensor-core path itself (callers leave them alone)
+  long long wait_limit;  // SM cycles after which a bounded wait gives up
+  int withhold_step;     // test aid: step whose tile is never loaded, or -1
 };
 
 // Tries the streamed TMA path for TimestepNorm (norm), causal EMA (ema) or both fused.  Returns

@@ -44,9 +44,9 @@ class IncrementalStateMixin:
 
 
 def require_no_grad(*tensors):
-    """The CUDA path implements the forward pass only."""
+    """Entry points that carry an incremental state (decode helpers) are inference-only."""
     import torch
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
         raise NotImplementedError(
-            "mega_b200 implements the forward pass only: call the module under torch.no_grad() "
-            "(backward kernels are not part of this build)")
+            "this entry point is an inference helper (incremental state, single-step update): call it "
+            "under torch.no_grad(); the differentiable path is the module's forward")

@@ -17,6 +17,11 @@ class AttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, scale=1.0, dropout=0.0, use_causal_mask=True, training=True):
+        ctx.qk_dtypes = (q.dtype, k.dtype)
+        if q.dtype != v.dtype or k.dtype != v.dtype:
+            # the Mega block's rotary embedding returns float32 queries and keys whatever the model's
+            # dtype (relative_positional_bias.py:83-89): the products run in the values' dtype
+            q, k = q.to(v.dtype), k.to(v.dtype)
         qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)       # (B, N, L, H)
         s = torch.matmul(qh, kh.transpose(-1, -2))                                # (B, N, L, L)
         if scale != 1.0:
@@ -44,7 +49,8 @@ class AttentionFunction(torch.autograd.Function):
             s_grad = s_grad * ctx.scale
         q_grad = torch.matmul(s_grad, kh)
         k_grad = torch.matmul(s_grad.transpose(-1, -2), qh)
-        return (q_grad.transpose(1, 2).contiguous(), k_grad.transpose(1, 2).contiguous(),
+        return (q_grad.transpose(1, 2).contiguous().to(ctx.qk_dtypes[0]),
+                k_grad.transpose(1, 2).contiguous().to(ctx.qk_dtypes[1]),
                 v_grad.transpose(1, 2).contiguous(), None, None, None, None)
 
 

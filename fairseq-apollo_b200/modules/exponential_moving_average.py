@@ -147,7 +147,7 @@ class MultiHeadEMA(IncrementalStateMixin, nn.Module):
         if incremental_state is not None:
             saved_state = self._get_input_buffer(incremental_state)
             h = saved_state.get('prev_state')
-            if seq_len == 1:
+            if seq_len == 1 and padding_mask is None:
                 out, h = ops.ema_step(x, p, q, g, self.omega, h, silu=silu)
             else:
                 out, h = ops.ema_forward(x, p, q, g, self.omega, padding_mask, h, want_state=True, silu=silu)

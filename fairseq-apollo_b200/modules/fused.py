@@ -89,32 +89,93 @@ def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):
     return cache[1:]
 
 
+class _StepPlan:
+    """Everything a single-token step passes to the C entry point, converted once: the ctypes
+    argument list with the pointers of the parameters and of the running state, and a second count
+    array (the step writes the bumped counts there from its one launch; the two arrays alternate).
+    Valid for as long as the state tensors, the batch size, the dtype and the options stay the same
+    (``key``); the caller rebuilds it otherwise (new generation, reordered beams, ...)."""
+
+    __slots__ = ("key", "fn", "args", "count_ptr", "count_alt", "keep")
+
+    def __init__(self, key, fn, args, count_ptr, count_alt, keep):
+        self.key, self.fn, self.args, self.count_ptr, self.count_alt, self.keep = key, fn, args, count_ptr, count_alt, keep
+
+
 def _decode_step(norm, move, x, incremental_state, activation, return_normed):
-    """Single-token step (x: (B, 1, D)): one fused kernel, running state updated in place."""
+    """Single-token step (x: (B, 1, D)): one fused kernel, one launch, running state updated in place."""
+    import ctypes
+    from .. import _lib
     bsz, _, dim = x.shape
+    nstate = incremental_state.get(norm._state_key) if hasattr(norm, "_state_key") else None
+    if nstate is None:
+        norm._state_key = norm._get_full_incremental_state_key("norm_state")
+        move._state_key = move._get_full_incremental_state_key("ema_state")
+        nstate = incremental_state.get(norm._state_key)
+    estate = incremental_state.get(move._state_key)
+    if nstate is None or estate is None or 'prev_mean' not in nstate or estate.get('prev_state') is None:
+        nstate, estate = _seed_decode_state(norm, move, bsz, dim, x.device, incremental_state)
+    count, mean, var, h = nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'], estate['prev_state']
     gamma, beta, p, q, g, omega = _fp32_params(norm, move)
+    key = (mean.data_ptr(), var.data_ptr(), h.data_ptr(), gamma.data_ptr(), bsz, x.dtype, activation, return_normed)
+    plan = getattr(move, "_step_plan", None)
+    if plan is None or plan.key != key or plan.count_ptr != count.data_ptr():
+        sdtype = torch.complex64 if move.complex else torch.float32
+        if (mean.dtype != torch.float32 or not mean.is_contiguous() or var.dtype != torch.float32
+                or not var.is_contiguous() or h.dtype != sdtype or not h.is_contiguous()
+                or count.dtype != torch.int64 or not count.is_contiguous()):
+            nstate['prev_mean'], nstate['prev_var'] = mean.float().contiguous(), var.float().contiguous()
+            nstate['prev_count'] = count.long().contiguous()
+            estate['prev_state'] = h.to(sdtype).contiguous()
+            return _decode_step(norm, move, x, incremental_state, activation, return_normed)
+        lib = _lib.lib()
+        fn = lib.mega_tsn_cema_step if move.complex else lib.mega_tsn_ema_step
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        count_alt = torch.empty_like(count)
+        # x, y, xn_out, dtype, B, D, count, count_next, mean, var, gamma, beta, eps, p, q, g, omega, N, h, flags, stream
+        args = [vp(0), vp(0), vp(None), ci(ops._dt(x)), ci(bsz), ci(dim), vp(count.data_ptr()),
+                vp(count_alt.data_ptr()), vp(mean.data_ptr()), vp(var.data_ptr()), vp(gamma.data_ptr()),
+                vp(beta.data_ptr()), ctypes.c_double(norm.eps), vp(p.data_ptr()), vp(q.data_ptr()), vp(g.data_ptr()),
+                vp(omega.data_ptr()), ci(p.shape[1]), vp(h.data_ptr()),
+                ctypes.c_uint(ops.EMA_SILU if activation == 'silu' else 0), vp(0)]
+        plan = _StepPlan(key, fn, args, count.data_ptr(), count_alt, (gamma, beta, p, q, g, omega, mean, var, h))
+        move._step_plan = plan
+    args = plan.args
+    y = torch.empty_like(x)
+    args[0].value = x.data_ptr()
+    args[1].value = y.data_ptr()
+    xn = None
+    if return_normed:
+        xn = torch.empty_like(x)
+        args[2].value = xn.data_ptr()
+    # counts: read from the state's array, written to the other one, which becomes the state's
+    alt = plan.count_alt
+    args[6].value = count.data_ptr()
+    args[7].value = alt.data_ptr()
+    args[20].value = torch.cuda.current_stream(x.device).cuda_stream
+    if torch.cuda.current_device() == x.device.index:
+        rc = plan.fn(*args)
+    else:
+        with torch.cuda.device(x.device):
+            rc = plan.fn(*args)
+    if rc != 0:
+        _lib.check(rc, "tsn_ema_step")
+    nstate['prev_count'] = alt
+    plan.count_alt, plan.count_ptr = count, alt.data_ptr()
+    return (y, xn) if return_normed else y
+
+
+def _seed_decode_state(norm, move, bsz, dim, device, incremental_state):
+    """First single-token call of a generation: running statistics from the priors (fresh tensors,
+    never views of the parameters: the step updates them in place) and zero pole states."""
     nstate = norm._get_input_buffer(incremental_state)
     if 'prev_mean' not in nstate:
         count, mean, var, nstate = norm.initial_statistics(bsz, incremental_state)
-        nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'] = count.clone(), mean, var
+        nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'] = count.clone(), mean.clone(), var.clone()
         norm._set_input_buffer(incremental_state, nstate)
-    for k in ('prev_mean', 'prev_var'):
-        t = nstate[k]
-        if t.dtype != torch.float32 or not t.is_contiguous():
-            nstate[k] = t.float().contiguous()
     estate = move._get_input_buffer(incremental_state)
-    h = estate.get('prev_state')
-    sdtype = torch.complex64 if move.complex else torch.float32
-    if h is None:
-        h = torch.zeros(bsz, dim, move.ndim, device=x.device, dtype=sdtype)
-    elif h.dtype != sdtype or not h.is_contiguous():
-        h = h.to(sdtype).contiguous()
-    estate['prev_state'] = h
+    if estate.get('prev_state') is None:
+        sdtype = torch.complex64 if move.complex else torch.float32
+        estate['prev_state'] = torch.zeros(bsz, dim, move.ndim, device=device, dtype=sdtype)
     move._set_input_buffer(incremental_state, estate)
-    y = torch.empty_like(x)
-    xn = torch.empty_like(x) if return_normed else None
-    step = ops.tsn_cema_step_ if move.complex else ops.tsn_ema_step_
-    step(x.view(bsz, dim), y.view(bsz, dim), nstate['prev_count'], nstate['prev_mean'],
-         nstate['prev_var'], gamma, beta, norm.eps, p, q, g, omega, h,
-         silu=activation == 'silu', xn_out=None if xn is None else xn.view(bsz, dim))
-    return (y, xn) if return_normed else y
+    return nstate, estate

@@ -58,11 +58,13 @@ class TimestepNorm(IncrementalStateMixin, nn.Module):
                 prev_var = saved_state['prev_var']
                 prev_count = saved_state['prev_count']
         if prev_count is None:
-            prev_count = self.prior_count.expand(batch_size).contiguous()
+            prev_count = self.prior_count.expand(batch_size).clone()
+        # fresh tensors: a (1, G) expand of an fp32 parameter is a view of the parameter itself, and
+        # the decode step updates its statistics in place
         if prev_mean is None:
-            prev_mean = self.prior_mean.detach().float().expand(batch_size, -1).contiguous()
+            prev_mean = self.prior_mean.detach().float().expand(batch_size, -1).clone()
         if prev_var is None:
-            prev_var = torch.exp(self.prior_logv.detach().float()).expand(batch_size, -1).contiguous()
+            prev_var = torch.exp(self.prior_logv.detach().float()).expand(batch_size, -1).clone()
         return prev_count, prev_mean, prev_var, saved_state
 
     def store_statistics(self, incremental_state, saved_state, count, mean, var):

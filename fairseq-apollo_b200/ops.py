@@ -285,26 +285,32 @@ def sqn_ema_forward(x, gamma, beta, eps, p, q, g, omega, padding_mask=None, bidi
     return y
 
 
-def tsn_ema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None):
+def tsn_ema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None,
+                  count_next=None):
     """In-place decode step: x, y (B, D) contiguous; count (B) int64, mean/var (B, D) fp32 and
     h (B, D, N) fp32 are UPDATED IN PLACE (pass count=None to skip the norm).  All parameter
-    tensors must already be fp32 and contiguous: nothing is converted or allocated here."""
+    tensors must already be fp32 and contiguous: nothing is converted or allocated here.
+    With ``count_next`` (a second (B) int64 tensor) the bumped counts go there from the same launch
+    and ``count`` stays as it was; without it a second launch bumps ``count`` in place."""
     bsz, dim = x.shape
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().mega_tsn_ema_step(
-            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, _ptr(count), _ptr(mean), _ptr(var),
+            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, _ptr(count), _ptr(count_next), _ptr(mean),
+            _ptr(var),
             _ptr(gamma), _ptr(beta), float(eps), p.data_ptr(), q.data_ptr(), g.data_ptr(), omega.data_ptr(),
             p.shape[1], h.data_ptr(), EMA_SILU if silu else 0, _stream()), "tsn_ema_step")
     return y
 
 
-def tsn_cema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None):
+def tsn_cema_step_(x, y, count, mean, var, gamma, beta, eps, p, q, g, omega, h, silu=False, xn_out=None,
+                   count_next=None):
     """tsn_ema_step_ for the complex layer: q, g (K, N, 2) and h (B, D, N, 2) are fp32 views of the
     complex64 tensors; everything is updated in place, nothing is converted or allocated."""
     bsz, dim = x.shape
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().mega_tsn_cema_step(
-            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, count.data_ptr(), mean.data_ptr(),
+            x.data_ptr(), y.data_ptr(), _ptr(xn_out), _dt(x), bsz, dim, count.data_ptr(), _ptr(count_next),
+            mean.data_ptr(),
             var.data_ptr(), gamma.data_ptr(), beta.data_ptr(), float(eps), p.data_ptr(), q.data_ptr(), g.data_ptr(),
             omega.data_ptr(), p.shape[1], h.data_ptr(), EMA_SILU if silu else 0, _stream()), "tsn_cema_step")
     return y

@@ -77,7 +77,17 @@ MEGA_API uint64_t mega_launch_count(void);
 #define MEGA_OPT_DISABLE_MMA 1 /* non-zero: skip the tensor-core kernels */
 #define MEGA_OPT_MMA_TILE 2    /* 2, 4, 7, 8: force 16-, 32-, 56-, 64-channel tensor-core tiles; 22: 16 channels
                                   with two warps per 16-byte column; 0: automatic */
+#define MEGA_OPT_WAIT_LIMIT 3    /* > 0: SM cycles after which a bounded device-side wait gives up (default ~2 s) */
+#define MEGA_OPT_WITHHOLD_LOAD 4 /* test aid, value k > 0: the tensor-core kernel never issues the TMA load of its
+                                    step k (the barrier keeps expecting its bytes), so that every waiter of that
+                                    stage runs into the wait limit, the kernel returns early without its final
+                                    stores and raises the device error word; nothing faults or traps */
 MEGA_API int mega_set_option(int key, int value);
+/*
+ * Test aid: name of the kernel family of this process's most recent launch ("tsn_ema_mma tile=7 pipe=1",
+ * "stream_cl", "rowres", ... or "other").  The string is static; do not free it.
+ */
+MEGA_API const char* mega_debug_last_kernel(void);
 /*
  * Debug aid (synchronises the device): reads the device-side error word that a kernel raises
  * when one of its bounded waits gives up; `reset` != 0 clears it.  host_value is a HOST pointer.
@@ -212,12 +222,15 @@ MEGA_API int mega_sqn_ema_fwd(const void* x, void* y, int dtype, int B, int D, i
  * Single-token decode step of the fused pair, all running state updated IN PLACE:
  * count (B) int64, mean/var (B,D) fp32 (pass count = NULL to skip the TimestepNorm),
  * h (B,D,N) fp32 pole states (16-byte aligned when N is a multiple of 4).  x, y, xn_out (B,D)
- * contiguous activations; xn_out may be NULL.  Queues two launches (elements, then counts).
+ * contiguous activations; xn_out may be NULL.  count_next: NULL or == count: the counts are
+ * bumped in place, by a second launch after the element kernel (every CTA reads them); a
+ * DISTINCT array (B): it receives count + 1 from the element kernel itself and count is left as it
+ * was - one launch per step; the caller alternates two arrays.
  * Replaces: the L == 1 case of TimestepNorm.forward + BaseMovingLayer.forward with an
  * incremental state (norm_layer/timestep_norm.py:100-139, base_moving_average.py:144-160).
  */
 MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D,
-                               int64_t* count, float* mean, float* var,
+                               int64_t* count, int64_t* count_next, float* mean, float* var,
                                const float* gamma, const float* beta, double eps,
                                const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
                                float* h, unsigned flags, mega_stream_t stream);
@@ -375,13 +388,14 @@ MEGA_API int mega_tsn_cema_fwd(const void* x, void* y, void* xn_out, int dtype, 
  * mega_tsn_cema_step: single-token decode step of TimestepNorm -> MultiHeadComplexEMA, all running
  * state updated IN PLACE like mega_tsn_ema_step: count (B) int64, mean/var (B,D) fp32, h (B,D,N,2)
  * fp32 complex pole states (16-byte aligned).  N must be 2, 4, 8, 16 or 32 (MEGA_ERR_UNSUPPORTED
- * otherwise: run the two operators in turn).  Queues two launches (elements, then counts).
+ * otherwise: run the two operators in turn).  count_next as in mega_tsn_ema_step (a distinct array:
+ * one launch; NULL or == count: two launches).
  * Replaces: the L == 1 case of TimestepNorm.forward + BaseMovingLayer.forward with an incremental
  * state and the complex layer (norm_layer/timestep_norm.py:100-139, base_moving_average.py:144-160,
  * complex_exponential_moving_average.py:79-109).
  */
 MEGA_API int mega_tsn_cema_step(const void* x, void* y, void* xn_out, int dtype, int B, int D, int64_t* count,
-                       float* mean, float* var, const float* gamma, const float* beta, double eps,
+                       int64_t* count_next, float* mean, float* var, const float* gamma, const float* beta, double eps,
                        const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
                        float* h, unsigned flags, mega_stream_t stream);
 

@@ -91,6 +91,89 @@ def build_cuda(reference_root=DEFAULT_REFERENCE, verbose=False):
     return cuda_so_path()
 
 
+# The Mega block itself (the caller of this library's modules) as the reference wrote it: Python files
+# staged, unmodified, under oracle/_ref/py (git-ignored, travels to the GPU box like the .so files) so
+# that a GPU test can run the reference's own MovingAverageGatedAttention with this package's classes
+# swapped in for its EMA / norm / attention imports.
+BLOCK_FILES = (
+    "incremental_decoding_utils.py",
+    "modules/moving_average_gated_attention.py",
+    "modules/fairseq_dropout.py",
+    "modules/relative_positional_bias.py",
+    "modules/normalized_feedforward_network.py",
+    "modules/norm_layer/layer_norm.py",
+)
+
+
+def py_dir():
+    return os.path.join(OUT_DIR, "py")
+
+
+def stage_block_sources(reference_root=DEFAULT_REFERENCE):
+    """Copy the reference's block-level Python files (BLOCK_FILES) to oracle/_ref/py/fairseq/...;
+    returns that directory.  Nothing is edited."""
+    import shutil
+    for rel in BLOCK_FILES:
+        src = os.path.join(reference_root, "fairseq", rel)
+        if not os.path.exists(src):
+            raise FileNotFoundError(src)
+        dst = os.path.join(py_dir(), "fairseq", rel)
+        os.makedirs(os.path.dirname(dst), exist_ok=True)
+        shutil.copy2(src, dst)
+    return py_dir()
+
+
+def load_reference_block(swap):
+    """Import the staged reference block with ``swap`` (a dict: class name -> class) standing in for
+    the classes it imports from fairseq.modules.{exponential_moving_average, complex_exponential_moving_average,
+    norm_layer.timestep_norm, norm_layer.sequence_norm, efficient_attention, attention_softmax}.
+    Returns the module ``fairseq.modules.moving_average_gated_attention`` (None when nothing is
+    staged).  The placeholder ``fairseq`` packages it installs in sys.modules are private to the
+    test process."""
+    import types
+
+    import torch
+    import torch.nn.functional as F
+    root = os.path.join(py_dir(), "fairseq")
+    if not os.path.exists(os.path.join(root, "modules", "moving_average_gated_attention.py")):
+        return None
+
+    def pkg(name, path=None):
+        m = types.ModuleType(name)
+        m.__path__ = [path] if path else []
+        sys.modules[name] = m
+        return m
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, rel))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[name] = m
+        spec.loader.exec_module(m)
+        return m
+
+    fs = pkg("fairseq", root)
+    utils = pkg("fairseq.utils")   # the one helper the softmax branch of the block calls (fairseq/utils.py)
+    utils.softmax = lambda x, dim, onnx_trace=False: F.softmax(x.float(), dim=dim, dtype=torch.float32)
+    fs.utils = utils
+    pkg("fairseq.modules", os.path.join(root, "modules"))
+    pkg("fairseq.modules.norm_layer", os.path.join(root, "modules", "norm_layer"))
+    load("fairseq.incremental_decoding_utils", "incremental_decoding_utils.py")
+    load("fairseq.modules.fairseq_dropout", "modules/fairseq_dropout.py")
+    load("fairseq.modules.relative_positional_bias", "modules/relative_positional_bias.py")
+    load("fairseq.modules.norm_layer.layer_norm", "modules/norm_layer/layer_norm.py")
+    for mod, names in (("fairseq.modules.exponential_moving_average", ("MultiHeadEMA",)),
+                       ("fairseq.modules.complex_exponential_moving_average", ("MultiHeadComplexEMA",)),
+                       ("fairseq.modules.norm_layer.timestep_norm", ("TimestepNorm",)),
+                       ("fairseq.modules.norm_layer.sequence_norm", ("SequenceNorm",)),
+                       ("fairseq.modules.efficient_attention", ("EfficientAttention",)),
+                       ("fairseq.modules.attention_softmax", ("AttentionSoftmax",))):
+        m = pkg(mod)
+        for n in names:
+            setattr(m, n, swap[n])
+    load("fairseq.modules.normalized_feedforward_network", "modules/normalized_feedforward_network.py")
+    return load("fairseq.modules.moving_average_gated_attention", "modules/moving_average_gated_attention.py")
+
+
 def load_ref_cuda():
     """Import the prebuilt CUDA build of the reference extension; None when it was never built."""
     p = cuda_so_path()
@@ -129,5 +212,6 @@ if __name__ == "__main__":
     ap.add_argument("--cuda", action="store_true", help="also build the reference's CUDA operators (minutes)")
     a = ap.parse_args()
     print(build(a.reference, a.verbose))
+    print(stage_block_sources(a.reference))
     if a.cuda:
         print(build_cuda(a.reference, a.verbose))

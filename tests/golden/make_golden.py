@@ -452,8 +452,90 @@ def truncated_backward_fixtures():
             dgamma=m.gamma.grad, domega=m.omega.grad)
 
 
+def block_fixtures():
+    """The reference's own MovingAverageGatedAttention (the Mega block that calls the EMA layer, the
+    norm and the attention softmax), built from the reference's unmodified Python on top of its own
+    modules and CPU operators: input, state dict and output in fp32.  The GPU test rebuilds the same
+    block class on top of this package's modules from the same state dict.
+
+    Configuration: moving_layer='cema' (the reference's real-valued MultiHeadEMA does not run in the
+    snapshot), moving_act='silu', grouped TimestepNorm (the per-feature form cannot be constructed
+    through the block, whose TimestepNorm call leaves prior_count at 0), rotary positions, chunked
+    causal softmax attention with the causal mask passed as attn_mask, as the decoder layer does."""
+    ops, cema, tsn, sqn = import_reference()
+    import types
+    import torch.nn.functional as F
+    fs = os.path.join(REF, "fairseq")
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(fs, rel))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[name] = m
+        spec.loader.exec_module(m)
+        return m
+
+    utils = types.ModuleType("fairseq.utils")
+    utils.softmax = lambda x, dim, onnx_trace=False: F.softmax(x.float(), dim=dim, dtype=torch.float32)
+    sys.modules["fairseq.utils"] = utils
+    sys.modules["fairseq"].utils = utils
+    load("fairseq.modules.fairseq_dropout", "modules/fairseq_dropout.py")
+    load("fairseq.modules.relative_positional_bias", "modules/relative_positional_bias.py")
+    load("fairseq.modules.norm_layer.layer_norm", "modules/norm_layer/layer_norm.py")
+    load("fairseq.modules.exponential_moving_average", "modules/exponential_moving_average.py")
+    load("fairseq.modules.efficient_attention", "modules/efficient_attention.py")
+    load("fairseq.modules.attention_softmax", "modules/attention_softmax.py")
+    mag = load("fairseq.modules.moving_average_gated_attention", "modules/moving_average_gated_attention.py")
+    nffn = load("fairseq.modules.normalized_feedforward_network", "modules/normalized_feedforward_network.py")
+
+    dim, zdim, hdim, ndim, chunk, groups = 64, 16, 128, 16, 32, 8
+    for name, bsz, length, padded in (("mega_block_causal", 2, 96, False), ("mega_block_causal_padded", 3, 64, True)):
+        torch.manual_seed(20 + length)
+        gen = torch.Generator().manual_seed(77 + length)
+        blk = mag.MovingAverageGatedAttention(dim, zdim, hdim, ndim, chunk_size=chunk, moving_layer='cema',
+                                              moving_act='silu', norm_num_groups=groups, rel_pos_bias='rotary',
+                                              efficient_attn=False).eval()
+        with torch.no_grad():   # leave the all-zero initialisations so that every parameter matters
+            blk.norm.weight.normal_(0, 0.1, generator=gen)
+            blk.norm.bias.normal_(0, 0.1, generator=gen)
+            blk.gamma.normal_(0, 0.2, generator=gen)
+            blk.beta.normal_(0, 0.2, generator=gen)
+            blk.v_proj.bias.normal_(0, 0.1, generator=gen)
+            blk.mx_proj.bias.normal_(0, 0.1, generator=gen)
+            blk.mx_proj.weight.mul_(8.0)
+            blk.v_proj.weight.mul_(8.0)
+            blk.h_proj.weight.mul_(8.0)
+        x = torch.randn(bsz, length, dim, generator=gen)
+        mask = right_pad_mask(gen, bsz, length, 0.4) if padded else None
+        causal = torch.tril(torch.ones(chunk, chunk))
+        attn_mask = torch.zeros(chunk, chunk).masked_fill(causal == 0, float("-inf"))
+        with torch.no_grad():
+            y, _ = blk(x, padding_mask=mask, attn_mask=attn_mask)
+        arrs = {"x": x, "y": y, "mask": mask if mask is not None else torch.zeros(0),
+                "dims": torch.tensor([dim, zdim, hdim, ndim, chunk, groups])}
+        for k, v in blk.state_dict().items():
+            arrs["sd." + k] = v
+        npz(name, **arrs)
+    # the normalised feed-forward network that follows the block in a Mega layer (layer norm, SiLU MLP)
+    torch.manual_seed(5)
+    gen = torch.Generator().manual_seed(5)
+    ff = nffn.NormalizedFeedForwardNetwork(dim, 96, norm_type='layernorm').eval()
+    with torch.no_grad():
+        for prm in ff.parameters():
+            if prm.dim() == 1:
+                prm.normal_(0, 0.1, generator=gen)
+    x = torch.randn(2, 40, dim, generator=gen)
+    with torch.no_grad():
+        y = ff(x)
+    arrs = {"x": x, "y": y}
+    for k, v in ff.state_dict().items():
+        arrs["sd." + k] = v
+    npz("mega_nffn", **arrs)
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which in ("all", "block"):
+        block_fixtures()
     if which in ("all", "backward_truncated"):
         truncated_backward_fixtures()
     if which in ("all", "cema_backward"):
