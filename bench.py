@@ -355,6 +355,7 @@ def run_ours(args, B, L, D, dtype_name):
     barrier()
     t1 = time.time()
     launches = M.launch_count() - l0
+    kernel_name = _lib.last_kernel()
     clocks = sampler.stop(t0, t1) if sampler else None
     total_ms = evs[0].elapsed_time(evs[-1])
     per_step = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
@@ -447,21 +448,24 @@ def run_ours(args, B, L, D, dtype_name):
         _lib.set_option(1, 0)
     ref = yv.float()
     rel = float((y[:1, :vl].float() - ref).norm() / ref.norm())
-    e2e_same = True
+    e2e_rel = 0.0   # (a slice may run a different tile form than the whole batch: compared within the tolerance)
     if whole_host_batch:
-        e2e_same = bool(torch.equal(hy_all[:min(sl, Bl)].to(dev), y[:min(sl, Bl)]))
-    chk = torch.tensor([rel, 1.0 if e2e_same else 0.0], device=dev, dtype=torch.float64)
+        n = min(sl, Bl)
+        ys = y[:n].float()
+        e2e_rel = float((hy_all[:n].to(dev).float() - ys).norm() / ys.norm())
+        del ys
+    chk = torch.tensor([rel, e2e_rel], device=dev, dtype=torch.float64)
     outs = [chk]
     if world > 1:
         outs = [torch.empty_like(chk) for _ in range(world)]
         dist.all_gather(outs, chk)
     verify = {"max_rel_l2_vs_simt_kernel": max(float(o[0]) for o in outs), "tolerance": 1e-2,
-              "e2e_host_output_equals_device_output": all(float(o[1]) == 1.0 for o in outs)}
-    verify["ok"] = verify["max_rel_l2_vs_simt_kernel"] < 1e-2 and verify["e2e_host_output_equals_device_output"]
+              "max_rel_l2_e2e_host_output_vs_device_output": max(float(o[1]) for o in outs)}
+    verify["ok"] = (verify["max_rel_l2_vs_simt_kernel"] < 1e-2
+                    and verify["max_rel_l2_e2e_host_output_vs_device_output"] < 1e-2)
     del hx_all, hy_all, hxs, hys, dx, dy
 
     aux = None
-    kernel_name = _lib.last_kernel()
     if rank == 0 and world == 1 and not args.no_aux:
         del x, y
         torch.cuda.empty_cache()

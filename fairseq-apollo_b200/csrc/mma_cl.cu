@@ -55,14 +55,17 @@ constexpr int kStep = 32;  // positions per step (2 chunks of 16)
 // kWp: pipeline depth along the sequence (see the kernel): kWp groups of warps work on kWp
 // consecutive steps of the same strip at once and hand the running quantities over through
 // per-warp mailboxes in shared memory.
-template <int kCg, bool kXn = false, bool kCplx = false, int kWs = 1, int kWp = 1>
+// kSm: (kWp == 1) the running quantities of a warp live in its shared-memory mailbox between steps
+// instead of in registers (56 registers of a thread that only hold state).
+template <int kCg, bool kXn = false, bool kCplx = false, int kWs = 1, int kWp = 1, bool kSm = false>
 struct Cfg {
+  static constexpr bool kMail = kWp > 1 || kSm;
   static constexpr int kCm = kCplx ? 2 : 1;
   // Ring depth: a tile is fetched kStages - kWp steps before it is used.  Without the pipeline
   // deeper rings were measured and do not pay: a fifth stage leaves the SM too little L1 for the
   // few spilled registers.  With it a tile is small (narrow tiles only) and the ring holds three
   // rounds of the pipeline.
-  static constexpr int kStages = kWp > 1 ? 3 * kWp : (kXn ? 3 : 4);
+  static constexpr int kStages = kWp > 1 ? 3 * kWp : ((kXn || kSm) ? 3 : 4);
   static constexpr int kWarps = kCg * kWs * kWp;
   static constexpr int kE = 8 / kWs;  // channels per warp
   static constexpr int kCh = kCg * 8;                       // channels per CTA
@@ -81,7 +84,7 @@ struct Cfg {
   // 16 bytes of data, and one mbarrier whose phases count the steps that have been posted
   static constexpr int kOffMail = (kOffBar + (2 * kStages + 2) * 8 + 16 + 15) / 16 * 16;
   static constexpr int kMailWarp = 2 * kE * 32 * 16;
-  static constexpr int kOffFlag = kOffMail + (kWp > 1 ? kWarps * kMailWarp : 0);
+  static constexpr int kOffFlag = kOffMail + (kMail ? kWarps * kMailWarp : 0);
   static constexpr int kFlagWarp = 2 * kE * 8;  // one mbarrier per kind and channel: "this step's value is posted"
   static constexpr int kSmemBytes = kOffFlag + (kWp > 1 ? kWarps * kFlagWarp : 0) + 1024;  // + alignment slack
   static_assert(kSmemBytes <= 227 * 1024, "tile does not fit the shared memory of an SM");
@@ -268,7 +271,14 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 // of squares are taken about a centre the warp already holds, its own latest mean, and moved to the
 // incoming mean afterwards), the pole states right after the local-state product.  The warps of
 // consecutive steps thus run a few hundred cycles apart instead of a whole step.
-template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false, int kWp = 1>
+// kMask: a padding mask (B, L) is honoured as TimestepNorm defines it: a padded position does not
+// advance the statistics and its normalised value is 0 (so it feeds 0 to the EMA, whose state just
+// decays across it); positions past the end of a ragged last step count as padded.  Per step a warp
+// turns the mask bytes of its 8 sequences x 32 positions into 0/1 flags, takes their prefix counts
+// with the same triangular MMA as the sums (the divisor of the running mean at each position), and
+// multiplies the inputs of the sums and the normalised values by the flags.
+template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false, int kWp = 1,
+          bool kMask = false, bool kSm = false>
 __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
@@ -276,7 +286,11 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   static_assert(kEma || (kNorm && !kXn && !kSilu), "without the EMA the kernel is the plain normalisation");
   static_assert(!kCplx || kEma, "complex poles need the EMA");
   static_assert(kWp == 1 || (!kXn && !kCplx && kEma), "the pipelined form covers the real EMA without the second output");
-  using C = Cfg<kCg, kXn, kCplx, kWs, kWp>;
+  static_assert(!kMask || (kNorm && kWp == 1 && !kCplx), "masks: with the normalisation, real poles, not pipelined");
+  static_assert(!kSm || (kWp == 1 && !kXn && !kCplx && kEma && !kMask), "state in shared memory: the plain real form");
+  using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
+  constexpr bool kMail = C::kMail;   // running quantities travel through / live in the mailboxes
+  constexpr bool kLate = kWp > 1;    // ... and arrive from another warp, after this warp's own sums
   constexpr int kCh = C::kCh;
   constexpr int kCm = C::kCm;
   constexpr int kThreads = kCg * kWs * kWp * 32;
@@ -312,7 +326,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   // mailboxes: this warp writes its own, and reads that of the same strip's warp one group before
   const uint32_t mail_out = sm_s + C::kOffMail + (uint32_t)(tid >> 5) * C::kMailWarp + lane * 16;
   const uint32_t flag_out = sm_s + C::kOffFlag + (uint32_t)(tid >> 5) * C::kFlagWarp;
-  const int wprev = ((wp + kWp - 1) % kWp) * kGroup + wig;
+  const int wprev = kSm ? (tid >> 5) : ((wp + kWp - 1) % kWp) * kGroup + wig;
   const uint32_t mail_in = sm_s + C::kOffMail + (uint32_t)wprev * C::kMailWarp + lane * 16;
   const uint32_t flag_in = sm_s + C::kOffFlag + (uint32_t)wprev * C::kFlagWarp;
   const int g = lane >> 2, q = lane & 3;
@@ -494,12 +508,12 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     constexpr int e = decltype(e_c)::value;
     const int d = d0 + cbase + e;
     const bool ok = seq_ok && d < a.D;
-    if constexpr (kWp > 1) {
+    if constexpr (kMail) {
       mu_run[e] = (kNorm && ok) ? a.prev_mean[(size_t)bseq * a.D + d] : 0.f;
       // The warps of the last group put the call's initial statistics and pole states into their
       // mailboxes, where step 0 (first group) looks for what "step -1" left (it does not wait: the
       // barrier before the loop orders these writes).
-      if (wp == kWp - 1) {
+      if (kSm || wp == kWp - 1) {
         float c0 = 0.f, vv = 0.f;
         if (kNorm && ok) {
           c0 = (float)a.prev_count[bseq];
@@ -542,6 +556,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     }
   });
   if (kNorm && seq_ok) nbase = (float)a.prev_count[bseq] + 1.f;
+  // kMask: running count of unmasked positions (exact in fp32: L < 2^24) and the mask row of this
+  // thread's sequence; the flags of a step are fetched one step ahead
+  float n_run = nbase - 1.f, nvalid = 0.f;
+  const unsigned char* mrow = (kMask && seq_ok) ? a.mask + (size_t)bseq * L : nullptr;
   const float ut0 = (2 * q <= g) ? 1.f : 0.f, ut1 = (2 * q + 1 <= g) ? 1.f : 0.f;
   const float eps = a.eps;
   // position offsets of the 8 vectors this thread touches: j = 0..3 chunk 0, j = 4..7 chunk 1.
@@ -573,6 +591,20 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
 
   __syncthreads();  // matrices visible
 
+  // bit j: position toff[j] of step `step` is a valid (unmasked, in-range) position of this sequence
+  auto mask_bits = [&](int step) -> uint32_t {
+    uint32_t bits = 0;
+    if (kMask && mrow != nullptr && step < nsteps) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = step * kStep + toff[j];
+        const unsigned char m = t < L ? __ldg(mrow + t) : (unsigned char)1;
+        bits |= (m == 0 ? 1u : 0u) << j;
+      }
+    }
+    return bits;
+  };
+  uint32_t mk_next = mask_bits(wp);
   bool live = true;  // false once a bounded wait of this thread gave up
   for (int i = wp; i < nsteps; i += kWp) {
     const int s = i % kStages;
@@ -584,7 +616,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     const bool ok = mbar_wait_lim(&full[s], ph, abort_s, wait_limit);
     // kWp > 1, first step of this warp (other than step 0): it has no mean of its own yet, so it
     // waits for the incoming statistics before it centres its sums (`early`)
-    const bool early = kWp > 1 && i < kWp;
+    const bool early = kSm || (kWp > 1 && i < kWp);
     // phase of the hand-off barriers that the warp of step i - 1 completes with that step
     const uint32_t hand_par = kWp > 1 ? (uint32_t)((((i > 0 ? i - 1 : 0) / kWp)) & 1) : 0u;
     const uint32_t st0 = stage_s + tb0, st1 = stage_s + tb1;
@@ -602,8 +634,39 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     });
     float invn[8];
     float inv_end = 0.f, n_end = 1.f, n_in = 0.f;
-    const bool tail = (i + 1) * kStep > L;
-    if (kNorm) {
+    const bool tail = !kMask && (i + 1) * kStep > L;
+    uint32_t vm[kMask ? 8 : 1];   // all ones / zero per position: valid flag as an AND mask
+    f32x2 vf2[kMask ? 4 : 1];     // the same as 1.0 / 0.0, position pairs
+    bool step_has_valid = true;
+    if constexpr (kMask) {
+      const uint32_t cur = mk_next;
+      mk_next = mask_bits(i + kWp);
+      float vf[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        vm[j] = 0u - ((cur >> j) & 1u);
+        vf[j] = __uint_as_float(vm[j] & 0x3f800000u);
+      }
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) vf2[jp] = pack2(vf[2 * jp], vf[2 * jp + 1]);
+      // prefix counts of the valid flags inside the halves, totals from the lane with q = 3
+      float D0[4], D1[4];
+      mma_tf32(D0, vf[0], vf[4], vf[1], vf[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
+      mma_tf32(D1, vf[2], vf[6], vf[3], vf[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
+      const int src3 = lane | 3;
+      const float t0 = __shfl_sync(0xffffffffu, D0[1], src3), t1 = __shfl_sync(0xffffffffu, D1[1], src3);
+      const float t2 = __shfl_sync(0xffffffffu, D0[3], src3), t3 = __shfl_sync(0xffffffffu, D1[3], src3);
+      const float c0 = n_run, c1 = c0 + t0, c2 = c1 + t1, c3 = c2 + t2;
+      n_in = n_run;
+      n_end = c3 + t3;
+      const float cnt[8] = {c0 + D0[0], c0 + D0[1], c1 + D1[0], c1 + D1[1], c2 + D0[2], c2 + D0[3], c3 + D1[2], c3 + D1[3]};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(fmaxf(cnt[j], 1.f));
+      step_has_valid = n_end > n_in;
+      inv_end = rcp_fast(fmaxf(n_end, 1.f));
+      nvalid += n_end - n_in;
+      n_run = n_end;
+    } else if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
 #pragma unroll
       for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(nb_f + (float)toff[j]);
@@ -623,7 +686,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         float xf[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t w32 = odd ? v[j ^ 1][pp] : v[j][pp];
+          uint32_t w32 = odd ? v[j ^ 1][pp] : v[j][pp];
+          if constexpr (kMask) w32 &= vm[j];   // a padded position enters every sum as 0
           xf[j] = __uint_as_float(h2 == 0 ? (w32 << 16) : (w32 & 0xffff0000u));
         }
         float xn[8];
@@ -633,7 +697,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           // warp one step ahead otherwise
           float s1_in = 0.f, m2_in = 0.f, mean_in = 0.f;
           auto fetch_stats = [&]() {  // (step 0 finds the call's initial statistics in the mailbox)
-            if (i != 0 && !mbar_try_s<e * 8>(flag_in, hand_par)) {
+            if (kLate && i != 0 && !mbar_try_s<e * 8>(flag_in, hand_par)) {
               if (!mbar_wait_slow(flag_in + e * 8, hand_par, abort_s, wait_limit)) live = false;
             }
             const uint4 m = lds128<e * 512>(mail_in);
@@ -642,7 +706,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
             mean_in = __uint_as_float(m.z);
           };
           float cm = mu_run[e];
-          if constexpr (kWp > 1) {
+          if constexpr (kMail) {
             if (early) {
               fetch_stats();
               cm = mean_in;
@@ -671,7 +735,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
             // kWp > 1: offsets of the halves only; the running total is added once it has arrived
-            k1[0] = kWp > 1 ? 0.f : s1_run[e];
+            k1[0] = kLate ? 0.f : (kSm ? s1_in : s1_run[e]);
             k1[1] = k1[0] + E0[0];
             k1[2] = k1[1] + E1[0];
             k1[3] = k1[2] + E0[2];
@@ -684,7 +748,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           {
             const f32x2 ncm2 = pack2(-cm, -cm);
 #pragma unroll
-            for (int jp = 0; jp < 4; ++jp) dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
+            for (int jp = 0; jp < 4; ++jp) {
+              dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
+              if constexpr (kMask) dv2[jp] = mul2(dv2[jp], vf2[jp]);   // no deviation at a padded position
+            }
           }
           float k2[4];  // the same carries for the sum of squared deviations
           {  // sum of (x - c)^2
@@ -708,7 +775,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
             const float ea = E0[0], fa = E1[0], eb = E0[2], fb = E1[2];
-            k2[0] = kWp > 1 ? 0.f : m2_run[e];
+            k2[0] = kLate ? 0.f : (kSm ? m2_in : m2_run[e]);
             k2[1] = k2[0] + ea;
             k2[2] = k2[1] + fa;
             k2[3] = k2[2] + eb;
@@ -725,7 +792,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           // running totals entering the step; the incoming squared deviations are about the
           // incoming mean and move to this step's centre (sum (x-c)^2 = sum (x-m)^2 + n (m-c)^2)
           float m2_base;
-          if constexpr (kWp > 1) {
+          if constexpr (kSm) {
+            m2_base = m2_in;   // (fetched before the sums; the centre is the incoming mean itself)
+          } else if constexpr (kLate) {
             if (!early) fetch_stats();
             const float dm = mean_in - cm;
             m2_base = fmaf(n_in * dm, dm, m2_in);
@@ -740,13 +809,17 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           }
           // running statistics after this step: the new mean, and the squared deviations moved
           // from the centre c to it
-          const float mnew = tot1 * inv_end;
+          float mnew = tot1 * inv_end;
           const float shift = mnew - cm;
-          const float m2new = fmaf(-shift * shift, n_end, m2_base + tot2);
+          float m2new = fmaf(-shift * shift, n_end, m2_base + tot2);
+          if constexpr (kMask) {  // a step without a valid position leaves the statistics as they were
+            mnew = step_has_valid ? mnew : cm;
+            m2new = step_has_valid ? m2new : m2_base;
+          }
           mu_run[e] = mnew;
-          if constexpr (kWp > 1) {
+          if constexpr (kMail) {
             sts128<e * 512>(mail_out, make_uint4(__float_as_uint(tot1), __float_as_uint(m2new), __float_as_uint(mnew), 0u));
-            mbar_arrive_s<e * 8>(flag_out);
+            if constexpr (kLate) mbar_arrive_s<e * 8>(flag_out);
           } else {
             s1_run[e] = tot1;
             m2_run[e] = m2new;
@@ -764,7 +837,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
               float va, vb;
               unpack2(sub2(e2, mul2(u2, u2)), va, vb);
               const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(va, eps)), rsqrt_fast(fmaxf(vb, eps))), w2);
-              unpack2(fma2(sub2(dv2[jp], u2), sc2, b2), xn[2 * jp], xn[2 * jp + 1]);
+              f32x2 xn2 = fma2(sub2(dv2[jp], u2), sc2, b2);
+              if constexpr (kMask) xn2 = mul2(xn2, vf2[jp]);   // TimestepNorm writes 0 at a padded position
+              unpack2(xn2, xn[2 * jp], xn[2 * jp + 1]);
             }
           }
         } else {
@@ -838,10 +913,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           mma_bf16(H1, xa0, xa1, xa2, xa3, pr.z, pr.w, 0.f, 0.f, 0.f, 0.f);  // poles 8+2q, 9+2q
           // states entering chunk 0 (= carried) and chunk 1, and the new carry
           float hs0[4];
-          if constexpr (kWp > 1) {
+          if constexpr (kMail) {
             // pole states entering the step: from the mailbox of the warp one step ahead (step 0
             // finds the call's h_in there)
-            if (i != 0 && !mbar_try_s<(kE + e) * 8>(flag_in, hand_par)) {
+            if (kLate && i != 0 && !mbar_try_s<(kE + e) * 8>(flag_in, hand_par)) {
               if (!mbar_wait_slow(flag_in + (kE + e) * 8, hand_par, abort_s, wait_limit)) live = false;
             }
             const uint4 m = lds128<(kE + e) * 512>(mail_in);
@@ -860,10 +935,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           hn[1] = fmaf(aq0.y, hs1[1], H0[3]);
           hn[2] = fmaf(aq1.x, hs1[2], H1[2]);
           hn[3] = fmaf(aq1.y, hs1[3], H1[3]);
-          if constexpr (kWp > 1) {
+          if constexpr (kMail) {
             sts128<(kE + e) * 512>(mail_out, make_uint4(__float_as_uint(hn[0]), __float_as_uint(hn[1]),
                                                         __float_as_uint(hn[2]), __float_as_uint(hn[3])));
-            mbar_arrive_s<(kE + e) * 8>(flag_out);
+            if constexpr (kLate) mbar_arrive_s<(kE + e) * 8>(flag_out);
           } else {
 #pragma unroll
             for (int k = 0; k < 4; ++k) hc[e][k] = hn[k];
@@ -953,9 +1028,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   if (!live) return;  // the error word is raised; the final statistics and states are not written
 
   // ---- final statistics and states -------------------------------------------------------------
-  if constexpr (kWp > 1) {
+  if constexpr (kMail) {
     // held by the group of the last step, in its own mailbox
-    if (wp != (nsteps - 1) % kWp) return;
+    if (kLate && wp != (nsteps - 1) % kWp) return;
     static_for<kE>([&](auto e_c) {
       constexpr int e = decltype(e_c)::value;
       if (kNorm) {
@@ -973,12 +1048,18 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     for (int e = 0; e < kE; ++e) {
       const int d = d0 + cbase + e;
       if (kNorm && d < a.D) {
-        const float n = (float)a.prev_count[bseq] + (float)L;
-        a.mean_out[(size_t)bseq * a.D + d] = mu_run[e];
-        a.var_out[(size_t)bseq * a.D + d] = fmaxf(m2_run[e] / n, 0.f);
+        const float n = kMask ? n_run : (float)a.prev_count[bseq] + (float)L;
+        float mo = mu_run[e], vo = fmaxf(m2_run[e] / n, 0.f);
+        if (kMask && !(n > 0.f)) {  // nothing counted, before or in this call: the incoming statistics stand
+          mo = a.prev_mean[(size_t)bseq * a.D + d];
+          vo = a.prev_var[(size_t)bseq * a.D + d];
+        }
+        a.mean_out[(size_t)bseq * a.D + d] = mo;
+        a.var_out[(size_t)bseq * a.D + d] = vo;
       }
     }
-    if (kNorm && blockIdx.x == 0 && warp == 0 && hf == 0) a.count_out[bseq] = a.prev_count[bseq] + L;
+    if (kNorm && blockIdx.x == 0 && warp == 0 && hf == 0)
+      a.count_out[bseq] = a.prev_count[bseq] + (kMask ? (long long)nvalid : (long long)L);
   }
   if (kEma && seq_ok && a.h_out) {
 #pragma unroll
@@ -1005,11 +1086,11 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
 
 // xn (with its strides nsb, nsl) is the optional second output; kXn selects the kernel form.
 template <bool kNorm, int kCg, bool kSilu, int kWs = 1, bool kXn = false, bool kEma = true, bool kCplx = false,
-          int kWp = 1>
+          int kWp = 1, bool kMask = false, bool kSm = false>
 static bool launch_variant(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                            long long ysl, const StreamArgs& a, cudaStream_t s, void* xn = nullptr,
                            long long nsb = 0, long long nsl = 0) {
-  using C = Cfg<kCg, kXn, kCplx, kWs, kWp>;
+  using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
   const CUtensorMapSwizzle sw = kCg == 8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE;
   CUtensorMap tx, ty, tn;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, sw)) return false;
@@ -1019,7 +1100,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   } else {
     tn = ty;
   }
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma, kCplx, kWp>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, kWs, kXn, kEma, kCplx, kWp, kMask, kSm>;
   static std::once_flag once;
   static bool attr_ok = true;
   std::call_once(once, [&] {
@@ -1033,7 +1114,7 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
   launch(kern, grid, dim3(kCg * kWs * kWp * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, tn, a);
   static const std::string name = std::string("tsn_ema_mma tile=") + std::to_string(kCg) + " warps_per_column=" +
                                   std::to_string(kWs) + " pipe=" + std::to_string(kWp) + (kNorm ? " norm" : "") +
-                                  (kEma ? " ema" : "") + (kCplx ? " complex" : "") + (kXn ? " xn" : "");
+                                  (kEma ? " ema" : "") + (kCplx ? " complex" : "") + (kXn ? " xn" : "") + (kMask ? " mask" : "") + (kSm ? " smstate" : "");
   g_last_kernel.store(name.c_str(), std::memory_order_relaxed);
   return true;
 }
@@ -1053,7 +1134,11 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     a_in.wait_limit = lim > 0 ? (long long)lim : 4000000000LL;
     a_in.withhold_step = wh > 0 ? wh : -1;
   }
-  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1 || a_in.mask != nullptr) return false;
+  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1) return false;
+  // a padding mask: the fused pair and TimestepNorm alone (the EMA alone adds omega times the
+  // UNMASKED input, which the tile no longer holds where the mask zeroed it), real poles
+  const bool masked = a_in.mask != nullptr;
+  if (masked && (!norm || a_in.cplx)) return false;
   const bool want_xn = xn != nullptr;  // second output: the normalised activations, strided like y
   if (want_xn && (!norm || xn == y || xn == x)) return false;
   const bool ema = a_in.N > 0;  // N = 0: TimestepNorm alone
@@ -1062,7 +1147,7 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   const bool forced_pipe = forced == 222 || forced == 224 || forced == 422 || forced == 124;
   // fewer than 4 sequences leave most rows of the MMAs empty: only the pipelined form, which fills the SMs
   // from the sequence length, is then worth more than the SIMT kernels
-  const bool can_pipe = ema && !want_xn && !a_in.cplx;
+  const bool can_pipe = ema && !want_xn && !a_in.cplx && !(a_in.mask != nullptr);
   if (a_in.N > 16 || a_in.N < 0 || (a_in.B < 4 && !(forced_pipe || (forced == 0 && can_pipe))) ||
       a_in.L >= (1 << 24) || a_in.D < 8)
     return false;
@@ -1084,9 +1169,10 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   };
   int tile = g_options[OPT_MMA_TILE].load();
   // pipelined forms (real EMA, with or without the normalisation, no second output)
-  if ((tile == 222 || tile == 224 || tile == 422 || tile == 124) && (a_in.cplx || !ema || want_xn)) tile = 0;
+  if ((tile == 222 || tile == 224 || tile == 422 || tile == 124) && (a_in.cplx || !ema || want_xn || masked)) tile = 0;
+  if (tile == 71 && (a_in.cplx || !ema || want_xn || masked)) tile = 0;
   if (tile != 2 && tile != 4 && tile != 7 && tile != 8 && tile != 22 && tile != 222 && tile != 224 && tile != 422 &&
-      tile != 124) {
+      tile != 124 && tile != 71) {
     // (the EMA alone is closer to the memory bound and prefers the 128-byte rows of the 64-channel
     // tile: 1.71 against 2.02 ms at B = 64, L = 16384, D = 2048, unless 56 channels save a wave)
     if (ctas(64) >= 148 || ctas(56) >= 148)
@@ -1112,6 +1198,19 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     return a_in.silu ? launch_variant<true, 2, true, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
                      : launch_variant<true, 2, false, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
   }
+  if (masked) {
+    // masked forms: 56-channel tile for large problems, the 16-channel two-warp tile otherwise
+    tile = (tile == 7 || tile == 8) ? 7 : 22;
+#define MEGA_MASKED(SILU, XN, EMA)                                                                                  \
+  (tile == 7 ? launch_variant<true, 7, SILU, 1, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, \
+                                                                         ysb, ysl)                                   \
+             : launch_variant<true, 2, SILU, 2, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, \
+                                                                         ysb, ysl))
+    if (!ema) return MEGA_MASKED(false, false, false);
+    if (want_xn) return a_in.silu ? MEGA_MASKED(true, true, true) : MEGA_MASKED(false, true, true);
+    return a_in.silu ? MEGA_MASKED(true, false, true) : MEGA_MASKED(false, false, true);
+#undef MEGA_MASKED
+  }
   if (!ema) {
     if (tile == 2 || tile == 4) tile = 22;
     return tile == 22  ? launch_variant<true, 2, false, 2, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
@@ -1129,7 +1228,8 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
                      : launch_variant<true, 2, false, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
   }
 #define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
-  (tile == 222 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+  (tile == 71 ? launch_variant<NORM, 7, SILU, 1, false, true, false, 1, false, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+   : tile == 222 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
    : tile == 224 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
    : tile == 422 ? launch_variant<NORM, 4, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
    : tile == 124 ? launch_variant<NORM, 1, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \

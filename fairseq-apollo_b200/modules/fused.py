@@ -26,7 +26,7 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     """
     assert activation in (None, 'silu')
     per_feature = norm.num_groups is None or norm.num_groups == norm.num_features
-    train = needs_grad(x, *norm.parameters(), *move.parameters())
+    train = torch.is_grad_enabled() and needs_grad(x, *norm.parameters(), *move.parameters())
     if train or not per_feature or move.bidirectional:
         # training, grouped statistics or a bidirectional layer: the two modules in turn
         xn = norm(x, padding_mask, incremental_state)
@@ -75,18 +75,29 @@ def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):
     is modified (checked through the tensors' version counters)."""
     third = move.theta if move.complex else move.beta
     tensors = (norm.weight, norm.bias, move.alpha, move.delta, third, move.gamma, move.omega)
-    key = tuple((t.data_ptr(), t._version) for t in tensors)
+    # (in-place updates bump the version counters; a parameter that was replaced has a new identity)
+    key = (norm.weight._version, norm.bias._version, move.alpha._version, move.delta._version, third._version,
+           move.gamma._version, move.omega._version)
     cache = getattr(move, "_decode_cache", None)
-    if cache is None or cache[0] != key:
+    if cache is not None and (cache[0] != key or any(a is not b for a, b in zip(cache[-1], tensors))):
+        cache = None
+    if cache is None:
         if move.complex:   # q, g complex64 (K, N): the kernel reads them as interleaved (re, im) floats
             p, q, g = ops.cema_coeffs(move.alpha, move.delta, move.theta, move.gamma)
             p, q, g = p.reshape(p.shape[0], -1).contiguous(), q.reshape(q.shape[0], -1).contiguous(), g.contiguous()
         else:
             p, q, g = ops.ema_coeffs(move.alpha, move.delta, move.beta, move.gamma)
         cache = (key, (norm.weight.detach().float() + 1.0).contiguous(), norm.bias.detach().float().contiguous(),
-                 p, q, g, move.omega.detach().float().reshape(-1).contiguous())
+                 p, q, g, move.omega.detach().float().reshape(-1).contiguous(), tensors)
         move._decode_cache = cache
-    return cache[1:]
+    return cache[1:7]
+
+
+try:   # the raw handle of the current stream without building a torch.cuda.Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:   # pragma: no cover - older / newer torch
+    def _raw_stream(index):
+        return torch.cuda.current_stream(index).cuda_stream
 
 
 class _StepPlan:
@@ -152,7 +163,7 @@ def _decode_step(norm, move, x, incremental_state, activation, return_normed):
     alt = plan.count_alt
     args[6].value = count.data_ptr()
     args[7].value = alt.data_ptr()
-    args[20].value = torch.cuda.current_stream(x.device).cuda_stream
+    args[20].value = _raw_stream(x.device.index)
     if torch.cuda.current_device() == x.device.index:
         rc = plan.fn(*args)
     else:

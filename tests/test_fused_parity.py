@@ -390,3 +390,71 @@ def test_bounded_wait_runs_out(tile):
     yref = O.ema_forward_recurrence(xn.transpose(1, 2), *prm).transpose(1, 2)
     assert rel_l2(res["y"].float(), yref) < 1e-2
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("tile", [7, 22])
+@pytest.mark.parametrize("bsz,length,dim", [(8, 1024, 128), (9, 300, 72), (16, 4096, 64), (5, 96, 200)])
+@pytest.mark.parametrize("interior", [False, True])
+def test_tensor_core_path_with_padding_mask(tile, bsz, length, dim, interior):
+    """bf16 with a padding mask on the tensor-core kernel (fused pair, with and without the
+    normalised activations as a second output, and TimestepNorm alone): right padding of up to 40 %,
+    one fully padded sequence, optionally pads in the interior, a length that is not a multiple of
+    the step; against the oracle and the streamed SIMT kernel.  Padded positions of the normalised
+    output are exactly zero, counts are exact, and the launch is checked to be the masked form."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(bsz * 7 + length + dim + tile)
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.2 + 0.3).to(torch.bfloat16)
+    mask = right_pad_mask(gen, bsz, length, 0.4)
+    mask[bsz - 1] = True
+    if interior:
+        mask[0, 3] = True
+        mask[1, 40:75] = True
+        mask[2, 0] = True
+    pc = torch.full((bsz,), 2, dtype=torch.int64)
+    pc[1] = 1
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1 + 0.3
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    h0 = torch.randn(bsz, dim, 16, generator=gen) * 0.3
+    want_state = length % 32 == 0
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, mask, acc_dtype=torch.float64)[:4]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, mask, h=h0, return_state=True, silu=True)
+    outs = []
+    for disable in (0, 1):
+        _lib.set_option(1, disable)
+        _lib.set_option(2, tile)
+        try:
+            both = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                         p, q, g, prm[4].cuda(), mask.cuda(), h_in=h0.cuda(), want_state=want_state,
+                                         want_normed=True, silu=True)
+            name_both = _lib.last_kernel()
+            plain = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                          p, q, g, prm[4].cuda(), mask.cuda(), h_in=h0.cuda(), silu=True)
+            name_plain = _lib.last_kernel()
+            tsn = M.ops.timestep_norm_fwd(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), mask.cuda())
+            name_tsn = _lib.last_kernel()
+        finally:
+            _lib.set_option(1, 0)
+            _lib.set_option(2, 0)
+        if disable == 0:
+            for n in (name_both, name_plain, name_tsn):
+                assert "tsn_ema_mma" in n and "mask" in n, n
+        outs.append((both, plain, tsn))
+        assert rel_l2(both["y"].float(), yref.transpose(1, 2)) < 1e-2, disable
+        assert rel_l2(plain["y"].float(), yref.transpose(1, 2)) < 1e-2, disable
+        assert rel_l2(both["xn"].float(), xn) < 1e-2 and rel_l2(tsn[0].float(), xn) < 1e-2, disable
+        assert (both["xn"].cpu()[mask] == 0).all() and (tsn[0].cpu()[mask] == 0).all()
+        assert torch.equal(both["count"].cpu(), cnt) and torch.equal(tsn[1].cpu(), cnt)
+        assert rel_l2(both["mean"], mean) < 1e-4 and rel_l2(both["var"], var) < 2e-3, disable
+        assert rel_l2(tsn[2], mean) < 1e-4 and rel_l2(tsn[3], var) < 2e-3, disable
+        if want_state:
+            assert rel_l2(both["h"], href) < 1e-2, disable
+    # the fully padded sequence hands its incoming statistics back unchanged
+    assert torch.allclose(outs[0][0]["mean"][bsz - 1].cpu(), pm[bsz - 1], atol=1e-6)
+    assert torch.allclose(outs[0][0]["var"][bsz - 1].cpu(), pv[bsz - 1], rtol=1e-5)
+    assert rel_l2(outs[0][0]["y"].float(), outs[1][0]["y"].float()) < 1e-2
+    assert _lib.device_error() == 0
