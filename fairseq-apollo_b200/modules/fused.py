@@ -26,6 +26,11 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
     """
     assert activation in (None, 'silu')
     per_feature = norm.num_groups is None or norm.num_groups == norm.num_features
+    # the decode fast path first: one token, an incremental state, inference
+    if (incremental_state is not None and x.size(1) == 1 and padding_mask is None and per_feature
+            and not move.bidirectional and not torch.is_grad_enabled() and x.is_contiguous()
+            and (not move.complex or move.ndim in (2, 4, 8, 16, 32))):
+        return _decode_step(norm, move, x, incremental_state, activation, return_normed)
     train = torch.is_grad_enabled() and needs_grad(x, *norm.parameters(), *move.parameters())
     if train or not per_feature or move.bidirectional:
         # training, grouped statistics or a bidirectional layer: the two modules in turn

@@ -102,6 +102,11 @@ BLOCK_FILES = (
     "modules/relative_positional_bias.py",
     "modules/normalized_feedforward_network.py",
     "modules/norm_layer/layer_norm.py",
+    # the wrappers that call fairseq.mega2_extension.ops by name (operator-level drop-in test)
+    "modules/norm_layer/timestep_norm.py",
+    "modules/norm_layer/sequence_norm.py",
+    "modules/attention_softmax.py",
+    "modules/efficient_attention.py",
 )
 
 
@@ -172,6 +177,42 @@ def load_reference_block(swap):
             setattr(m, n, swap[n])
     load("fairseq.modules.normalized_feedforward_network", "modules/normalized_feedforward_network.py")
     return load("fairseq.modules.moving_average_gated_attention", "modules/moving_average_gated_attention.py")
+
+
+def load_reference_wrappers(ops_module):
+    """Import the staged reference wrappers (norm_layer/timestep_norm.py, norm_layer/sequence_norm.py,
+    attention_softmax.py, efficient_attention.py) with ``ops_module`` bound as
+    ``fairseq.mega2_extension.ops``, the name they import.  Returns the four modules in that order,
+    or None when nothing is staged."""
+    import types
+    root = os.path.join(py_dir(), "fairseq")
+    if not os.path.exists(os.path.join(root, "modules", "norm_layer", "timestep_norm.py")):
+        return None
+
+    def pkg(name, path=None):
+        m = types.ModuleType(name)
+        m.__path__ = [path] if path else []
+        sys.modules[name] = m
+        return m
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, rel))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[name] = m
+        spec.loader.exec_module(m)
+        return m
+
+    pkg("fairseq", root)
+    ext = pkg("fairseq.mega2_extension")
+    ext.ops = ops_module
+    sys.modules["fairseq.mega2_extension.ops"] = ops_module
+    pkg("fairseq.modules", os.path.join(root, "modules"))
+    pkg("fairseq.modules.norm_layer", os.path.join(root, "modules", "norm_layer"))
+    load("fairseq.incremental_decoding_utils", "incremental_decoding_utils.py")
+    return (load("fairseq.modules.norm_layer.timestep_norm", "modules/norm_layer/timestep_norm.py"),
+            load("fairseq.modules.norm_layer.sequence_norm", "modules/norm_layer/sequence_norm.py"),
+            load("fairseq.modules.attention_softmax", "modules/attention_softmax.py"),
+            load("fairseq.modules.efficient_attention", "modules/efficient_attention.py"))
 
 
 def load_ref_cuda():
