@@ -263,10 +263,11 @@ def job_throughput(tokens_per_rank, world, steps, total_ms):
     return tokens_per_rank * world * steps / (total_ms * 1e-3)
 
 
-# DRAM bytes per token of the tensor-core kernel from its ncu capture (profiles/
-# tsn_ema_mma_kernel__b32_l4096.md: 1036.3 MB for 32 x 4096 tokens of 2048 bf16 channels);
-# it scales with the tokens of a launch.
-NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = 1036.28e6 / (32 * 4096)
+# DRAM bytes per token of the tensor-core kernel (56-channel tile, TimestepNorm -> EMA), from an ncu capture
+# of one launch of the current kernel at B=32, L=4096, D=2048: dram__bytes_read.sum 539.26 MB +
+# dram__bytes_write.sum 490.85 MB for 32 x 4096 tokens (0.96 of the algorithmic 8192 B per token: the tail of
+# the output is still in L2 when the kernel ends).  The traffic grows with the tokens of a launch.
+NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = (539.26e6 + 490.85e6) / (32 * 4096)
 
 
 def workload_name(args, B, L, D, dtype_name):
