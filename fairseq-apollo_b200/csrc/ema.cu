@@ -430,6 +430,25 @@ extern "C" int mega_ema_fwd(const void* x, void* y, int dtype, int B, int D, int
     sa.B = B; sa.L = L; sa.D = D; sa.N = N;
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+    // (a state is exported and L is not a multiple of the tensor-core step of 32: head on the
+    // tensor-core kernel, ragged tail on the streamed kernel, continuing from the head's state in place)
+    const int Lh = L - L % 32;
+    if (h_out && Lh > 0 && Lh < L && !pad_mask) {
+      StreamArgs head = sa;
+      head.L = Lh;
+      if (mma_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, head, (cudaStream_t)stream)) {
+        const size_t es = (size_t)elem_size(dtype);
+        const void* xt = (const char*)x + (size_t)Lh * xsl * es;
+        void* yt = (char*)y + (size_t)Lh * ysl * es;
+        StreamArgs tail = sa;
+        tail.L = L - Lh;
+        tail.h_in = h_out;
+        if (stream_cl_try(dtype, xt, yt, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, true, tail, (cudaStream_t)stream))
+          return check_launch("ema_fwd(mma head + stream tail)");
+        a.x = xt; a.y = yt; a.L = L - Lh; a.h_in = h_out;
+        return ema_fwd_simt(a, flags, truncation, dtype, (cudaStream_t)stream);
+      }
+    }
     if (mma_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, sa, (cudaStream_t)stream))
       return check_launch("ema_fwd(mma)");
     if (stream_cl_try(dtype, x, y, nullptr, xsb, xsl, xsd, ysb, ysl, ysd, false, true, sa, (cudaStream_t)stream))

@@ -17,6 +17,7 @@ struct FusedArgs {
   int B, L, D, N;
   long long xsb, xsl, xsd, ysb, ysl, ysd;
   const long long* prev_count;
+  long long count_offset;  // added to prev_count (a call that continues another call's positions)
   const float *prev_mean, *prev_var, *gamma, *beta;
   float eps;
   long long* count_out;
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(128) tsn_ema_rows_kernel(FusedArgs a) {
   T* yp = reinterpret_cast<T*>(a.y) + b * a.ysb + d * a.ysd;
   T* np_ = a.xn ? reinterpret_cast<T*>(a.xn) + b * a.ysb + d * a.ysd : nullptr;
   const unsigned char* mp = a.mask ? a.mask + (size_t)b * a.L : nullptr;
-  const long long cnt0 = a.prev_count[b];
+  const long long cnt0 = a.prev_count[b] + a.count_offset;
   const float cnt0f = (float)cnt0;  // 32-bit step counter on top: no 64-bit conversions in the loop
   int seen = 0;
   float mean = a.prev_mean[gid], var = a.prev_var[gid];
@@ -412,6 +413,34 @@ extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype,
     sa.beta = beta; sa.eps = (float)eps; sa.count_out = a.count_out; sa.mean_out = mean_out; sa.var_out = var_out;
     sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out; sa.mask = pad_mask;
     sa.silu = a.silu;
+    // A state is exported and L is not a multiple of the tensor-core kernel's step of 32 positions (it
+    // cannot stop a pole state in mid-step): the head, a multiple of 32, goes to the tensor-core
+    // kernel and the ragged tail of fewer than 32 positions to the streamed (or generic) kernel, which
+    // continues in place from the statistics and states the head has written.
+    const int Lh = L - L % 32;
+    if (h_out && Lh > 0 && Lh < L && !pad_mask && (const void*)count_out != (const void*)prev_count) {
+      StreamArgs head = sa;
+      head.L = Lh;
+      if (mma_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, head, (cudaStream_t)stream)) {
+        const size_t es = (size_t)elem_size(dtype);
+        const void* xt = (const char*)x + (size_t)Lh * xsl * es;
+        void* yt = (char*)y + (size_t)Lh * ysl * es;
+        void* nt = xn_out ? (char*)xn_out + (size_t)Lh * ysl * es : nullptr;
+        StreamArgs tail = sa;
+        tail.L = L - Lh;
+        tail.count_offset = Lh;
+        tail.prev_mean = mean_out; tail.prev_var = var_out; tail.h_in = h_out;
+        if (stream_cl_try(dtype, xt, yt, nt, xsb, xsl, xsd, ysb, ysl, ysd, true, true, tail, (cudaStream_t)stream))
+          return check_launch("tsn_ema_fwd(mma head + stream tail)");
+        a.x = xt; a.y = yt; a.xn = nt; a.L = L - Lh; a.count_offset = Lh;
+        a.prev_mean = mean_out; a.prev_var = var_out; a.h_in = h_out;
+        const int npt = next_pow2_ndim(N);
+        const unsigned gridt = (unsigned)(((long long)B * D + 127) / 128);
+        MEGA_DISPATCH_DTYPE(dtype, MEGA_DISPATCH_NP(npt, launch(tsn_ema_rows_kernel<T, NP, true>, gridt, 128, 0,
+                                                                stream, a)));
+        return check_launch("tsn_ema_fwd(mma head + generic tail)");
+      }
+    }
     // (the tensor-core kernel writes the normalised activations too when xn_out is given)
     if (mma_cl_try(dtype, x, y, xn_out, xsb, xsl, xsd, ysb, ysl, ysd, true, sa, (cudaStream_t)stream))
       return check_launch("tsn_ema_fwd(mma)");

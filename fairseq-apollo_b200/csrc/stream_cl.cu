@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kW) stream_cl_kernel(const __grid_constant__ C
 
   // warp 0 keeps the running count and publishes, per timestep of the next tile, the Welford
   // coefficient 1/count (negative = padded step)
-  long long cnt_run = kNorm ? a.prev_count[b] : 0;
+  long long cnt_run = kNorm ? a.prev_count[b] + a.count_offset : 0;
   const unsigned char* mrow = a.mask ? a.mask + (size_t)b * L : nullptr;
   auto publish = [&](int tile, unsigned char mk_byte) {
     // called by warp 0 (kR == 32 lanes); lane r handles timestep tile*kR + r

@@ -22,6 +22,7 @@ struct StreamArgs {
   // set by the tensor-core path itself (callers leave them alone)
   long long wait_limit;  // SM cycles after which a bounded wait gives up
   int withhold_step;     // test aid: step whose tile is never loaded, or -1
+  long long count_offset;  // added to prev_count (a call that continues another call's positions)
 };
 
 // Tries the streamed TMA path for TimestepNorm (norm), causal EMA (ema) or both fused.  Returns

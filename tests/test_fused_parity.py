@@ -458,3 +458,48 @@ def test_tensor_core_path_with_padding_mask(tile, bsz, length, dim, interior):
     assert torch.allclose(outs[0][0]["var"][bsz - 1].cpu(), pv[bsz - 1], rtol=1e-5)
     assert rel_l2(outs[0][0]["y"].float(), outs[1][0]["y"].float()) < 1e-2
     assert _lib.device_error() == 0
+
+
+@pytest.mark.parametrize("length", [1000, 33, 4100])
+def test_ragged_length_with_exported_state(length):
+    """A state is exported and the length is not a multiple of the tensor-core kernel's step: the
+    head runs on the tensor-core kernel and the ragged tail on the streamed kernel, continuing in
+    place from the head's statistics and pole states (two launches); outputs, states, statistics and
+    counts against the oracle, for the fused pair and for the EMA alone."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(length)
+    bsz, dim = 8, 128
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.1 + 0.2).to(torch.bfloat16)
+    pc = torch.full((bsz,), 3, dtype=torch.int64)
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1 + 0.2
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    h0 = torch.randn(bsz, dim, 16, generator=gen) * 0.3
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    before = M.launch_count()
+    res = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                p, q, g, prm[4].cuda(), None, h_in=h0.cuda(), want_state=True, want_normed=True)
+    assert M.launch_count() - before == 2 and "stream_cl" in _lib.last_kernel()
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[:4]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, None, h=h0, return_state=True)
+    assert rel_l2(res["y"].float(), yref.transpose(1, 2)) < 1e-2 and rel_l2(res["xn"].float(), xn) < 1e-2
+    assert rel_l2(res["h"], href) < 1e-2
+    assert torch.equal(res["count"].cpu(), cnt)
+    assert rel_l2(res["mean"], mean) < 1e-4 and rel_l2(res["var"], var) < 1e-3
+    before = M.launch_count()
+    y, h = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), None, h0.cuda(), want_state=True)
+    assert M.launch_count() - before == 2
+    eref, ehref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, None, h=h0, return_state=True)
+    assert rel_l2(y.float(), eref) < 1e-2 and rel_l2(h, ehref) < 1e-2
+    # against the whole call on the streamed kernel
+    _lib.set_option(1, 1)
+    try:
+        ref2 = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                     p, q, g, prm[4].cuda(), None, h_in=h0.cuda(), want_state=True)
+    finally:
+        _lib.set_option(1, 0)
+    assert rel_l2(res["y"].float(), ref2["y"].float()) < 1e-2 and rel_l2(res["h"], ref2["h"]) < 1e-2
+    assert _lib.device_error() == 0
