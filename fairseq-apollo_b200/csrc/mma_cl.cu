@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   static_assert(kEma || (kNorm && !kXn && !kSilu), "without the EMA the kernel is the plain normalisation");
   static_assert(!kCplx || kEma, "complex poles need the EMA");
   static_assert(kWp == 1 || (!kXn && !kCplx && kEma), "the pipelined form covers the real EMA without the second output");
-  static_assert(!kMask || (kNorm && kWp == 1 && !kCplx), "masks: with the normalisation, real poles, not pipelined");
+  static_assert(!kMask || (kWp == 1 && !kCplx && !(kXn && !kNorm)), "masks: real poles, not pipelined");
   static_assert(!kSm || (kWp == 1 && !kXn && !kCplx && kEma && !kMask), "state in shared memory: the plain real form");
   using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
   constexpr bool kMail = C::kMail;   // running quantities travel through / live in the mailboxes
@@ -399,6 +399,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     if (l < 2) {
       float v = (l == 0) ? 1.f : 0.f;
       if (kNorm && d < a.D) v = (l == 0) ? __ldg(a.gamma + d) : __ldg(a.beta + d);
+      if (!kNorm && kMask && kEma && l == 0 && d < a.D) v = __ldg(a.omega + d);   // see the masked EMA epilogue
       WB[ch * 2 + l] = v;
     }
   }
@@ -647,6 +648,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         vm[j] = 0u - ((cur >> j) & 1u);
         vf[j] = __uint_as_float(vm[j] & 0x3f800000u);
       }
+      if constexpr (kNorm) {
 #pragma unroll
       for (int jp = 0; jp < 4; ++jp) vf2[jp] = pack2(vf[2 * jp], vf[2 * jp + 1]);
       // prefix counts of the valid flags inside the halves, totals from the lane with q = 3
@@ -666,6 +668,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       inv_end = rcp_fast(fmaxf(n_end, 1.f));
       nvalid += n_end - n_in;
       n_run = n_end;
+      }
     } else if (kNorm) {
       const float nb_f = nbase + (float)(i * kStep);
 #pragma unroll
@@ -684,9 +687,14 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         constexpr int e = 2 * pp + h2;
         const int ch = cbase + e;
         float xf[8];
+        float xpad[(kMask && !kNorm) ? 8 : 1];   // the input at padded positions, 0 elsewhere
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint32_t w32 = odd ? v[j ^ 1][pp] : v[j][pp];
+          if constexpr (kMask && !kNorm) {  // the EMA alone: omega multiplies the UNMASKED input
+            const uint32_t pad = w32 & ~vm[j];
+            xpad[j] = __uint_as_float(h2 == 0 ? (pad << 16) : (pad & 0xffff0000u));
+          }
           if constexpr (kMask) w32 &= vm[j];   // a padded position enters every sum as 0
           xf[j] = __uint_as_float(h2 == 0 ? (w32 << 16) : (w32 & 0xffff0000u));
         }
@@ -952,6 +960,13 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         }
         yv[h2][0] = Y0[0]; yv[h2][1] = Y0[1]; yv[h2][4] = Y0[2]; yv[h2][5] = Y0[3];
         yv[h2][2] = Y1[0]; yv[h2][3] = Y1[1]; yv[h2][6] = Y1[2]; yv[h2][7] = Y1[3];
+        if constexpr (kMask && !kNorm) {
+          // the Toeplitz diagonal carries omega times the masked input: a padded position still gets
+          // omega times its own (unmasked) input, as the reference's residual does
+          const float om = __uint_as_float(lds32<e * 8>(wb_base));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) yv[h2][j] = fmaf(om, xpad[j], yv[h2][j]);
+        }
         if (kSilu) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) yv[h2][j] = silu_tanh(yv[h2][j]);
@@ -1135,10 +1150,9 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     a_in.withhold_step = wh > 0 ? wh : -1;
   }
   if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1) return false;
-  // a padding mask: the fused pair and TimestepNorm alone (the EMA alone adds omega times the
-  // UNMASKED input, which the tile no longer holds where the mask zeroed it), real poles
+  // a padding mask: real poles only
   const bool masked = a_in.mask != nullptr;
-  if (masked && (!norm || a_in.cplx)) return false;
+  if (masked && a_in.cplx) return false;
   const bool want_xn = xn != nullptr;  // second output: the normalised activations, strided like y
   if (want_xn && (!norm || xn == y || xn == x)) return false;
   const bool ema = a_in.N > 0;  // N = 0: TimestepNorm alone
@@ -1206,6 +1220,13 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
                                                                          ysb, ysl)                                   \
              : launch_variant<true, 2, SILU, 2, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, \
                                                                          ysb, ysl))
+    if (!norm) {  // the EMA alone
+#define MEGA_MASKED_EMA(SILU)                                                                                          \
+  (tile == 7 ? launch_variant<false, 7, SILU, 1, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
+             : launch_variant<false, 2, SILU, 2, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
+      return a_in.silu ? MEGA_MASKED_EMA(true) : MEGA_MASKED_EMA(false);
+#undef MEGA_MASKED_EMA
+    }
     if (!ema) return MEGA_MASKED(false, false, false);
     if (want_xn) return a_in.silu ? MEGA_MASKED(true, true, true) : MEGA_MASKED(false, true, true);
     return a_in.silu ? MEGA_MASKED(true, false, true) : MEGA_MASKED(false, false, true);

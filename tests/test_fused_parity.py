@@ -437,12 +437,20 @@ def test_tensor_core_path_with_padding_mask(tile, bsz, length, dim, interior):
             name_plain = _lib.last_kernel()
             tsn = M.ops.timestep_norm_fwd(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), mask.cuda())
             name_tsn = _lib.last_kernel()
+            # the EMA alone: omega times the UNMASKED input stays at padded positions
+            ema = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), mask.cuda(), h0.cuda(),
+                                    want_state=want_state, silu=True)
+            name_ema = _lib.last_kernel()
         finally:
             _lib.set_option(1, 0)
             _lib.set_option(2, 0)
         if disable == 0:
-            for n in (name_both, name_plain, name_tsn):
+            for n in (name_both, name_plain, name_tsn, name_ema):
                 assert "tsn_ema_mma" in n and "mask" in n, n
+        eref, ehref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, mask, h=h0, return_state=True, silu=True)
+        assert rel_l2((ema[0] if want_state else ema).float(), eref) < 1e-2, disable
+        if want_state:
+            assert rel_l2(ema[1], ehref) < 1e-2, disable
         outs.append((both, plain, tsn))
         assert rel_l2(both["y"].float(), yref.transpose(1, 2)) < 1e-2, disable
         assert rel_l2(plain["y"].float(), yref.transpose(1, 2)) < 1e-2, disable
