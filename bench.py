@@ -37,9 +37,9 @@ WORKLOADS = {
     "tiny": (4, 2048, 256, "bf16"),
 }
 # side workloads (BASELINE configs 0, 2 and the decode half of config 4): own JSON line, N=1 only
-AUX_WORKLOADS = ("c0", "c2", "c3", "decode", "cema", "train", "c4n", "c1n")
+AUX_WORKLOADS = ("c0", "c2", "c3", "decode", "cema", "train", "c4n", "c1n", "c4pad")
 # side workloads measured after the headline run and reported under its "aux" key (N = 1 only)
-AUX_IN_HEADLINE = ("c0", "c1", "c2", "c3", "c4n", "cema", "train", "decode")
+AUX_IN_HEADLINE = ("c0", "c1", "c2", "c3", "c4n", "c4pad", "cema", "train", "decode")
 NDIM = 16
 FALLBACK_HBM_GBS = 6650.0
 CPU_DETAIL = {
@@ -602,6 +602,23 @@ def aux_workload(workload, steps, warm):
             # compulsory traffic of the norm -> EMA part only (x in, mx and xn out); the layer as a whole is GEMM-bound
             tokens, bytes_alg, dt = B * L, 3.0 * B * L * D * 2 * (ms / ms_ema), "bf16"
             name = "c3: Mega decoder block + NFFN fwd bf16 L=8192 B=8 D=1024 z=256 h=2048 ffn=2048 chunk=1024"
+        elif args.workload == "c4pad":
+            # config 4's shape with right padding of 0-25 % per sequence (padded batches are the reference's normal case)
+            L, B, D = 32768, 64, 2048
+            x = torch.empty(B, L, D, dtype=torch.bfloat16, device=dev)
+            for b in range(B):
+                x[b] = torch.randn(L, D, device=dev, dtype=torch.bfloat16)
+            mask = torch.zeros(B, L, dtype=torch.bool)
+            for b in range(B):
+                n = int(torch.rand((), generator=gen).item() * 0.25 * L)
+                if n:
+                    mask[b, L - n:] = True
+            mask = mask.to(dev)
+            ema = M.MultiHeadEMA(D, ndim=NDIM).to(dev).eval()
+            norm = M.TimestepNorm(D, prior_count=2).to(dev).eval()
+            ms = timed(lambda: M.timestep_norm_ema(norm, ema, x, mask), steps, warm)
+            tokens, bytes_alg, dt = B * L, 2.0 * B * L * D * 2, "bf16"
+            name = "c4pad: TimestepNorm+MultiHeadEMA causal fwd bf16 L=32768 B=64 D=2048, 0-25% right padding"
         elif args.workload == "c1":
             L, B, D = 4096, 16, 1024
             x = torch.randn(B, L, D, generator=gen).to(dev).bfloat16()
