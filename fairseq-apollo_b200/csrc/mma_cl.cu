@@ -77,8 +77,8 @@ struct Cfg {
   static constexpr int kOffP = kOffT + kCh * 2 * 32 * 4;            // [kCh][kCm][32] uint4
   static constexpr int kOffG = kOffP + kCm * kCh * 4 * 32 * 4;      // [kCh][kCm][32] uint4
   static constexpr int kOffA = kOffG + kCm * kCh * 4 * 32 * 4;      // [kCh][16] f32 (q^16; kCplx: float2)
-  static constexpr int kOffWB = kOffA + kCm * kCh * 16 * 4;         // [kCh][2] f32
-  static constexpr int kOffKp = kOffWB + kCh * 2 * 4;               // [kCh][16] f32 scratch: kernel taps
+  static constexpr int kOffWB = kOffA + kCm * kCh * 16 * 4;         // [kCh] {w, w, b, b} f32 (pairs as the packed operations take them)
+  static constexpr int kOffKp = kOffWB + kCh * 4 * 4;               // [kCh][16] f32 scratch: kernel taps
   static constexpr int kOffBar = kOffKp + kCh * 16 * 4;             // full[kStages], done[kStages], xfree[2], abort word
   // mailboxes (kWp > 1): per warp, per kind (0: statistics, 1: pole states), per channel: 32 lanes x
   // 16 bytes of data, and one mbarrier whose phases count the steps that have been posted
@@ -277,8 +277,18 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 // turns the mask bytes of its 8 sequences x 32 positions into 0/1 flags, takes their prefix counts
 // with the same triangular MMA as the sums (the divisor of the running mean at each position), and
 // multiplies the inputs of the sums and the normalised values by the flags.
+// kPs: segmented form for problems of more than one wave of CTAs.  A strip is a serial chain along
+// the sequence, so a grid of (tile, group of sequences) CTAs runs in whole waves: 256 CTAs of 8 warps
+// on 148 SMs take two waves although they are 1.73 waves of work.  Here the sequence is cut into
+// n_seg runs and the grid has one CTA per work item (run, tile, group).  A CTA draws its item from a
+// counter when it starts, so the items are taken in run-major order by CTAs that are running, and
+// an item starts from the statistics and pole states that the item of the run before left in
+// global memory (the call's own mean / variance outputs, and h_out or a hand-off buffer) once that
+// item's flag is set.  An item depends on one that was drawn earlier, by a CTA that is running or
+// done, so the waits end; they are bounded like every other wait of this kernel.  The SMs stay
+// busy because the hardware hands the next CTA to whichever SM becomes free.
 template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false, int kWp = 1,
-          bool kMask = false, bool kSm = false>
+          bool kMask = false, bool kSm = false, bool kPs = false>
 __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
@@ -288,6 +298,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   static_assert(kWp == 1 || (!kXn && !kCplx && kEma), "the pipelined form covers the real EMA without the second output");
   static_assert(!kMask || (kWp == 1 && !kCplx && !(kXn && !kNorm)), "masks: real poles, not pipelined");
   static_assert(!kSm || (kWp == 1 && !kXn && !kCplx && kEma && !kMask), "state in shared memory: the plain real form");
+  static_assert(!kPs || (kWp == 1 && kWs == 1 && !kXn && !kCplx && kEma && !kMask && !kSm), "segmented: the plain real form");
   using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
   constexpr bool kMail = C::kMail;   // running quantities travel through / live in the mailboxes
   constexpr bool kLate = kWp > 1;    // ... and arrive from another warp, after this warp's own sums
@@ -315,6 +326,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
 
   const uint32_t sm_s = smem_u32(sm);
   const uint32_t abort_s = sm_s + kOffBar + (2 * kStages + 2) * 8;  // set when a bounded wait gave up
+  // kPs: the work item of this pass, its last step + 1 and (ring position - step), kept here rather
+  // than in registers that would be live across the whole step loop
+  const uint32_t item_s = abort_s + 4, iend_s = abort_s + 8, delta_s = abort_s + 12;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int wp = (tid >> 5) / kGroup;            // pipeline group: takes the steps i = wp (mod kWp)
@@ -330,10 +344,12 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   const uint32_t mail_in = sm_s + C::kOffMail + (uint32_t)wprev * C::kMailWarp + lane * 16;
   const uint32_t flag_in = sm_s + C::kOffFlag + (uint32_t)wprev * C::kFlagWarp;
   const int g = lane >> 2, q = lane & 3;
-  const int d0 = blockIdx.x * kCh;
-  const int b0 = blockIdx.y * kSeq;
+  int d0 = blockIdx.x * kCh;   // (kPs: set per work item)
+  int b0 = blockIdx.y * kSeq;
   const int L = a.L;
   const int nsteps = (L + kStep - 1) / kStep;
+  int i_begin = 0, i_end = nsteps;  // steps of this CTA (kPs: those of its run)
+  int seg = 0;
 
   if (tid == 0) {
     prefetch_tensormap(&tmx);
@@ -353,11 +369,31 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     }
     mbar_fence_init();
   }
+  if constexpr (kPs) {
+    if (tid == 0) st_volatile_s(item_s, (uint32_t)atomicAdd(a.sched, 1));
+  }
   __syncthreads();
+  if constexpr (kPs) {
+    const int item = (int)ld_volatile_s(item_s);   // (< n_items: the grid has one CTA per item)
+    const int n_grp = a.n_items / a.n_seg;
+    seg = item / n_grp;
+    const int grp = item - seg * n_grp;
+    d0 = (grp % a.tiles_d) * kCh;
+    b0 = (grp / a.tiles_d) * kSeq;
+    i_begin = seg * a.seg_steps;
+    i_end = min(nsteps, i_begin + a.seg_steps);
+    if (tid == 0) {
+      st_volatile_s(iend_s, (uint32_t)i_end);
+      st_volatile_s(delta_s, (uint32_t)(0 - i_begin));
+    }
+    // (visible to all after the barrier between the two phases of the matrices below)
+  }
   if (tid == 0) {
-    for (int s = 0; s < kStages - kWp && s < nsteps; ++s) {
-      mbar_expect_tx(&full[s], kStageBytes);
-      if (s != a.withhold_step) tma_load_3d(sm + kOffStages + s * kStageBytes, &tmx, d0, s * kStep, b0, &full[s]);
+    for (int s = 0; s < kStages - kWp && i_begin + s < i_end; ++s) {
+      const int s2 = s;
+      mbar_expect_tx(&full[s2], kStageBytes);
+      if (i_begin + s != a.withhold_step)
+        tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, (i_begin + s) * kStep, b0, &full[s2]);
     }
   }
 
@@ -394,13 +430,14 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       Ac[2 * it] = a16;
       Ac[2 * it + 1] = a16i;
     } else {
-      Ac[it] = a16;  // entry (ch, pole l); poles >= N stay 0
+      Ac[it] = a16;  // entry (ch, pole l); poles >= a.N stay 0
     }
     if (l < 2) {
       float v = (l == 0) ? 1.f : 0.f;
       if (kNorm && d < a.D) v = (l == 0) ? __ldg(a.gamma + d) : __ldg(a.beta + d);
       if (!kNorm && kMask && kEma && l == 0 && d < a.D) v = __ldg(a.omega + d);   // see the masked EMA epilogue
-      WB[ch * 2 + l] = v;
+      WB[ch * 4 + 2 * l] = v;
+      WB[ch * 4 + 2 * l + 1] = v;
     }
   }
   __syncthreads();
@@ -493,6 +530,23 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     Pc[ch * 32 + ln] = make_uint4(pr[0], pr[1], pr[2], pr[3]);
     Gc[ch * 32 + ln] = make_uint4(gr[0], gr[1], gr[2], gr[3]);
   }
+  if (kPs && seg > 0 && tid == 0) {
+    // the item of the run before (same tile and sequences) has written its statistics and states
+    const int* flag = a.sched + 1 + ((int)ld_volatile_s(item_s) - a.n_items / a.n_seg);
+    const long long start = clock64();
+    for (;;) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v != 0) break;
+      if (clock64() - start > wait_limit) {
+        g_device_error = 3;
+        st_volatile_s(abort_s, 1u);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  if constexpr (kPs) __syncthreads();   // the hand-off of the run before may be read
 
   // ---- running state of this thread: sequence b0 + g, channels 8*warp + e ----------------------
   const int bseq = b0 + g;
@@ -540,6 +594,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
           hc[e][k] = have ? __ldg(a.h_in + c) : 0.f;
           hci[e][k] = have ? __ldg(a.h_in + c + 1) : 0.f;
+        } else if (kPs && seg > 0) {  // what the run before left (written by another SM: read past the L1)
+          const float* hand = a.h_out ? a.h_out : a.handoff_h;
+          hc[e][k] = (ok && pole < a.N) ? __ldcg(hand + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
         } else {
           hc[e][k] = (kEma && ok && a.h_in && pole < a.N) ? __ldg(a.h_in + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
         }
@@ -548,11 +605,20 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       m2_run[e] = 0.f;
       s1_run[e] = 0.f;
       if (kNorm && ok) {
-        const float c0 = (float)a.prev_count[bseq];
-        const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
-        mu_run[e] = mu;
-        m2_run[e] = c0 * vv;
-        s1_run[e] = c0 * mu;
+        if (kPs && seg > 0) {
+          // the running sums as the run before held them (bit for bit, so that the result does not
+          // depend on the number of runs), its mean from the call's own output
+          const float2 sm2 = __ldcg(reinterpret_cast<const float2*>(a.handoff_s) + (size_t)bseq * a.D + d);
+          mu_run[e] = __ldcg(a.mean_out + (size_t)bseq * a.D + d);
+          s1_run[e] = sm2.x;
+          m2_run[e] = sm2.y;
+        } else {
+          const float c0 = (float)a.prev_count[bseq];
+          const float mu = a.prev_mean[(size_t)bseq * a.D + d], vv = a.prev_var[(size_t)bseq * a.D + d];
+          mu_run[e] = mu;
+          m2_run[e] = c0 * vv;
+          s1_run[e] = c0 * mu;
+        }
       }
     }
   });
@@ -561,7 +627,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   // thread's sequence; the flags of a step are fetched one step ahead
   float n_run = nbase - 1.f, nvalid = 0.f;
   const unsigned char* mrow = (kMask && seq_ok) ? a.mask + (size_t)bseq * L : nullptr;
-  const float ut0 = (2 * q <= g) ? 1.f : 0.f, ut1 = (2 * q + 1 <= g) ? 1.f : 0.f;
+  // (minus the 0/1 triangle: the prefix sums come out negated, which lets the finishing arithmetic
+  // below form -(mean - c) and -(variance) with fused multiply-adds only)
+  const float ut0 = (2 * q <= g) ? -1.f : 0.f, ut1 = (2 * q + 1 <= g) ? -1.f : 0.f;
   const float eps = a.eps;
   // position offsets of the 8 vectors this thread touches: j = 0..3 chunk 0, j = 4..7 chunk 1.
   // Rows of sequences g and g + 1 lie a multiple of 128 bytes apart, so the two sequences of a
@@ -588,7 +656,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   const uint32_t p_base = sm_s + kOffP + (cbase * kCm * 32 + lane) * 16;
   const uint32_t g_base = sm_s + kOffG + (cbase * kCm * 32 + lane) * 16;
   const uint32_t a_base = sm_s + kOffA + (cbase * 16 + 2 * q) * 4 * kCm;
-  const uint32_t wb_base = sm_s + kOffWB + cbase * 8;
+  const uint32_t wb_base = sm_s + kOffWB + cbase * 16;
 
   __syncthreads();  // matrices visible
 
@@ -607,9 +675,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   };
   uint32_t mk_next = mask_bits(wp);
   bool live = true;  // false once a bounded wait of this thread gave up
-  for (int i = wp; i < nsteps; i += kWp) {
-    const int s = i % kStages;
-    const uint32_t ph = (uint32_t)((i / kStages) & 1);
+  for (int i = i_begin + wp; i < (kPs ? (int)ld_volatile_s(iend_s) : nsteps); i += kWp) {
+    const int gi = kPs ? i + (int)ld_volatile_s(delta_s) : i;  // position in the ring
+    const int s = gi % kStages;
+    const uint32_t ph = (uint32_t)((gi / kStages) & 1);
     unsigned char* stage = sm + kOffStages + s * kStageBytes;
     const uint32_t stage_s = sm_s + kOffStages + s * kStageBytes;
     if (ld_volatile_s(abort_s) != 0) live = false;  // another waiter of this CTA gave up: leave together
@@ -658,10 +727,10 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       const int src3 = lane | 3;
       const float t0 = __shfl_sync(0xffffffffu, D0[1], src3), t1 = __shfl_sync(0xffffffffu, D1[1], src3);
       const float t2 = __shfl_sync(0xffffffffu, D0[3], src3), t3 = __shfl_sync(0xffffffffu, D1[3], src3);
-      const float c0 = n_run, c1 = c0 + t0, c2 = c1 + t1, c3 = c2 + t2;
+      const float c0 = n_run, c1 = c0 - t0, c2 = c1 - t1, c3 = c2 - t2;   // (the triangle is negated)
       n_in = n_run;
-      n_end = c3 + t3;
-      const float cnt[8] = {c0 + D0[0], c0 + D0[1], c1 + D1[0], c1 + D1[1], c2 + D0[2], c2 + D0[3], c3 + D1[2], c3 + D1[3]};
+      n_end = c3 - t3;
+      const float cnt[8] = {c0 - D0[0], c0 - D0[1], c1 - D1[0], c1 - D1[1], c2 - D0[2], c2 - D0[3], c3 - D1[2], c3 - D1[3]};
 #pragma unroll
       for (int j = 0; j < 8; ++j) invn[j] = rcp_fast(fmaxf(cnt[j], 1.f));
       step_has_valid = n_end > n_in;
@@ -726,6 +795,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           // 0/1 upper-triangular matrix per half.  The total of a half is its last prefix, held
           // by the lane with q = 3; a shuffle hands it to the row's other lanes, and the carries
           // (running total + totals of the halves before) are added afterwards in fp32.
+          // All sums below are NEGATED (S1, S2, k1, k2, the E totals): the MMAs multiply by minus the
+          // triangle, and the carries start from minus the running totals.
           float k1[4];  // carry of the sum of x for (row g, first half), (g, second), (g + 8, first), (g + 8, second)
           {  // sum of x: exact (bf16 inputs, fp32 accumulation)
             float D0[4], D1[4], E0[4], E1[4];
@@ -735,29 +806,29 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
             // column, i.e. into every lane of the row (a shuffle goes through the LSU data pipe, which
             // the two-warps-per-column form loads to 60 %)
             if (kLeanLsu) {
-              mma_tf32(E0, xf[0], xf[4], xf[1], xf[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
-              mma_tf32(E1, xf[2], xf[6], xf[3], xf[7], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E0, xf[0], xf[4], xf[1], xf[5], -1.f, -1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E1, xf[2], xf[6], xf[3], xf[7], -1.f, -1.f, 0.f, 0.f, 0.f, 0.f);
             } else {  // the total of a half is its last prefix, held by the lane with q = 3
               const int src3 = lane | 3;
               E0[0] = __shfl_sync(0xffffffffu, D0[1], src3); E1[0] = __shfl_sync(0xffffffffu, D1[1], src3);
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
             // kWp > 1: offsets of the halves only; the running total is added once it has arrived
-            k1[0] = kLate ? 0.f : (kSm ? s1_in : s1_run[e]);
+            k1[0] = kLate ? 0.f : -(kSm ? s1_in : s1_run[e]);
             k1[1] = k1[0] + E0[0];
             k1[2] = k1[1] + E1[0];
             k1[3] = k1[2] + E0[2];
-            tot1 = k1[3] + E1[2];
+            tot1 = -k1[3] - E1[2];   // (positive; kLate: still without the incoming total)
             S1[0] = D0[0]; S1[1] = D0[1]; S1[4] = D0[2]; S1[5] = D0[3];
             S1[2] = D1[0]; S1[3] = D1[1]; S1[6] = D1[2]; S1[7] = D1[3];
           }
           // deviations from the centre, two positions (t, t + 1 of one row) per packed operation
           f32x2 dv2[4];
+          const f32x2 cm2 = pack2(cm, cm);
           {
-            const f32x2 ncm2 = pack2(-cm, -cm);
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
-              dv2[jp] = add2(pack2(xf[2 * jp], xf[2 * jp + 1]), ncm2);
+              dv2[jp] = sub2(pack2(xf[2 * jp], xf[2 * jp + 1]), cm2);
               if constexpr (kMask) dv2[jp] = mul2(dv2[jp], vf2[jp]);   // no deviation at a padded position
             }
           }
@@ -775,19 +846,19 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
             mma_tf32(D0, sq[0], sq[4], sq[1], sq[5], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             mma_tf32(D1, sq[2], sq[6], sq[3], sq[7], ut0, ut1, 0.f, 0.f, 0.f, 0.f);
             if (kLeanLsu) {
-              mma_tf32(E0, sq[0], sq[4], sq[1], sq[5], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
-              mma_tf32(E1, sq[2], sq[6], sq[3], sq[7], 1.f, 1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E0, sq[0], sq[4], sq[1], sq[5], -1.f, -1.f, 0.f, 0.f, 0.f, 0.f);
+              mma_tf32(E1, sq[2], sq[6], sq[3], sq[7], -1.f, -1.f, 0.f, 0.f, 0.f, 0.f);
             } else {
               const int src3 = lane | 3;
               E0[0] = __shfl_sync(0xffffffffu, D0[1], src3); E1[0] = __shfl_sync(0xffffffffu, D1[1], src3);
               E0[2] = __shfl_sync(0xffffffffu, D0[3], src3); E1[2] = __shfl_sync(0xffffffffu, D1[3], src3);
             }
             const float ea = E0[0], fa = E1[0], eb = E0[2], fb = E1[2];
-            k2[0] = kLate ? 0.f : (kSm ? m2_in : m2_run[e]);
+            k2[0] = kLate ? 0.f : -(kSm ? m2_in : m2_run[e]);
             k2[1] = k2[0] + ea;
             k2[2] = k2[1] + fa;
             k2[3] = k2[2] + eb;
-            tot2 = (ea + fa) + (eb + fb);
+            tot2 = -(ea + fa) - (eb + fb);   // (positive)
             S2[0] = D0[0]; S2[1] = D0[1]; S2[4] = D0[2]; S2[5] = D0[3];
             S2[2] = D1[0]; S2[3] = D1[1]; S2[6] = D1[2]; S2[7] = D1[3];
           }
@@ -809,8 +880,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
             tot1 += s1_in;
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
-              k1[jp] += s1_in;
-              k2[jp] += m2_base;
+              k1[jp] -= s1_in;
+              k2[jp] -= m2_base;
             }
           } else {
             m2_base = m2_run[e];
@@ -832,20 +903,21 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
             s1_run[e] = tot1;
             m2_run[e] = m2new;
           }
-          const uint2 wbu = lds64<e * 8>(wb_base);
-          const float2 wb = make_float2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
+          const uint4 wbu = lds128<e * 16>(wb_base);   // {w, w, b, b}
           {
-            const f32x2 ncm2 = pack2(-cm, -cm), eps2 = pack2(eps, eps);
-            const f32x2 w2 = pack2(wb.x, wb.x), b2 = pack2(wb.y, wb.y);
+            const f32x2 neps2 = pack2(-eps, -eps);
+            const f32x2 w2 = pack2(__uint_as_float(wbu.x), __uint_as_float(wbu.y));
+            const f32x2 b2 = pack2(__uint_as_float(wbu.z), __uint_as_float(wbu.w));
 #pragma unroll
             for (int jp = 0; jp < 4; ++jp) {
               const f32x2 in2 = pack2(invn[2 * jp], invn[2 * jp + 1]);
-              const f32x2 u2 = fma2(add2(pack2(S1[2 * jp], S1[2 * jp + 1]), pack2(k1[jp], k1[jp])), in2, ncm2);  // mean - c
-              const f32x2 e2 = fma2(add2(pack2(S2[2 * jp], S2[2 * jp + 1]), pack2(k2[jp], k2[jp])), in2, eps2);
-              float va, vb;
-              unpack2(sub2(e2, mul2(u2, u2)), va, vb);
-              const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(va, eps)), rsqrt_fast(fmaxf(vb, eps))), w2);
-              f32x2 xn2 = fma2(sub2(dv2[jp], u2), sc2, b2);
+              // (negated sums) nu = c - mean, ne = -(E[d^2] + eps), nv = nu^2 + ne = -(variance + eps)
+              const f32x2 nu2 = fma2(add2(pack2(S1[2 * jp], S1[2 * jp + 1]), pack2(k1[jp], k1[jp])), in2, cm2);
+              const f32x2 ne2 = fma2(add2(pack2(S2[2 * jp], S2[2 * jp + 1]), pack2(k2[jp], k2[jp])), in2, neps2);
+              float nva, nvb;
+              unpack2(fma2(nu2, nu2, ne2), nva, nvb);
+              const f32x2 sc2 = mul2(pack2(rsqrt_fast(fmaxf(-nva, eps)), rsqrt_fast(fmaxf(-nvb, eps))), w2);
+              f32x2 xn2 = fma2(add2(dv2[jp], nu2), sc2, b2);
               if constexpr (kMask) xn2 = mul2(xn2, vf2[jp]);   // TimestepNorm writes 0 at a padded position
               unpack2(xn2, xn[2 * jp], xn[2 * jp + 1]);
             }
@@ -963,7 +1035,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         if constexpr (kMask && !kNorm) {
           // the Toeplitz diagonal carries omega times the masked input: a padded position still gets
           // omega times its own (unmasked) input, as the reference's residual does
-          const float om = __uint_as_float(lds32<e * 8>(wb_base));
+          const float om = __uint_as_float(lds32<e * 16>(wb_base));
 #pragma unroll
           for (int j = 0; j < 8; ++j) yv[h2][j] = fmaf(om, xpad[j], yv[h2][j]);
         }
@@ -1025,9 +1097,9 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           }
           // refill: the stage of this thread's previous store (step i - kWp) takes tile i - kWp + kStages
           const int nt = i + kStages - kWp;
-          if (nt < nsteps) {
+          if (nt < (kPs ? (int)ld_volatile_s(iend_s) : nsteps)) {
             if (!kXn) bulk_wait_read<1>();  // the store issued before this one has drained its stage
-            const int s2 = nt % kStages;
+            const int s2 = (kPs ? gi + kStages - kWp : nt) % kStages;
             mbar_expect_tx(&full[s2], kStageBytes);
             if (nt != a.withhold_step)
               tma_load_3d(sm + kOffStages + s2 * kStageBytes, &tmx, d0, nt * kStep, b0, &full[s2]);
@@ -1063,7 +1135,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     for (int e = 0; e < kE; ++e) {
       const int d = d0 + cbase + e;
       if (kNorm && d < a.D) {
-        const float n = kMask ? n_run : (float)a.prev_count[bseq] + (float)L;
+        const int i_last = kPs ? (int)ld_volatile_s(iend_s) : nsteps;
+        const float n = kMask ? n_run : (float)a.prev_count[bseq] + (float)min(i_last * kStep, L);
         float mo = mu_run[e], vo = fmaxf(m2_run[e] / n, 0.f);
         if (kMask && !(n > 0.f)) {  // nothing counted, before or in this call: the incoming statistics stand
           mo = a.prev_mean[(size_t)bseq * a.D + d];
@@ -1071,12 +1144,16 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
         }
         a.mean_out[(size_t)bseq * a.D + d] = mo;
         a.var_out[(size_t)bseq * a.D + d] = vo;
+        if constexpr (kPs)
+          reinterpret_cast<float2*>(a.handoff_s)[(size_t)bseq * a.D + d] = make_float2(s1_run[e], m2_run[e]);
       }
     }
-    if (kNorm && blockIdx.x == 0 && warp == 0 && hf == 0)
+    if (kNorm && d0 == 0 && (!kPs || (int)ld_volatile_s(iend_s) == nsteps) && warp == 0 && hf == 0)
       a.count_out[bseq] = a.prev_count[bseq] + (kMask ? (long long)nvalid : (long long)L);
   }
-  if (kEma && seq_ok && a.h_out) {
+  // (kPs: a run that is not the last leaves its pole states for the next one, in h_out if the call has one)
+  float* const h_dst = (kPs && !a.h_out && (int)ld_volatile_s(iend_s) < nsteps) ? a.handoff_h : a.h_out;
+  if (kEma && seq_ok && h_dst) {
 #pragma unroll
     for (int e = 0; e < kE; ++e) {
       const int d = d0 + cbase + e;
@@ -1087,14 +1164,22 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           if (pole < a.N) {
             if (kCplx) {
               const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
-              a.h_out[c] = hc[e][k];
-              a.h_out[c + 1] = hci[e][k];
+              h_dst[c] = hc[e][k];
+              h_dst[c + 1] = hci[e][k];
             } else {
-              a.h_out[((size_t)bseq * a.D + d) * a.N + pole] = hc[e][k];
+              h_dst[((size_t)bseq * a.D + d) * a.N + pole] = hc[e][k];
             }
           }
         }
       }
+    }
+  }
+  if constexpr (kPs) {
+    // publish: every thread's statistics and states are written, then the item's flag is set
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(a.sched + 1 + (int)ld_volatile_s(item_s)), "r"(1) : "memory");
     }
   }
 }
@@ -1131,6 +1216,98 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
                                   std::to_string(kWs) + " pipe=" + std::to_string(kWp) + (kNorm ? " norm" : "") +
                                   (kEma ? " ema" : "") + (kCplx ? " complex" : "") + (kXn ? " xn" : "") + (kMask ? " mask" : "") + (kSm ? " smstate" : "");
   g_last_kernel.store(name.c_str(), std::memory_order_relaxed);
+  return true;
+}
+
+// ---- segmented form (kPs): scratch and launch ---------------------------------------------------
+// The hand-off of the pole states between the runs of a strip (when the call has no h_out) and the
+// work counter with the items' flags live in fixed device arrays of this library; nothing is
+// allocated.  Calls that use them must not overlap: a call on another stream than the one before
+// first waits (on the device) for that one's event.
+constexpr size_t kHandoffFloats = size_t(4) << 20;  // 16 MiB: pole states of B x D x ndim <= 4 Mi values
+constexpr size_t kHandoffStats = size_t(512) << 10;  // 2 MiB: running sums (two values) of B x D <= 256 Ki channels
+constexpr int kSchedItems = 16384;
+__device__ __align__(256) float g_handoff[kHandoffFloats];
+__device__ __align__(256) float g_handoff_stats[kHandoffStats];
+__device__ __align__(256) int g_sched[1 + kSchedItems];
+
+struct SegScratch {
+  bool tried = false, ok = false;
+  float* handoff = nullptr;
+  float* stats = nullptr;
+  int* sched = nullptr;
+  cudaEvent_t done = nullptr;
+  cudaStream_t last = nullptr;
+  bool used = false;
+};
+static std::mutex g_seg_mutex;
+static SegScratch g_seg[16];
+
+// (g_seg_mutex held) scratch of the current device, or nullptr
+static SegScratch* seg_scratch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  SegScratch& sc = g_seg[dev];
+  if (!sc.tried) {
+    sc.tried = true;
+    bool ok = cudaGetSymbolAddress((void**)&sc.handoff, g_handoff) == cudaSuccess;
+    ok = ok && cudaGetSymbolAddress((void**)&sc.stats, g_handoff_stats) == cudaSuccess;
+    ok = ok && cudaGetSymbolAddress((void**)&sc.sched, g_sched) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) cudaGetLastError();
+    sc.ok = ok;
+  }
+  return sc.ok ? &sc : nullptr;
+}
+
+// Runs the call as n_seg runs per strip, one CTA per (run, tile, group of sequences).  False (nothing launched) when the
+// call does not fit the scratch, the stream is being captured, or the set-up failed.
+template <bool kNorm, bool kSilu>
+static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
+                             long long ysl, const StreamArgs& a_in, int n_seg, cudaStream_t s) {
+  constexpr int kCg = 8;
+  using C = Cfg<kCg, false, false, 1, 1, false>;
+  StreamArgs a = a_in;
+  const int nsteps = (a.L + kStep - 1) / kStep;
+  if ((n_seg != 2 && n_seg != 4 && n_seg != 8) || nsteps % n_seg != 0) return false;
+  a.n_seg = n_seg;
+  a.seg_steps = nsteps / n_seg;
+  a.tiles_d = (a.D + C::kCh - 1) / C::kCh;
+  const long long items = (long long)a.tiles_d * ((a.B + kSeq - 1) / kSeq) * n_seg;
+  if (items > kSchedItems) return false;
+  a.n_items = (int)items;
+  if (!a.h_out && (size_t)a.B * a.D * a.N > kHandoffFloats) return false;
+  if (kNorm && (size_t)a.B * a.D * 2 > kHandoffStats) return false;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return false;
+  }
+  CUtensorMap tx, ty;
+  if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+  if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, true, false, 1, false, false, true>;
+  std::lock_guard<std::mutex> lock(g_seg_mutex);
+  SegScratch* sc = seg_scratch();
+  if (sc == nullptr) return false;
+  a.handoff_h = sc->handoff;
+  a.handoff_s = sc->stats;
+  a.sched = sc->sched;
+  if (sc->used && sc->last != s && cudaStreamWaitEvent(s, sc->done, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (cudaMemsetAsync(sc->sched, 0, sizeof(int) * (size_t)(1 + a.n_items), s) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  launch(kern, dim3((unsigned)a.n_items), dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, ty, a);
+  cudaEventRecord(sc->done, s);
+  sc->last = s;
+  sc->used = true;
+  static const std::string base = std::string("tsn_ema_mma tile=8 warps_per_column=1 pipe=1") + (kNorm ? " norm" : "") + " ema segmented runs=";
+  static const std::string names[3] = {base + "2", base + "4", base + "8"};
+  g_last_kernel.store(names[n_seg == 2 ? 0 : n_seg == 4 ? 1 : 2].c_str(), std::memory_order_relaxed);
   return true;
 }
 
@@ -1182,6 +1359,18 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     return (double)waves * ch;  // time ~ waves x work per CTA
   };
   int tile = g_options[OPT_MMA_TILE].load();
+  // segmented form (64-channel tile, the sequence in 2, 4 or 8 runs): real EMA, no second output, no mask
+  if (tile == 82 || tile == 84 || tile == 88) {
+    const int n_seg = tile - 80;
+    tile = 0;
+    if (can_pipe && a_in.B >= 4) {
+      const bool ok = norm ? (a_in.silu ? launch_segmented<true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s)
+                                        : launch_segmented<true, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s))
+                           : (a_in.silu ? launch_segmented<false, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s)
+                                        : launch_segmented<false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s));
+      if (ok) return true;
+    }
+  }
   // pipelined forms (real EMA, with or without the normalisation, no second output)
   if ((tile == 222 || tile == 224 || tile == 422 || tile == 124) && (a_in.cplx || !ema || want_xn || masked)) tile = 0;
   if (tile == 71 && (a_in.cplx || !ema || want_xn || masked)) tile = 0;
@@ -1189,8 +1378,33 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
       tile != 124 && tile != 71) {
     // (the EMA alone is closer to the memory bound and prefers the 128-byte rows of the 64-channel
     // tile: 1.71 against 2.02 ms at B = 64, L = 16384, D = 2048, unless 56 channels save a wave)
-    if (ctas(64) >= 148 || ctas(56) >= 148)
+    if (ctas(64) >= 148 || ctas(56) >= 148) {
       tile = waves_cost(56) * (norm ? 1.0 : 1.15) < waves_cost(64) ? 7 : 8;
+      // More than one wave: whole waves waste the SMs that the last one leaves idle.  The segmented
+      // form takes ceil(items x runs / SMs) / runs waves of 64-channel steps instead (a step of the
+      // 56- and of the 64-channel tile take about the same time); it pays when that saves 4 %.
+      if (can_pipe && a_in.B >= 4 && ctas(64) > 148) {
+        const int nsteps = (a_in.L + kStep - 1) / kStep;
+        const double plain = (double)((ctas(tile == 7 ? 56 : 64) + 147) / 148);
+        int best = 0;
+        double best_cost = plain * 0.96;
+        for (int n_seg = 2; n_seg <= 8; n_seg *= 2) {
+          if (nsteps % n_seg != 0 || nsteps / n_seg < 64) continue;
+          const double cost = (double)((ctas(64) * n_seg + 147) / 148) / n_seg * 1.02;
+          if (cost < best_cost) {
+            best_cost = cost;
+            best = n_seg;
+          }
+        }
+        if (best != 0) {
+          const bool ok = norm ? (a_in.silu ? launch_segmented<true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, best, s)
+                                            : launch_segmented<true, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, best, s))
+                               : (a_in.silu ? launch_segmented<false, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, best, s)
+                                            : launch_segmented<false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, best, s));
+          if (ok) return true;
+        }
+      }
+    }
     else if (can_pipe && (ctas(16) <= 148 || a_in.B < 4))
       // too few strips for the SMs: four groups of warps per 16-channel strip set, pipelined along the
       // sequence (B = 8, L = 32768, D = 2048: 1.21 -> 1.05 ms; B = 16, L = 4096, D = 1024: 0.168 -> 0.143 ms;

@@ -350,6 +350,81 @@ def test_pipelined_tensor_core_forms(tile, bsz, length, dim):
     assert _lib.device_error() == 0
 
 
+@pytest.mark.parametrize("runs", [2, 4, 8])
+@pytest.mark.parametrize("bsz,length,dim,state", [(8, 2048, 192, True), (20, 1024, 72, False), (4, 4096, 64, True)])
+def test_segmented_tensor_core_form(runs, bsz, length, dim, state):
+    """The segmented form of the tensor-core kernel (the sequence cut into runs, one CTA per run and
+    tile, the running sums and pole states handed from a run to the next through global memory
+    behind a flag) against the oracle and, bit for bit, against the unsegmented 64-channel form:
+    with and without an exported state (the pole states then travel through h_out or through the
+    library's hand-off buffer), with carried-in statistics and states, the EMA alone with SiLU, a
+    channel count that leaves a partial tile and a batch that leaves a partial group of sequences;
+    two calls in a row reuse the counter and flags."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(runs * 1000 + length)
+    prm = make_ema_params(gen, dim, 16)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.1 - 0.3).to(torch.bfloat16)
+    pc = torch.full((bsz,), 3, dtype=torch.int64)
+    pc[0] = 0
+    pm = torch.randn(bsz, dim, generator=gen) * 0.1 - 0.3
+    pv = torch.rand(bsz, dim, generator=gen) + 0.5
+    gamma = torch.randn(dim, generator=gen) * 0.1 + 1
+    beta = torch.randn(dim, generator=gen) * 0.1
+    h0 = torch.randn(bsz, dim, 16, generator=gen) * 0.3
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    xn, cnt, mean, var = O.timestep_norm(x.float(), pc, pm, pv, gamma, beta, None, acc_dtype=torch.float64)[:4]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, None, h=h0, return_state=True)
+    eref = O.ema_forward_recurrence(x.float().transpose(1, 2), *prm, None, h=h0, silu=True)
+    res = {}
+    for t in (80 + runs, 80 + runs, 8):
+        _lib.set_option(2, t)
+        try:
+            fused = M.ops.tsn_ema_forward(x.cuda(), pc.cuda(), pm.cuda(), pv.cuda(), gamma.cuda(), beta.cuda(), 1e-5,
+                                          p, q, g, prm[4].cuda(), None, h_in=h0.cuda(), want_state=state)
+            name = _lib.last_kernel()
+            ema = M.ops.ema_forward(x.cuda().transpose(1, 2), p, q, g, prm[4].cuda(), None, h0.cuda(), silu=True)
+            name2 = _lib.last_kernel()
+        finally:
+            _lib.set_option(2, 0)
+        if t != 8:
+            assert "segmented runs=%d" % runs in name and "segmented runs=%d" % runs in name2, (name, name2)
+        else:
+            assert "tile=8" in name and "segmented" not in name, name
+        res[t] = (fused, ema)
+    fused, ema = res[80 + runs]
+    assert rel_l2(fused["y"].float(), yref.transpose(1, 2)) < 1e-2
+    assert rel_l2(ema.float(), eref) < 1e-2
+    assert torch.equal(fused["count"].cpu(), cnt)
+    assert rel_l2(fused["mean"], mean) < 1e-4 and rel_l2(fused["var"], var) < 1e-3
+    if state:
+        assert rel_l2(fused["h"], href) < 1e-2
+        assert torch.equal(fused["h"], res[8][0]["h"])
+    # the hand-off is exact: the same bits as the unsegmented form
+    assert torch.equal(fused["y"], res[8][0]["y"])
+    assert torch.equal(ema, res[8][1])
+    assert torch.equal(fused["mean"], res[8][0]["mean"]) and torch.equal(fused["var"], res[8][0]["var"])
+    assert _lib.device_error() == 0
+
+
+def test_segmented_form_falls_back():
+    """A number of steps that the runs do not divide takes the unsegmented kernel."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(9)
+    prm = make_ema_params(gen, 64, 16)
+    x = torch.randn(8, 32 * 7, 64, generator=gen).to(torch.bfloat16).cuda()
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    _lib.set_option(2, 84)
+    try:
+        y = M.ops.ema_forward(x.transpose(1, 2), p, q, g, prm[4].cuda(), None, None)
+        name = _lib.last_kernel()
+    finally:
+        _lib.set_option(2, 0)
+    assert "tsn_ema_mma" in name and "segmented" not in name, name
+    assert torch.isfinite(y.float()).all()
+
+
 @pytest.mark.parametrize("tile", [7, 22, 224])
 def test_bounded_wait_runs_out(tile):
     """A device-side wait that can never complete must give up, not hang: a test switch makes the
