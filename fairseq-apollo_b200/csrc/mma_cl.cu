@@ -286,9 +286,14 @@ __device__ __forceinline__ uint32_t vec_off(int seq, int t, int cg) {
 // global memory (the call's own mean / variance outputs, and h_out or a hand-off buffer) once that
 // item's flag is set.  An item depends on one that was drawn earlier, by a CTA that is running or
 // done, so the waits end; they are bounded like every other wait of this kernel.  The SMs stay
-// busy because the hardware hands the next CTA to whichever SM becomes free.
+// busy because the hardware hands the next CTA to whichever SM becomes free.  A CTA lives for one
+// run only, so its set-up counts: the matrices of each tile of channels are built once, by a launch
+// of this kernel in its builder form (kPs == 2: set-up only, the shared-memory image of the
+// matrices copied to global memory), and the CTAs of the runs (kPs == 1) fetch that image with a
+// bulk copy instead of building it.  (kPs == 3: the CTAs of the runs build their matrices themselves;
+// kept for the normalising form, whose step loop the compiler allocates better that way.)
 template <bool kNorm, int kCg, bool kSilu, int kWs, bool kXn, bool kEma = true, bool kCplx = false, int kWp = 1,
-          bool kMask = false, bool kSm = false, bool kPs = false>
+          bool kMask = false, bool kSm = false, int kPs = 0>
 __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     tsn_ema_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                        const __grid_constant__ CUtensorMap tmn, StreamArgs a) {
@@ -299,6 +304,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   static_assert(!kMask || (kWp == 1 && !kCplx && !(kXn && !kNorm)), "masks: real poles, not pipelined");
   static_assert(!kSm || (kWp == 1 && !kXn && !kCplx && kEma && !kMask), "state in shared memory: the plain real form");
   static_assert(!kPs || (kWp == 1 && kWs == 1 && !kXn && !kCplx && kEma && !kMask && !kSm), "segmented: the plain real form");
+
   using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
   constexpr bool kMail = C::kMail;   // running quantities travel through / live in the mailboxes
   constexpr bool kLate = kWp > 1;    // ... and arrive from another warp, after this warp's own sums
@@ -312,6 +318,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   constexpr int kStageBytes = C::kStageBytes;
   constexpr int kOffStages = C::kOffStages, kOffT = C::kOffT, kOffP = C::kOffP, kOffG = C::kOffG;
   constexpr int kOffA = C::kOffA, kOffWB = C::kOffWB, kOffKp = C::kOffKp, kOffBar = C::kOffBar;
+  constexpr int kMatBytes = C::kOffKp - C::kOffT;   // T, P, G, q^16 and the affine pair of a tile
+  static_assert(kMatBytes % 16 == 0 && C::kOffT % 16 == 0, "bulk copies move 16-byte units");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint32_t* Tc = reinterpret_cast<uint32_t*>(sm + kOffT);
@@ -362,6 +370,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       mbar_init(&xfree[0], 1);
       mbar_init(&xfree[1], 1);
     }
+    if (kPs == 1) mbar_init(&xfree[0], 1);   // (here: the bulk copy of the matrices)
     st_volatile_s(abort_s, 0u);
     if (kWp > 1) {  // hand-off barriers: all 32 lanes of the posting warp arrive
       for (int k = 0; k < C::kWarps * 2 * C::kE; ++k)
@@ -369,11 +378,11 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     }
     mbar_fence_init();
   }
-  if constexpr (kPs) {
+  if constexpr (kPs == 1 || kPs == 3) {
     if (tid == 0) st_volatile_s(item_s, (uint32_t)atomicAdd(a.sched, 1));
   }
   __syncthreads();
-  if constexpr (kPs) {
+  if constexpr (kPs == 1 || kPs == 3) {
     const int item = (int)ld_volatile_s(item_s);   // (< n_items: the grid has one CTA per item)
     const int n_grp = a.n_items / a.n_seg;
     seg = item / n_grp;
@@ -388,7 +397,13 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     }
     // (visible to all after the barrier between the two phases of the matrices below)
   }
-  if (tid == 0) {
+  if (tid == 0 && kPs != 2) {
+    if constexpr (kPs == 1) {
+      const unsigned char* src = a.matrices + (size_t)(d0 / kCh) * kMatBytes;
+      mbar_expect_tx(&xfree[0], kMatBytes);
+      for (int o = 0; o < kMatBytes; o += 32768)
+        bulk_load_1d(sm + kOffT + o, src + o, (uint32_t)min(32768, kMatBytes - o), &xfree[0]);
+    }
     for (int s = 0; s < kStages - kWp && i_begin + s < i_end; ++s) {
       const int s2 = s;
       mbar_expect_tx(&full[s2], kStageBytes);
@@ -398,7 +413,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   }
 
   // ---- per-channel matrices, phase 1: kernel taps k'[l], q^16, affine ---------------------
-  for (int it = tid; it < kCh * 16; it += kThreads) {
+  for (int it = tid; kPs != 1 && it < kCh * 16; it += kThreads) {
     const int ch = it >> 4, l = it & 15;
     const int d = d0 + ch;
     float acc = 0.f, a16 = 0.f, a16i = 0.f;
@@ -442,7 +457,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   }
   __syncthreads();
   // ---- phase 2: fragment-ordered T, P, G --------------------------------------------------
-  for (int it = tid; kEma && it < kCh * 32; it += kThreads) {
+  for (int it = tid; kEma && kPs != 1 && it < kCh * 32; it += kThreads) {
     const int ch = it >> 5, ln = it & 31;
     const int gg = ln >> 2, qq = ln & 3;
     const int d = d0 + ch;
@@ -548,6 +563,17 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   }
   if constexpr (kPs) __syncthreads();   // the hand-off of the run before may be read
 
+  if constexpr (kPs == 2) {
+    // builder: the image of the matrices goes to global memory, and that is all
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(a.matrices + (size_t)blockIdx.x * kMatBytes);
+    const uint4* src = reinterpret_cast<const uint4*>(sm + kOffT);
+    for (int it = tid; it < kMatBytes / 16; it += kThreads) dst[it] = src[it];
+    return;
+  }
+  if constexpr (kPs == 1) {
+    if (!mbar_wait_lim(&xfree[0], 0u, abort_s, wait_limit)) { /* abort word set: every warp leaves at its first step */ }
+  }
   // ---- running state of this thread: sequence b0 + g, channels 8*warp + e ----------------------
   const int bseq = b0 + g;
   const bool seq_ok = bseq < a.B;
@@ -1226,7 +1252,9 @@ static bool launch_variant(int dtype, const void* x, void* y, long long xsb, lon
 // first waits (on the device) for that one's event.
 constexpr size_t kHandoffFloats = size_t(4) << 20;  // 16 MiB: pole states of B x D x ndim <= 4 Mi values
 constexpr size_t kHandoffStats = size_t(512) << 10;  // 2 MiB: running sums (two values) of B x D <= 256 Ki channels
+constexpr size_t kMatrixBytes = size_t(12) << 20;   // 12 MiB: the matrices of 144 tiles of 64 channels
 constexpr int kSchedItems = 16384;
+__device__ __align__(256) unsigned char g_matrices[kMatrixBytes];
 __device__ __align__(256) float g_handoff[kHandoffFloats];
 __device__ __align__(256) float g_handoff_stats[kHandoffStats];
 __device__ __align__(256) int g_sched[1 + kSchedItems];
@@ -1235,6 +1263,7 @@ struct SegScratch {
   bool tried = false, ok = false;
   float* handoff = nullptr;
   float* stats = nullptr;
+  unsigned char* matrices = nullptr;
   int* sched = nullptr;
   cudaEvent_t done = nullptr;
   cudaStream_t last = nullptr;
@@ -1252,6 +1281,7 @@ static SegScratch* seg_scratch() {
     sc.tried = true;
     bool ok = cudaGetSymbolAddress((void**)&sc.handoff, g_handoff) == cudaSuccess;
     ok = ok && cudaGetSymbolAddress((void**)&sc.stats, g_handoff_stats) == cudaSuccess;
+    ok = ok && cudaGetSymbolAddress((void**)&sc.matrices, g_matrices) == cudaSuccess;
     ok = ok && cudaGetSymbolAddress((void**)&sc.sched, g_sched) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) cudaGetLastError();
@@ -1278,6 +1308,7 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   a.n_items = (int)items;
   if (!a.h_out && (size_t)a.B * a.D * a.N > kHandoffFloats) return false;
   if (kNorm && (size_t)a.B * a.D * 2 > kHandoffStats) return false;
+  if ((size_t)a.tiles_d * (C::kOffKp - C::kOffT) > kMatrixBytes) return false;
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
     cudaGetLastError();
@@ -1286,12 +1317,14 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   CUtensorMap tx, ty;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
   if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, true, false, 1, false, false, true>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, true, false, 1, false, false, kNorm ? 3 : 1>;
+  auto builder = tsn_ema_mma_kernel<kNorm, kCg, false, 1, false, true, false, 1, false, false, 2>;
   std::lock_guard<std::mutex> lock(g_seg_mutex);
   SegScratch* sc = seg_scratch();
   if (sc == nullptr) return false;
   a.handoff_h = sc->handoff;
   a.handoff_s = sc->stats;
+  a.matrices = sc->matrices;
   a.sched = sc->sched;
   if (sc->used && sc->last != s && cudaStreamWaitEvent(s, sc->done, 0) != cudaSuccess) {
     cudaGetLastError();
@@ -1301,6 +1334,7 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
     cudaGetLastError();
     return false;
   }
+  if (!kNorm) launch(builder, dim3((unsigned)a.tiles_d), dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, ty, a);
   launch(kern, dim3((unsigned)a.n_items), dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, ty, a);
   cudaEventRecord(sc->done, s);
   sc->last = s;

@@ -28,6 +28,7 @@ struct StreamArgs {
   int n_seg, seg_steps, n_items, tiles_d;
   float* handoff_h;  // pole states between the runs of a strip, laid out like h_out
   float* handoff_s;  // running sum and squared deviations (B, D, 2) between the runs
+  unsigned char* matrices;  // per tile of channels: the tile's matrices as the kernel holds them in shared memory
   int* sched;        // [0]: next work item; [1 + item]: set once the item's statistics and states are written
 };
 
