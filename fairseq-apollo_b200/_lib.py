@@ -29,6 +29,8 @@ SIGNATURES = {
                                c_i, c_d, c_p, c_p, c_p, c_p],
     "mega_tsn_ema_fwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
                          c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_u, c_p],
+    "mega_tsn_ema_fwd_runs": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
+                              c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_u, c_i, c_p],
     "mega_sqn_ema_fwd": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_d, c_p, c_p, c_p,
                          c_p, c_p, c_p, c_p, c_i, c_p, c_u, c_p],
     "mega_tsn_ema_step": [c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_d, c_p, c_p, c_p, c_p, c_i,

@@ -381,6 +381,33 @@ extern "C" MEGA_API int mega_tsn_ema_step(const void* x, void* y, void* xn_out, 
   return check_launch("tsn_ema_step");
 }
 
+extern "C" int mega_tsn_ema_fwd_runs(const void* x, void* y, int dtype, int B, int L, int D, int64_t xsb, int64_t xsl,
+                                     int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd, const int64_t* prev_count,
+                                     const float* prev_mean, const float* prev_var, const float* gamma,
+                                     const float* beta, double eps, int64_t* count_out, float* mean_out,
+                                     float* var_out, const float* p, const float* q, const float* gamma_hat,
+                                     const float* omega, int N, const float* h_in, float* h_out, unsigned flags,
+                                     int runs, mega_stream_t stream) {
+  if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
+      !var_out || !p || !q || !gamma_hat || !omega)
+    return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
+  if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
+  if (flags & MEGA_EMA_BIDIRECTIONAL) return MEGA_ERR_UNSUPPORTED;
+  if (runs != 2 && runs != 4 && runs != 8) return MEGA_ERR_SHAPE;
+  if (!aligned_to(x, elem_size(dtype)) || !aligned_to(y, elem_size(dtype))) return MEGA_ERR_ALIGN;
+  StreamArgs sa{};
+  sa.B = B; sa.L = L; sa.D = D; sa.N = N;
+  sa.prev_count = (const long long*)prev_count; sa.prev_mean = prev_mean; sa.prev_var = prev_var; sa.gamma = gamma;
+  sa.beta = beta; sa.eps = (float)eps; sa.count_out = (long long*)count_out; sa.mean_out = mean_out;
+  sa.var_out = var_out; sa.p = p; sa.q = q; sa.g = gamma_hat; sa.omega = omega; sa.h_in = h_in; sa.h_out = h_out;
+  sa.silu = (flags & MEGA_EMA_SILU) ? 1 : 0;
+  if (!mma_cl_runs(dtype, x, y, xsb, xsl, xsd, ysb, ysl, ysd, sa, runs, (cudaStream_t)stream))
+    return MEGA_ERR_UNSUPPORTED;
+  return check_launch("tsn_ema_fwd_runs");
+}
+
 extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, int B, int L, int D,
                                 int64_t xsb, int64_t xsl, int64_t xsd, int64_t ysb, int64_t ysl, int64_t ysd,
                                 const int64_t* prev_count, const float* prev_mean, const float* prev_var,

@@ -1254,10 +1254,10 @@ constexpr size_t kHandoffFloats = size_t(4) << 20;  // 16 MiB: pole states of B 
 constexpr size_t kHandoffStats = size_t(512) << 10;  // 2 MiB: running sums (two values) of B x D <= 256 Ki channels
 constexpr size_t kMatrixBytes = size_t(12) << 20;   // 12 MiB: the matrices of 144 tiles of 64 channels
 constexpr int kSchedItems = 16384;
-__device__ __align__(256) unsigned char g_matrices[kMatrixBytes];
-__device__ __align__(256) float g_handoff[kHandoffFloats];
-__device__ __align__(256) float g_handoff_stats[kHandoffStats];
-__device__ __align__(256) int g_sched[1 + kSchedItems];
+static __device__ __align__(256) unsigned char g_matrices[kMatrixBytes];
+static __device__ __align__(256) float g_handoff[kHandoffFloats];
+static __device__ __align__(256) float g_handoff_stats[kHandoffStats];
+static __device__ __align__(256) int g_sched[1 + kSchedItems];
 
 struct SegScratch {
   bool tried = false, ok = false;
@@ -1265,15 +1265,17 @@ struct SegScratch {
   float* stats = nullptr;
   unsigned char* matrices = nullptr;
   int* sched = nullptr;
-  cudaEvent_t done = nullptr;
+  bool ev_tried = false;
+  cudaEvent_t done = nullptr;   // made on first use by a caller that orders its calls across streams
   cudaStream_t last = nullptr;
   bool used = false;
 };
 static std::mutex g_seg_mutex;
 static SegScratch g_seg[16];
 
-// (g_seg_mutex held) scratch of the current device, or nullptr
-static SegScratch* seg_scratch() {
+// (g_seg_mutex held) scratch of the current device, or nullptr; with_event: also the event that orders
+// calls on different streams
+static SegScratch* seg_scratch(bool with_event) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
   SegScratch& sc = g_seg[dev];
@@ -1283,18 +1285,28 @@ static SegScratch* seg_scratch() {
     ok = ok && cudaGetSymbolAddress((void**)&sc.stats, g_handoff_stats) == cudaSuccess;
     ok = ok && cudaGetSymbolAddress((void**)&sc.matrices, g_matrices) == cudaSuccess;
     ok = ok && cudaGetSymbolAddress((void**)&sc.sched, g_sched) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) cudaGetLastError();
     sc.ok = ok;
   }
+  if (sc.ok && with_event && !sc.ev_tried) {
+    sc.ev_tried = true;
+    if (cudaEventCreateWithFlags(&sc.done, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      sc.done = nullptr;
+    }
+  }
+  if (with_event && sc.done == nullptr) return nullptr;
   return sc.ok ? &sc : nullptr;
 }
 
 // Runs the call as n_seg runs per strip, one CTA per (run, tile, group of sequences).  False (nothing launched) when the
 // call does not fit the scratch, the stream is being captured, or the set-up failed.
+// order_streams: a call on another stream than the scratch's last user first waits for that one's event
+// (the automatic path); without it the caller keeps calls that use the scratch from overlapping.
 template <bool kNorm, bool kSilu>
 static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
-                             long long ysl, const StreamArgs& a_in, int n_seg, cudaStream_t s) {
+                             long long ysl, const StreamArgs& a_in, int n_seg, cudaStream_t s,
+                             bool order_streams = true) {
   constexpr int kCg = 8;
   using C = Cfg<kCg, false, false, 1, 1, false>;
   StreamArgs a = a_in;
@@ -1320,13 +1332,13 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, true, false, 1, false, false, kNorm ? 3 : 1>;
   auto builder = tsn_ema_mma_kernel<kNorm, kCg, false, 1, false, true, false, 1, false, false, 2>;
   std::lock_guard<std::mutex> lock(g_seg_mutex);
-  SegScratch* sc = seg_scratch();
+  SegScratch* sc = seg_scratch(order_streams);
   if (sc == nullptr) return false;
   a.handoff_h = sc->handoff;
   a.handoff_s = sc->stats;
   a.matrices = sc->matrices;
   a.sched = sc->sched;
-  if (sc->used && sc->last != s && cudaStreamWaitEvent(s, sc->done, 0) != cudaSuccess) {
+  if (order_streams && sc->used && sc->last != s && cudaStreamWaitEvent(s, sc->done, 0) != cudaSuccess) {
     cudaGetLastError();
     return false;
   }
@@ -1336,9 +1348,11 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   }
   if (!kNorm) launch(builder, dim3((unsigned)a.tiles_d), dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, ty, a);
   launch(kern, dim3((unsigned)a.n_items), dim3(kCg * 32), (size_t)C::kSmemBytes, (void*)s, tx, ty, ty, a);
-  cudaEventRecord(sc->done, s);
-  sc->last = s;
-  sc->used = true;
+  if (order_streams) {
+    cudaEventRecord(sc->done, s);
+    sc->last = s;
+    sc->used = true;
+  }
   static const std::string base = std::string("tsn_ema_mma tile=8 warps_per_column=1 pipe=1") + (kNorm ? " norm" : "") + " ema segmented runs=";
   static const std::string names[3] = {base + "2", base + "4", base + "8"};
   g_last_kernel.store(names[n_seg == 2 ? 0 : n_seg == 4 ? 1 : 2].c_str(), std::memory_order_relaxed);
@@ -1510,6 +1524,22 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   if (norm) return a_in.silu ? MEGA_MMA_VARIANT(true, true) : MEGA_MMA_VARIANT(true, false);
   return a_in.silu ? MEGA_MMA_VARIANT(false, true) : MEGA_MMA_VARIANT(false, false);
 #undef MEGA_MMA_VARIANT
+}
+
+// The segmented form on request (mega_tsn_ema_fwd_runs): the normalising kernel in `runs` runs or
+// nothing.  Uses only the fixed device arrays above (no event either).
+bool mma_cl_runs(int dtype, const void* x, void* y, long long xsb, long long xsl, long long xsd, long long ysb,
+                 long long ysl, long long ysd, const StreamArgs& a_arg, int runs, cudaStream_t s) {
+  if (dtype != MEGA_BF16 || xsd != 1 || ysd != 1) return false;
+  if (a_arg.mask != nullptr || a_arg.cplx || a_arg.N < 1 || a_arg.N > 16 || a_arg.B < 4 || a_arg.L >= (1 << 24) ||
+      a_arg.D < 8 || (a_arg.L % kStep) != 0 || (a_arg.B + kSeq - 1) / kSeq > 65535)
+    return false;
+  StreamArgs a = a_arg;
+  const int lim = g_options[OPT_WAIT_LIMIT].load();
+  a.wait_limit = lim > 0 ? (long long)lim : 4000000000LL;
+  a.withhold_step = -1;
+  return a.silu ? launch_segmented<true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a, runs, s, false)
+                : launch_segmented<true, false>(dtype, x, y, xsb, xsl, ysb, ysl, a, runs, s, false);
 }
 
 cudaError_t mma_cl_read_device_error(int* v, bool reset) { return read_device_error(v, reset); }

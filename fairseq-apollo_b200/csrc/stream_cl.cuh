@@ -43,6 +43,10 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
 // no normalised-copy output, at least 4 sequences.  Same contract as stream_cl_try.
 bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
                 long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a, cudaStream_t s);
+// The segmented form of the tensor-core path with the given number of runs (2, 4 or 8), or false
+// (nothing launched) when the call is outside its envelope or its scratch.
+bool mma_cl_runs(int dtype, const void* x, void* y, long long xsb, long long xsl, long long xsd, long long ysb,
+                 long long ysl, long long ysd, const StreamArgs& a, int runs, cudaStream_t s);
 cudaError_t mma_cl_read_device_error(int* v, bool reset);
 
 }  // namespace mega

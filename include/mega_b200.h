@@ -201,6 +201,30 @@ MEGA_API int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype, i
                      unsigned flags, mega_stream_t stream);
 
 /*
+ * mega_tsn_ema_fwd in its segmented form, on request: the sequence is cut into `runs` (2, 4 or 8) runs,
+ * one thread block per run and tile of 64 channels x 8 sequences; a run starts from the running sums
+ * and pole states that the run before left in device memory.  Same arguments, meaning and results
+ * (bit for bit) as mega_tsn_ema_fwd without xn_out and pad_mask; bf16, channel strides 1, L a
+ * multiple of 32 x runs, B >= 4, N <= 16.
+ * No counterpart in the reference (a scheduling variant of this library's own kernel).
+ * Allocates nothing: its scratch (hand-off of the states, work counter and flags) are fixed arrays
+ * in device memory owned by the library: 16 MiB of pole states (B x D x N <= 4 Mi values, unused
+ * when h_out is given), 2 MiB of running sums (B x D <= 256 Ki) and 16384 work items; a call
+ * beyond these, or outside the envelope above, returns MEGA_ERR_UNSUPPORTED and launches nothing.
+ * The arrays are shared by every call on the device (mega_tsn_ema_fwd may use them too for large
+ * problems): calls that use them must not overlap in time, whatever their streams; this entry
+ * point does not order them.  The counter and flags are cleared on the stream before each launch.
+ */
+MEGA_API int mega_tsn_ema_fwd_runs(const void* x, void* y, int dtype, int B, int L, int D,
+                     int64_t x_stride_b, int64_t x_stride_l, int64_t x_stride_d,
+                     int64_t y_stride_b, int64_t y_stride_l, int64_t y_stride_d,
+                     const int64_t* prev_count, const float* prev_mean, const float* prev_var,
+                     const float* gamma, const float* beta, double eps,
+                     int64_t* count_out, float* mean_out, float* var_out,
+                     const float* p, const float* q, const float* gamma_hat, const float* omega, int N,
+                     const float* h_in, float* h_out, unsigned flags, int runs, mega_stream_t stream);
+
+/*
  * Fused per-channel SequenceNorm -> EMA (causal or bidirectional) on length-contiguous rows:
  * x, y (B,D,L) with stride_l == 1.  norm_gamma is the EFFECTIVE scale (module weight + 1).
  * count_out (B), mean_out / rstd_out (B,D) may be NULL.  flags as in mega_ema_fwd.  Returns
