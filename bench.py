@@ -263,11 +263,11 @@ def job_throughput(tokens_per_rank, world, steps, total_ms):
     return tokens_per_rank * world * steps / (total_ms * 1e-3)
 
 
-# DRAM bytes per token of the tensor-core kernel (56-channel tile, TimestepNorm -> EMA), from an ncu capture
-# of one launch of the current kernel at B=32, L=4096, D=2048: dram__bytes_read.sum 539.26 MB +
-# dram__bytes_write.sum 490.85 MB for 32 x 4096 tokens (0.96 of the algorithmic 8192 B per token: the tail of
-# the output is still in L2 when the kernel ends).  The traffic grows with the tokens of a launch.
-NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = (539.26e6 + 490.85e6) / (32 * 4096)
+# DRAM bytes per token of the tensor-core kernel (segmented 64-channel form, TimestepNorm -> EMA), from an ncu
+# capture of one launch of the current kernel at B=40, L=8192, D=2048: dram__bytes_read.sum 1355.64 MB +
+# dram__bytes_write.sum 1330.40 MB for 40 x 8192 tokens (1.0006 of the algorithmic 8192 B per token).  The
+# traffic grows with the tokens of a launch.
+NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = (1355.64e6 + 1330.40e6) / (40 * 8192)
 
 
 def workload_name(args, B, L, D, dtype_name):
@@ -498,7 +498,7 @@ def run_ours(args, B, L, D, dtype_name):
                          "traffic": (NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 * Bl * L
                                      if (D == 2048 and dtype_name == "bf16") else None),
                          "traffic_note": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
-                                         "kernel at B=32, L=4096, D=2048, scaled by the tokens of a launch",
+                                         "kernel at B=40, L=8192, D=2048, scaled by the tokens of a launch",
                          "peak_kind": peak_kind,
                          "kernel": kernel_name, "algorithmic_bytes_per_launch": alg_bytes,
                          "kernel_ms": kern_ms},
