@@ -268,6 +268,10 @@ def job_throughput(tokens_per_rank, world, steps, total_ms):
 # dram__bytes_write.sum 1330.40 MB for 40 x 8192 tokens (1.0006 of the algorithmic 8192 B per token).  The
 # traffic grows with the tokens of a launch.
 NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 = (1355.64e6 + 1330.40e6) / (40 * 8192)
+# The unsegmented 56-channel form (what a shard of 32 sequences or fewer runs), captured at B=32, L=4096, D=2048:
+# 539.26 MB + 490.85 MB for 32 x 4096 tokens (0.96 of the algorithmic bytes: the tail of the output is still in
+# L2 when the kernel ends).
+NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16_PLAIN = (539.26e6 + 490.85e6) / (32 * 4096)
 
 
 def workload_name(args, B, L, D, dtype_name):
@@ -495,10 +499,12 @@ def run_ours(args, B, L, D, dtype_name):
                        % (Bl * L * D * es / 2**30), "parallelism": "batch shards, no data-path collective"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
-                         "traffic": (NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 * Bl * L
+                         "traffic": ((NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16 if "segmented" in kernel_name
+                                      else NCU_DRAM_BYTES_PER_TOKEN_D2048_BF16_PLAIN) * Bl * L
                                      if (D == 2048 and dtype_name == "bf16") else None),
                          "traffic_note": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
-                                         "kernel at B=40, L=8192, D=2048, scaled by the tokens of a launch",
+                                         "kernel form (segmented: at B=40, L=8192; unsegmented: at B=32, L=4096; "
+                                         "D=2048), scaled by the tokens of a launch",
                          "peak_kind": peak_kind,
                          "kernel": kernel_name, "algorithmic_bytes_per_launch": alg_bytes,
                          "kernel_ms": kern_ms},
