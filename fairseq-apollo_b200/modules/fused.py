@@ -98,6 +98,8 @@ def _fp32_params(norm: TimestepNorm, move: MultiHeadEMA):
     return cache[1:7]
 
 
+_current_device = getattr(torch._C, "_cuda_getDevice", torch.cuda.current_device)
+
 try:   # the raw handle of the current stream without building a torch.cuda.Stream object
     _raw_stream = torch._C._cuda_getCurrentRawStream
 except AttributeError:   # pragma: no cover - older / newer torch
@@ -109,76 +111,111 @@ class _StepPlan:
     """Everything a single-token step passes to the C entry point, converted once: the ctypes
     argument list with the pointers of the parameters and of the running state, and a second count
     array (the step writes the bumped counts there from its one launch; the two arrays alternate).
-    Valid for as long as the state tensors, the batch size, the dtype and the options stay the same
-    (``key``); the caller rebuilds it otherwise (new generation, reordered beams, ...)."""
+    Valid for as long as the parameters (identity and version counters), the state tensors, the batch
+    size, the dtype and the options stay the same; the caller rebuilds it otherwise (new generation,
+    reordered beams, an optimiser step, ...)."""
 
-    __slots__ = ("key", "fn", "args", "count_ptr", "count_alt", "keep")
+    __slots__ = ("key", "fn", "args", "count_ptr", "count_cur", "count_alt", "keep", "params", "pver", "nkey", "ekey",
+                 "dev")
 
-    def __init__(self, key, fn, args, count_ptr, count_alt, keep):
-        self.key, self.fn, self.args, self.count_ptr, self.count_alt, self.keep = key, fn, args, count_ptr, count_alt, keep
+    def __init__(self, key, fn, args, count_cur, count_alt, keep, params, pver, nkey, ekey, dev):
+        self.key, self.fn, self.args, self.count_cur, self.count_alt, self.keep = key, fn, args, count_cur, count_alt, keep
+        self.count_ptr = count_cur.data_ptr()
+        self.params, self.pver, self.nkey, self.ekey, self.dev = params, pver, nkey, ekey, dev
 
 
-def _decode_step(norm, move, x, incremental_state, activation, return_normed):
+def _param_tensors(norm, move):
+    """The seven parameter tensors the step depends on, fetched from the modules' parameter dicts
+    (several times cheaper than attribute access through nn.Module.__getattr__)."""
+    np_, mp_ = norm._parameters, move._parameters
+    return (np_['weight'], np_['bias'], mp_['alpha'], mp_['delta'], mp_['theta' if move.complex else 'beta'],
+            mp_['gamma'], mp_['omega'])
+
+
+def _decode_step(norm, move, x, incremental_state, activation, return_normed, _fresh_plan=False):
     """Single-token step (x: (B, 1, D)): one fused kernel, one launch, running state updated in place."""
+    plan = move.__dict__.get("_step_plan")
+    if plan is not None:
+        nstate = incremental_state.get(plan.nkey)
+        estate = incremental_state.get(plan.ekey)
+        if nstate is not None and estate is not None:
+            count, mean, var, h = nstate.get('prev_count'), nstate.get('prev_mean'), nstate.get('prev_var'), \
+                estate.get('prev_state')
+            ps = _param_tensors(norm, move)
+            pp = plan.params
+            if (mean is not None and h is not None and ps[0] is pp[0] and ps[1] is pp[1] and ps[2] is pp[2]
+                    and ps[3] is pp[3] and ps[4] is pp[4] and ps[5] is pp[5] and ps[6] is pp[6]
+                    and (ps[0]._version, ps[1]._version, ps[2]._version, ps[3]._version, ps[4]._version,
+                         ps[5]._version, ps[6]._version) == plan.pver
+                    and mean is plan.keep[6] and var is plan.keep[7] and h is plan.keep[8] and count is plan.count_cur
+                    and plan.key == (x.shape[0], x.dtype, activation, return_normed, x.device.index)):
+                args = plan.args
+                y = torch.empty_like(x)
+                args[0].value = x.data_ptr()
+                args[1].value = y.data_ptr()
+                xn = None
+                if return_normed:
+                    xn = torch.empty_like(x)
+                    args[2].value = xn.data_ptr()
+                # counts: read from the state's array, written to the other one, which becomes the state's
+                alt = plan.count_alt
+                args[6].value = plan.count_ptr
+                args[7].value = alt.data_ptr()
+                args[20].value = _raw_stream(plan.dev)
+                if _current_device() == plan.dev:
+                    rc = plan.fn(*args)
+                else:
+                    with torch.cuda.device(plan.dev):
+                        rc = plan.fn(*args)
+                if rc != 0:
+                    from .. import _lib
+                    _lib.check(rc, "tsn_ema_step")
+                nstate['prev_count'] = alt
+                plan.count_alt, plan.count_cur, plan.count_ptr = count, alt, args[7].value
+                return (y, xn) if return_normed else y
+    if _fresh_plan:
+        raise RuntimeError("single-token step: a freshly built plan does not match its own inputs")
+    return _decode_step_plan(norm, move, x, incremental_state, activation, return_normed)
+
+
+def _decode_step_plan(norm, move, x, incremental_state, activation, return_normed):
+    """Builds (or rebuilds) the plan of the single-token step, then takes the step through it."""
     import ctypes
     from .. import _lib
     bsz, _, dim = x.shape
-    nstate = incremental_state.get(norm._state_key) if hasattr(norm, "_state_key") else None
-    if nstate is None:
-        norm._state_key = norm._get_full_incremental_state_key("norm_state")
-        move._state_key = move._get_full_incremental_state_key("ema_state")
-        nstate = incremental_state.get(norm._state_key)
-    estate = incremental_state.get(move._state_key)
+    nkey = norm._get_full_incremental_state_key("norm_state")
+    ekey = move._get_full_incremental_state_key("ema_state")
+    nstate = incremental_state.get(nkey)
+    estate = incremental_state.get(ekey)
     if nstate is None or estate is None or 'prev_mean' not in nstate or estate.get('prev_state') is None:
         nstate, estate = _seed_decode_state(norm, move, bsz, dim, x.device, incremental_state)
     count, mean, var, h = nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'], estate['prev_state']
+    sdtype = torch.complex64 if move.complex else torch.float32
+    if (mean.dtype != torch.float32 or not mean.is_contiguous() or var.dtype != torch.float32
+            or not var.is_contiguous() or h.dtype != sdtype or not h.is_contiguous()
+            or count.dtype != torch.int64 or not count.is_contiguous()):
+        nstate['prev_mean'], nstate['prev_var'] = mean.float().contiguous(), var.float().contiguous()
+        nstate['prev_count'] = count.long().contiguous()
+        estate['prev_state'] = h.to(sdtype).contiguous()
+        count, mean, var, h = nstate['prev_count'], nstate['prev_mean'], nstate['prev_var'], estate['prev_state']
     gamma, beta, p, q, g, omega = _fp32_params(norm, move)
-    key = (mean.data_ptr(), var.data_ptr(), h.data_ptr(), gamma.data_ptr(), bsz, x.dtype, activation, return_normed)
-    plan = getattr(move, "_step_plan", None)
-    if plan is None or plan.key != key or plan.count_ptr != count.data_ptr():
-        sdtype = torch.complex64 if move.complex else torch.float32
-        if (mean.dtype != torch.float32 or not mean.is_contiguous() or var.dtype != torch.float32
-                or not var.is_contiguous() or h.dtype != sdtype or not h.is_contiguous()
-                or count.dtype != torch.int64 or not count.is_contiguous()):
-            nstate['prev_mean'], nstate['prev_var'] = mean.float().contiguous(), var.float().contiguous()
-            nstate['prev_count'] = count.long().contiguous()
-            estate['prev_state'] = h.to(sdtype).contiguous()
-            return _decode_step(norm, move, x, incremental_state, activation, return_normed)
-        lib = _lib.lib()
-        fn = lib.mega_tsn_cema_step if move.complex else lib.mega_tsn_ema_step
-        vp, ci = ctypes.c_void_p, ctypes.c_int
-        count_alt = torch.empty_like(count)
-        # x, y, xn_out, dtype, B, D, count, count_next, mean, var, gamma, beta, eps, p, q, g, omega, N, h, flags, stream
-        args = [vp(0), vp(0), vp(None), ci(ops._dt(x)), ci(bsz), ci(dim), vp(count.data_ptr()),
-                vp(count_alt.data_ptr()), vp(mean.data_ptr()), vp(var.data_ptr()), vp(gamma.data_ptr()),
-                vp(beta.data_ptr()), ctypes.c_double(norm.eps), vp(p.data_ptr()), vp(q.data_ptr()), vp(g.data_ptr()),
-                vp(omega.data_ptr()), ci(p.shape[1]), vp(h.data_ptr()),
-                ctypes.c_uint(ops.EMA_SILU if activation == 'silu' else 0), vp(0)]
-        plan = _StepPlan(key, fn, args, count.data_ptr(), count_alt, (gamma, beta, p, q, g, omega, mean, var, h))
-        move._step_plan = plan
-    args = plan.args
-    y = torch.empty_like(x)
-    args[0].value = x.data_ptr()
-    args[1].value = y.data_ptr()
-    xn = None
-    if return_normed:
-        xn = torch.empty_like(x)
-        args[2].value = xn.data_ptr()
-    # counts: read from the state's array, written to the other one, which becomes the state's
-    alt = plan.count_alt
-    args[6].value = count.data_ptr()
-    args[7].value = alt.data_ptr()
-    args[20].value = _raw_stream(x.device.index)
-    if torch.cuda.current_device() == x.device.index:
-        rc = plan.fn(*args)
-    else:
-        with torch.cuda.device(x.device):
-            rc = plan.fn(*args)
-    if rc != 0:
-        _lib.check(rc, "tsn_ema_step")
-    nstate['prev_count'] = alt
-    plan.count_alt, plan.count_ptr = count, alt.data_ptr()
-    return (y, xn) if return_normed else y
+    params = _param_tensors(norm, move)
+    pver = tuple(t._version for t in params)
+    # (the state tensors themselves are compared by identity: keep[6:9] and count_cur)
+    key = (bsz, x.dtype, activation, return_normed, x.device.index)
+    lib = _lib.lib()
+    fn = lib.mega_tsn_cema_step if move.complex else lib.mega_tsn_ema_step
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    count_alt = torch.empty_like(count)
+    # x, y, xn_out, dtype, B, D, count, count_next, mean, var, gamma, beta, eps, p, q, g, omega, N, h, flags, stream
+    args = [vp(0), vp(0), vp(None), ci(ops._dt(x)), ci(bsz), ci(dim), vp(count.data_ptr()),
+            vp(count_alt.data_ptr()), vp(mean.data_ptr()), vp(var.data_ptr()), vp(gamma.data_ptr()),
+            vp(beta.data_ptr()), ctypes.c_double(norm.eps), vp(p.data_ptr()), vp(q.data_ptr()), vp(g.data_ptr()),
+            vp(omega.data_ptr()), ci(p.shape[1]), vp(h.data_ptr()),
+            ctypes.c_uint(ops.EMA_SILU if activation == 'silu' else 0), vp(0)]
+    move._step_plan = _StepPlan(key, fn, args, count, count_alt, (gamma, beta, p, q, g, omega, mean, var, h),
+                                params, pver, nkey, ekey, x.device.index)
+    return _decode_step(norm, move, x, incremental_state, activation, return_normed, _fresh_plan=True)
 
 
 def _seed_decode_state(norm, move, bsz, dim, device, incremental_state):
