@@ -56,7 +56,9 @@ def test_tsn_grid(bsz, length, feat, groups, dtype):
                                                 gamma.cuda(), beta.cuda(), mask.cuda(), 1e-5, groups)
     assert torch.equal(cnt.cpu(), ref[1])
     assert rel_l2(y.float(), ref[0]) < TOL[dtype]
-    assert rel_l2(mean, ref[2]) < 1e-5 and rel_l2(var, ref[3]) < 1e-5
+    # (bf16 with at least 4 sequences and 8-aligned features runs the tensor-core kernel, whose sums of
+    # squares go through tf32 MMAs: ~2^-11 of the variance)
+    assert rel_l2(mean, ref[2]) < 1e-5 and rel_l2(var, ref[3]) < (1e-3 if dtype == torch.bfloat16 else 1e-5)
     assert (y.cpu()[mask] == 0).all()
 
 
