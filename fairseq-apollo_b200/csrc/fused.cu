@@ -391,6 +391,8 @@ extern "C" int mega_tsn_ema_fwd_runs(const void* x, void* y, int dtype, int B, i
   if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
       !var_out || !p || !q || !gamma_hat || !omega)
     return MEGA_ERR_NULL;
+  // every thread block of a sequence reads its incoming count; one of them writes the new one
+  if ((const void*)count_out == (const void*)prev_count) return MEGA_ERR_UNSUPPORTED;
   if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
   if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;
@@ -418,6 +420,8 @@ extern "C" int mega_tsn_ema_fwd(const void* x, void* y, void* xn_out, int dtype,
   if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
       !var_out || !p || !q || !gamma_hat || !omega)
     return MEGA_ERR_NULL;
+  // every thread block of a sequence reads its incoming count; one of them writes the new one
+  if ((const void*)count_out == (const void*)prev_count) return MEGA_ERR_UNSUPPORTED;
   if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
   if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
   if (N < 1 || N > MEGA_MAX_NDIM) return MEGA_ERR_NDIM;

@@ -344,6 +344,8 @@ static int tsn_fwd_common(const void* x, void* y, int dtype, int B, int L, int D
   if (!x || !y || !prev_count || !prev_mean || !prev_var || !gamma || !beta || !count_out || !mean_out ||
       !var_out)
     return MEGA_ERR_NULL;
+  // every thread block of a sequence reads its incoming count; one of them writes the new one
+  if ((const void*)count_out == (const void*)prev_count) return MEGA_ERR_UNSUPPORTED;
   if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
   if (B <= 0 || L <= 0 || D <= 0) return MEGA_ERR_SHAPE;
   const int G = (num_groups <= 0 || num_groups == D) ? D : num_groups;

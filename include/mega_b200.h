@@ -151,7 +151,9 @@ MEGA_API int mega_ema_step(const void* x, void* y, int dtype, int B, int D,
  * TimestepNorm forward.  x, y (B,L,D) by strides.  prev_count (B) int64, prev_mean/prev_var
  * (B,G) fp32 with G = D for num_groups <= 0 or == D, else num_groups.  gamma is the EFFECTIVE
  * scale (module weight + 1), beta the bias, both (D) fp32.  Outputs count_out (B) int64,
- * mean_out/var_out (B,G) fp32 (may alias the prev_* arrays).  Padded steps output 0 and do not
+ * mean_out/var_out (B,G) fp32 (may alias prev_mean/prev_var; count_out must be a different array
+ * than prev_count, MEGA_ERR_UNSUPPORTED otherwise: every thread block of a sequence reads the incoming
+ * count).  The same holds for the fused entry points below.  Padded steps output 0 and do not
  * advance the statistics.
  * Replaces: timestep_norm_fwd / group_timestep_norm_fwd (fairseq/csrc/ops/timestep_norm.cc:23-103,
  * 218-316; CUDA fairseq/csrc/ops/timestep_norm_kernel.cu:26-185,269-484) minus the cummean/cumrstd

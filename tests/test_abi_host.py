@@ -48,7 +48,12 @@ def test_argument_rejection_without_gpu():
     assert lib.mega_ema_fwd(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, 16, None, one, None, 1, 0, None) == 7
     assert lib.mega_ema_fwd(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, 16, None, None, None, 0, 4, None) == 7
     # groups must divide features
-    assert lib.mega_timestep_norm_fwd(one, one, 0, 1, 1, 10, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 3, 1e-5, one, one, one, None) == 3
+    two = ctypes.c_void_p(32)
+    assert lib.mega_timestep_norm_fwd(one, one, 0, 1, 1, 10, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 3, 1e-5, two, one, one, None) == 3
+    # the new counts must not be written over the incoming ones (every thread block of a sequence reads them)
+    assert lib.mega_timestep_norm_fwd(one, one, 0, 1, 1, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, one, None, 8, 1e-5, one, one, one, None) == 7
+    assert lib.mega_tsn_ema_fwd(one, one, None, 1, 8, 64, 8, 1, 1, 1, 1, 1, 1, one, one, one, one, one, 1e-5, one, one, one,
+                                one, one, one, one, 16, None, None, None, 0, None) == 7
     assert lib.mega_sequence_norm_fwd(one, one, 0, 1, 10, 1, 1, 1, 1, 1, 1, 1, one, one, None, 3, 1e-5, one, one, one, None) == 3
     assert lib.mega_ema_step(one, one, 0, 1, 1, one, one, one, one, 16, None, None, 0, None) == 1
 
