@@ -358,15 +358,27 @@ __global__ void __launch_bounds__(256) gate_vec_kernel(const T* a, long long lda
       const unsigned v = v0 + u * stride;
       if (v < nvec) {
         float out[kN];
+        // 16-bit outputs: SiLU and the sigmoid from one tanh.approx each (relative error ~2^-11, below
+        // the rounding of the output); fp32 keeps the exponential forms
+        constexpr bool kFast = sizeof(T) == 2;
 #pragma unroll
         for (int k = 0; k < kN; ++k) {
           if (OP == 0) {  // silu(a [+ b])
-            out[k] = siluf_(b != nullptr ? fa[u][k] + fb[u][k] : fa[u][k]);
+            const float v = b != nullptr ? fa[u][k] + fb[u][k] : fa[u][k];
+            out[k] = kFast ? silu_tanh(v) : siluf_(v);
           } else if (OP == 1) {  // a * silu(b)
-            out[k] = fa[u][k] * siluf_(fb[u][k]);
+            out[k] = fa[u][k] * (kFast ? silu_tanh(fb[u][k]) : siluf_(fb[u][k]));
           } else {  // a = residual, b = u, c = hx, d = h_lin
-            const float g = sigmoidf_(fb[u][k]);
-            const float h = siluf_(fc[u][k] + fd[u][k]);
+            float g;
+            if (kFast) {
+              float t;
+              asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * fb[u][k]));
+              g = fmaf(0.5f, t, 0.5f);
+            } else {
+              g = sigmoidf_(fb[u][k]);
+            }
+            const float hs = fc[u][k] + fd[u][k];
+            const float h = kFast ? silu_tanh(hs) : siluf_(hs);
             out[k] = fmaf(g, h - fa[u][k], fa[u][k]);
           }
         }
