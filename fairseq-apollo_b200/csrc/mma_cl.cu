@@ -549,10 +549,15 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
     // the item of the run before (same tile and sequences) has written its statistics and states
     const int* flag = a.sched + 1 + ((int)ld_volatile_s(item_s) - a.n_items / a.n_seg);
     const long long start = clock64();
+    const int* gave_up = a.sched + 1 + a.n_items;   // set by a CTA of this launch whose wait ran out
     for (;;) {
       int v;
       asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
       if (v != 0) break;
+      if (*reinterpret_cast<const volatile int*>(gave_up) != 0) {  // the run before will never finish
+        st_volatile_s(abort_s, 1u);
+        break;
+      }
       if (clock64() - start > wait_limit) {
         g_device_error = 3;
         st_volatile_s(abort_s, 1u);
@@ -1138,7 +1143,11 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   }
   if (issuer) bulk_wait<0>();
   if (ld_volatile_s(abort_s) != 0) live = false;
-  if (!live) return;  // the error word is raised; the final statistics and states are not written
+  if (!live) {  // the error word is raised; the final statistics and states are not written
+    // (segmented: the runs that depend on this one learn of it instead of waiting out their limits)
+    if (kPs && lane == 0) *reinterpret_cast<volatile int*>(a.sched + 1 + a.n_items) = 1;
+    return;
+  }
 
   // ---- final statistics and states -------------------------------------------------------------
   if constexpr (kMail) {
@@ -1257,7 +1266,7 @@ constexpr int kSchedItems = 16384;
 static __device__ __align__(256) unsigned char g_matrices[kMatrixBytes];
 static __device__ __align__(256) float g_handoff[kHandoffFloats];
 static __device__ __align__(256) float g_handoff_stats[kHandoffStats];
-static __device__ __align__(256) int g_sched[1 + kSchedItems];
+static __device__ __align__(256) int g_sched[2 + kSchedItems];   // counter, one flag per item, "a wait ran out"
 
 struct SegScratch {
   bool tried = false, ok = false;
@@ -1342,7 +1351,7 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
     cudaGetLastError();
     return false;
   }
-  if (cudaMemsetAsync(sc->sched, 0, sizeof(int) * (size_t)(1 + a.n_items), s) != cudaSuccess) {
+  if (cudaMemsetAsync(sc->sched, 0, sizeof(int) * (size_t)(2 + a.n_items), s) != cudaSuccess) {
     cudaGetLastError();
     return false;
   }

@@ -29,7 +29,8 @@ struct StreamArgs {
   float* handoff_h;  // pole states between the runs of a strip, laid out like h_out
   float* handoff_s;  // running sum and squared deviations (B, D, 2) between the runs
   unsigned char* matrices;  // per tile of channels: the tile's matrices as the kernel holds them in shared memory
-  int* sched;        // [0]: next work item; [1 + item]: set once the item's statistics and states are written
+  int* sched;        // [0]: next work item; [1 + item]: set once the item's statistics and states are written;
+                     // [1 + n_items]: set when a wait of this launch ran out
 };
 
 // Tries the streamed TMA path for TimestepNorm (norm), causal EMA (ema) or both fused.  Returns

@@ -425,13 +425,14 @@ def test_segmented_form_falls_back():
     assert torch.isfinite(y.float()).all()
 
 
-@pytest.mark.parametrize("tile", [7, 22, 224])
+@pytest.mark.parametrize("tile", [7, 22, 224, 84])
 def test_bounded_wait_runs_out(tile):
     """A device-side wait that can never complete must give up, not hang: a test switch makes the
     kernel skip the TMA load of one step while its barrier keeps expecting the bytes, and shortens
     the wait limit to about a millisecond.  Every waiter of that stage gives up, all warps of the CTA
     leave the loop, the kernel returns without its final stores and the error word reads non-zero;
-    after a reset the next launch is clean and correct."""
+    after a reset the next launch is clean and correct.  Tile 84 is the segmented form: the run of the
+    withheld step gives up, and the run after it, which waits for that one's flag, leaves as well."""
     M, O = _mods()
     from fairseq_apollo_b200 import _lib
     gen = torch.Generator().manual_seed(5)
