@@ -1,5 +1,5 @@
-// Tensor-core variant of the fused TimestepNorm -> causal EMA (and of the EMA alone) for bf16
-// activations with contiguous channels and no padding mask.
+// Tensor-core variant of the fused TimestepNorm -> causal EMA (and of the EMA alone, and of
+// TimestepNorm alone) for bf16 activations with contiguous channels, with or without a padding mask.
 //
 // Work split.  A CTA owns kCg column groups (8 channels = 16 bytes each; kCg = 8, 7, 4 or 2) of 8
 // sequences and walks time in steps of 32 positions.  Warp w owns column group w (or, with two
@@ -31,7 +31,10 @@
 // the EMA (TimestepNorm alone); SiLU epilogue; one or two warps per 16-byte column; a second
 // output with the normalised activations (what the Mega block feeds its value projection);
 // complex poles (MultiHeadComplexEMA: P yields Re and Im of the local states, the carry is a
-// complex multiply by q^16, G takes Re(gamma q^(t+1)) against Re h and -Im(...) against Im h).
+// complex multiply by q^16, G takes Re(gamma q^(t+1)) against Re h and -Im(...) against Im h);
+// a padding mask; groups of warps pipelined along the sequence (problems with few strips); the
+// sequence cut into runs that separate CTAs take one after the other (problems of more than one
+// wave of CTAs).  Each is described at the kernel.
 #include <mutex>
 #include <string>
 #include <type_traits>
@@ -1370,10 +1373,10 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
 
 }  // namespace
 
-// Envelope: bf16, channel stride 1, no padding mask, ndim <= 16, a normalised-copy output (strided
-// like y) only together with the normalisation and distinct from x and y,
-// B >= 4 (rows of the MMAs are sequences), L < 2^24, and L a multiple of 32 when a state is
-// exported.  Returns false, launching nothing, outside of it.
+// Envelope: bf16, channel stride 1, ndim <= 16, a padding mask only with real poles, a
+// normalised-copy output (strided like y) only together with the normalisation and distinct from x
+// and y, B >= 4 (rows of the MMAs are sequences) unless the pipelined form applies, L < 2^24, and L
+// a multiple of 32 when a state is exported.  Returns false, launching nothing, outside of it.
 bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
                 long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a_arg, cudaStream_t s) {
   if (g_options[OPT_DISABLE_MMA].load() != 0) return false;

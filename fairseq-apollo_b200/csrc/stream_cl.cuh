@@ -40,8 +40,8 @@ bool stream_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, l
                    long long ysb, long long ysl, long long ysd, bool norm, bool ema, const StreamArgs& a,
                    cudaStream_t s);
 
-// Tries the tensor-core path (mma_cl.cu): bf16, channel stride 1, no padding mask, ndim <= 16,
-// no normalised-copy output, at least 4 sequences.  Same contract as stream_cl_try.
+// Tries the tensor-core path (mma_cl.cu): bf16, channel stride 1, ndim <= 16 (its envelope is
+// stated at the definition).  Same contract as stream_cl_try.
 bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long xsd,
                 long long ysb, long long ysl, long long ysd, bool norm, const StreamArgs& a, cudaStream_t s);
 // The segmented form of the tensor-core path with the given number of runs (2, 4 or 8), or false

@@ -76,7 +76,10 @@ MEGA_API uint64_t mega_launch_count(void);
 #define MEGA_OPT_DISABLE_STREAM 0
 #define MEGA_OPT_DISABLE_MMA 1 /* non-zero: skip the tensor-core kernels */
 #define MEGA_OPT_MMA_TILE 2    /* 2, 4, 7, 8: force 16-, 32-, 56-, 64-channel tensor-core tiles; 22: 16 channels
-                                  with two warps per 16-byte column; 0: automatic */
+                                  with two warps per 16-byte column; 222, 224, 422, 124: forms pipelined along the
+                                  sequence (channels / 8, warps per column, depth); 82, 84, 88: the segmented
+                                  64-channel form in 2, 4, 8 runs; 71: running state in shared memory;
+                                  0: automatic.  A form that does not apply to a call falls back to automatic */
 #define MEGA_OPT_WAIT_LIMIT 3    /* > 0: SM cycles after which a bounded device-side wait gives up (default ~2 s) */
 #define MEGA_OPT_WITHHOLD_LOAD 4 /* test aid, value k > 0: the tensor-core kernel never issues the TMA load of its
                                     step k (the barrier keeps expecting its bytes), so that every waiter of that
