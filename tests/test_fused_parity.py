@@ -407,6 +407,41 @@ def test_segmented_tensor_core_form(runs, bsz, length, dim, state):
     assert _lib.device_error() == 0
 
 
+def test_segmented_form_silu_and_fewer_poles():
+    """The segmented form with the SiLU epilogue, 8 poles instead of 16, a partial last tile of
+    channels and a partial group of sequences: the bits of the unsegmented form."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(77)
+    bsz, length, dim, ndim = 12, 1024, 136, 8
+    prm = make_ema_params(gen, dim, ndim)
+    x = (torch.randn(bsz, length, dim, generator=gen) * 0.9 + 0.2).to(torch.bfloat16).cuda()
+    pc = torch.full((bsz,), 2, dtype=torch.int64).cuda()
+    pm = (torch.randn(bsz, dim, generator=gen) * 0.1).cuda()
+    pv = (torch.rand(bsz, dim, generator=gen) + 0.5).cuda()
+    gamma = (torch.randn(dim, generator=gen) * 0.1 + 1).cuda()
+    beta = (torch.randn(dim, generator=gen) * 0.1).cuda()
+    p, q, g = M.ops.ema_coeffs(*[t.cuda() for t in prm[:4]])
+    res = {}
+    for t in (84, 8):
+        _lib.set_option(2, t)
+        try:
+            res[t] = M.ops.tsn_ema_forward(x, pc, pm, pv, gamma, beta, 1e-5, p, q, g, prm[4].cuda(), None,
+                                           want_state=True, silu=True)
+            name = _lib.last_kernel()
+        finally:
+            _lib.set_option(2, 0)
+        assert ("segmented runs=4" in name) == (t == 84), name
+    xn = O.timestep_norm(x.float().cpu(), pc.cpu(), pm.cpu(), pv.cpu(), gamma.cpu(), beta.cpu(), None,
+                         acc_dtype=torch.float64)[0]
+    yref, href = O.ema_forward_recurrence(xn.transpose(1, 2), *prm, None, silu=True, return_state=True)
+    assert rel_l2(res[84]["y"].float(), yref.transpose(1, 2)) < 1e-2
+    assert rel_l2(res[84]["h"], href) < 1e-2
+    for k in ("y", "h", "mean", "var", "count"):
+        assert torch.equal(res[84][k], res[8][k]), k
+    assert _lib.device_error() == 0
+
+
 def test_segmented_form_falls_back():
     """A number of steps that the runs do not divide takes the unsegmented kernel."""
     M, O = _mods()
