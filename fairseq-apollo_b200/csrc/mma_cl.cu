@@ -306,7 +306,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
   static_assert(kWp == 1 || (!kXn && !kCplx && kEma), "the pipelined form covers the real EMA without the second output");
   static_assert(!kMask || (kWp == 1 && !kCplx && !(kXn && !kNorm)), "masks: real poles, not pipelined");
   static_assert(!kSm || (kWp == 1 && !kXn && !kCplx && kEma && !kMask), "state in shared memory: the plain real form");
-  static_assert(!kPs || (kWp == 1 && kWs == 1 && !kXn && !kCplx && kEma && !kMask && !kSm), "segmented: the plain real form");
+  static_assert(!kPs || (kWp == 1 && kWs == 1 && !kXn && !kCplx && !kMask && !kSm), "segmented: the plain real form");
+  static_assert(kPs == 0 || kPs == 3 || kEma, "pre-built matrices exist for the EMA only");
 
   using C = Cfg<kCg, kXn, kCplx, kWs, kWp, kSm>;
   constexpr bool kMail = C::kMail;   // running quantities travel through / live in the mailboxes
@@ -628,7 +629,7 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
           const size_t c = (((size_t)bseq * a.D + d) * a.N + pole) * 2;
           hc[e][k] = have ? __ldg(a.h_in + c) : 0.f;
           hci[e][k] = have ? __ldg(a.h_in + c + 1) : 0.f;
-        } else if (kPs && seg > 0) {  // what the run before left (written by another SM: read past the L1)
+        } else if (kPs && kEma && seg > 0) {  // what the run before left (written by another SM: read past the L1)
           const float* hand = a.h_out ? a.h_out : a.handoff_h;
           hc[e][k] = (ok && pole < a.N) ? __ldcg(hand + ((size_t)bseq * a.D + d) * a.N + pole) : 0.f;
         } else {
@@ -1315,10 +1316,11 @@ static SegScratch* seg_scratch(bool with_event) {
 // call does not fit the scratch, the stream is being captured, or the set-up failed.
 // order_streams: a call on another stream than the scratch's last user first waits for that one's event
 // (the automatic path); without it the caller keeps calls that use the scratch from overlapping.
-template <bool kNorm, bool kSilu>
+template <bool kNorm, bool kSilu, bool kEma = true>
 static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb,
                              long long ysl, const StreamArgs& a_in, int n_seg, cudaStream_t s,
                              bool order_streams = true) {
+  static_assert(kEma || (kNorm && !kSilu), "without the EMA: TimestepNorm alone");
   constexpr int kCg = 8;
   using C = Cfg<kCg, false, false, 1, 1, false>;
   StreamArgs a = a_in;
@@ -1330,7 +1332,7 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   const long long items = (long long)a.tiles_d * ((a.B + kSeq - 1) / kSeq) * n_seg;
   if (items > kSchedItems) return false;
   a.n_items = (int)items;
-  if (!a.h_out && (size_t)a.B * a.D * a.N > kHandoffFloats) return false;
+  if (kEma && !a.h_out && (size_t)a.B * a.D * a.N > kHandoffFloats) return false;
   if (kNorm && (size_t)a.B * a.D * 2 > kHandoffStats) return false;
   if ((size_t)a.tiles_d * (C::kOffKp - C::kOffT) > kMatrixBytes) return false;
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
@@ -1341,8 +1343,8 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
   CUtensorMap tx, ty;
   if (!make_tensor_map_3d(&tx, dtype, x, a.D, a.L, a.B, xsl, xsb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
   if (!make_tensor_map_3d(&ty, dtype, y, a.D, a.L, a.B, ysl, ysb, C::kCh, kStep, kSeq, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
-  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, true, false, 1, false, false, kNorm ? 3 : 1>;
-  auto builder = tsn_ema_mma_kernel<kNorm, kCg, false, 1, false, true, false, 1, false, false, 2>;
+  auto kern = tsn_ema_mma_kernel<kNorm, kCg, kSilu, 1, false, kEma, false, 1, false, false, kNorm ? 3 : 1>;
+  auto builder = tsn_ema_mma_kernel<(kNorm && kEma), kCg, false, 1, false, true, false, 1, false, false, 2>;
   std::lock_guard<std::mutex> lock(g_seg_mutex);
   SegScratch* sc = seg_scratch(order_streams);
   if (sc == nullptr) return false;
@@ -1365,7 +1367,8 @@ static bool launch_segmented(int dtype, const void* x, void* y, long long xsb, l
     sc->last = s;
     sc->used = true;
   }
-  static const std::string base = std::string("tsn_ema_mma tile=8 warps_per_column=1 pipe=1") + (kNorm ? " norm" : "") + " ema segmented runs=";
+  static const std::string base = std::string("tsn_ema_mma tile=8 warps_per_column=1 pipe=1") + (kNorm ? " norm" : "") +
+                                  (kEma ? " ema" : "") + " segmented runs=";
   static const std::string names[3] = {base + "2", base + "4", base + "8"};
   g_last_kernel.store(names[n_seg == 2 ? 0 : n_seg == 4 ? 1 : 2].c_str(), std::memory_order_relaxed);
   return true;
@@ -1429,6 +1432,8 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
                            : (a_in.silu ? launch_segmented<false, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s)
                                         : launch_segmented<false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s));
       if (ok) return true;
+    } else if (!ema && norm && !masked && a_in.B >= 4) {  // TimestepNorm alone
+      if (launch_segmented<true, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, n_seg, s)) return true;
     }
   }
   // pipelined forms (real EMA, with or without the normalisation, no second output)
@@ -1508,6 +1513,22 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
   }
   if (!ema) {
     if (tile == 2 || tile == 4) tile = 22;
+    // more than one wave of wide tiles: the segmented form, as for the fused pair
+    if ((tile == 7 || tile == 8) && !masked && a_in.B >= 4 && ctas(64) > 148 && g_options[OPT_MMA_TILE].load() == 0) {
+      const int nsteps = (a_in.L + kStep - 1) / kStep;
+      const double plain = (double)((ctas(tile == 7 ? 56 : 64) + 147) / 148);
+      int best = 0;
+      double best_cost = plain * 0.96;
+      for (int n_seg = 2; n_seg <= 8; n_seg *= 2) {
+        if (nsteps % n_seg != 0 || nsteps / n_seg < 64) continue;
+        const double cost = (double)((ctas(64) * n_seg + 147) / 148) / n_seg * 1.02;
+        if (cost < best_cost) {
+          best_cost = cost;
+          best = n_seg;
+        }
+      }
+      if (best != 0 && launch_segmented<true, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, best, s)) return true;
+    }
     return tile == 22  ? launch_variant<true, 2, false, 2, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
            : tile == 7 ? launch_variant<true, 7, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
                        : launch_variant<true, 8, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);

@@ -442,6 +442,38 @@ def test_segmented_form_silu_and_fewer_poles():
     assert _lib.device_error() == 0
 
 
+def test_segmented_form_timestep_norm_alone():
+    """TimestepNorm alone (bf16, no mask) in the segmented form: the bits of the unsegmented form and the
+    oracle's values."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    gen = torch.Generator().manual_seed(78)
+    bsz, length, dim = 9, 2048, 200
+    x = (torch.randn(bsz, length, dim, generator=gen) * 1.4 - 0.3).to(torch.bfloat16).cuda()
+    pc = torch.full((bsz,), 4, dtype=torch.int64).cuda()
+    pm = (torch.randn(bsz, dim, generator=gen) * 0.1).cuda()
+    pv = (torch.rand(bsz, dim, generator=gen) + 0.5).cuda()
+    gamma = (torch.randn(dim, generator=gen) * 0.1 + 1).cuda()
+    beta = (torch.randn(dim, generator=gen) * 0.1).cuda()
+    res = {}
+    for t in (84, 8):
+        _lib.set_option(2, t)
+        try:
+            res[t] = M.ops.timestep_norm_fwd(x, pc, pm, pv, gamma, beta, None, 1e-5, None)
+            name = _lib.last_kernel()
+        finally:
+            _lib.set_option(2, 0)
+        assert "tsn_ema_mma" in name and ("segmented runs=4" in name) == (t == 84), name
+    ref = O.timestep_norm(x.float().cpu(), pc.cpu(), pm.cpu(), pv.cpu(), gamma.cpu(), beta.cpu(), None,
+                          acc_dtype=torch.float64)
+    assert rel_l2(res[84][0].float(), ref[0]) < 1e-2
+    assert torch.equal(res[84][1].cpu(), ref[1])
+    assert rel_l2(res[84][2], ref[2]) < 1e-5 and rel_l2(res[84][3], ref[3]) < 1e-3
+    for a, b in zip(res[84], res[8]):
+        assert torch.equal(a, b)
+    assert _lib.device_error() == 0
+
+
 def test_segmented_form_falls_back():
     """A number of steps that the runs do not divide takes the unsegmented kernel."""
     M, O = _mods()
