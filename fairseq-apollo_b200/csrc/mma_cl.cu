@@ -789,9 +789,8 @@ __global__ void __launch_bounds__(kCg * kWs * kWp * 32, 1)
       static_for<2>([&](auto h2_c) {
         constexpr int h2 = decltype(h2_c)::value;
         constexpr int e = 2 * pp + h2;
-        const int ch = cbase + e;
         float xf[8];
-        float xpad[(kMask && !kNorm) ? 8 : 1];   // the input at padded positions, 0 elsewhere
+        [[maybe_unused]] float xpad[(kMask && !kNorm) ? 8 : 1];   // the input at padded positions, 0 elsewhere
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint32_t w32 = odd ? v[j ^ 1][pp] : v[j][pp];
