@@ -21,6 +21,10 @@ LIB = os.path.join(PKG, "libmega_b200.so")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v"]
+# Per-file additions.  The step loop of the segmented tensor-core forms lives at the register limit; with ptxas'
+# most aggressive register usage level it runs 2.7 % faster (5.28 -> 5.14 ms on B=64, L=32768, D=2048), while the
+# other forms of the same kernel are 3 % slower with it, hence a translation unit of their own.
+FILE_FLAGS = {"mma_cl_seg.cu": ["-Xptxas", "--register-usage-level=10"]}
 
 
 def nvcc():
@@ -50,7 +54,8 @@ def build(force=False, verbose=False):
     for src in sources():
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = [cc, "-c", src, "-o", obj, "-I", os.path.join(ROOT, "include"), "-I", CSRC] + ARCH + NVCC_FLAGS
+        cmd = [cc, "-c", src, "-o", obj, "-I", os.path.join(ROOT, "include"), "-I", CSRC] + ARCH + NVCC_FLAGS + \
+            FILE_FLAGS.get(os.path.basename(src), [])
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     log = []
     for src, p in procs:

@@ -48,6 +48,10 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
 // (nothing launched) when the call is outside its envelope or its scratch.
 bool mma_cl_runs(int dtype, const void* x, void* y, long long xsb, long long xsl, long long xsd, long long ysb,
                  long long ysl, long long ysd, const StreamArgs& a, int runs, cudaStream_t s);
+// (mma_cl_seg.cu) the segmented form of the tensor-core kernel in n_seg runs, or false (nothing launched)
+bool mma_cl_segmented(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb, long long ysl,
+                      bool norm, const StreamArgs& a, int n_seg, cudaStream_t s);
+cudaError_t mma_cl_seg_read_device_error(int* v, bool reset);
 cudaError_t mma_cl_read_device_error(int* v, bool reset);
 
 }  // namespace mega
