@@ -41,14 +41,20 @@ def timestep_norm_ema(norm: TimestepNorm, move: MultiHeadEMA, x: Tensor,
             and (not move.complex or move.ndim in (2, 4, 8, 16, 32))):
         return _decode_step(norm, move, x, incremental_state, activation, return_normed)
     prev_count, prev_mean, prev_var, nstate = norm.initial_statistics(x.size(0), incremental_state)
-    p, q, g = move.coeffs()
+    if move.complex:
+        p, q, g = move.coeffs()
+        p, q, gamma_eff, beta, omega = p.squeeze(-1), q.squeeze(-1), norm.weight.detach().float() + 1.0, norm.bias, move.omega
+    else:
+        # inference: coefficients and the effective scale come from the cache that the single-token step
+        # uses too (rebuilt when a parameter's version counter moves), not from a kernel launch per call
+        gamma_eff, beta, p, q, g, omega = _fp32_params(norm, move)
     h_in = None
     estate = None
     if incremental_state is not None:
         estate = move._get_input_buffer(incremental_state)
         h_in = estate.get('prev_state')
-    res = ops.tsn_ema_forward(x, prev_count, prev_mean, prev_var, norm.weight.detach().float() + 1.0, norm.bias,
-                              norm.eps, p.squeeze(-1), q.squeeze(-1), g, move.omega, padding_mask, h_in,
+    res = ops.tsn_ema_forward(x, prev_count, prev_mean, prev_var, gamma_eff, beta,
+                              norm.eps, p, q, g, omega, padding_mask, h_in,
                               want_state=incremental_state is not None, silu=activation == 'silu',
                               want_normed=return_normed, complex_poles=move.complex)
     norm.store_statistics(incremental_state, nstate, res["count"], res["mean"], res["var"])
