@@ -23,7 +23,7 @@ struct StreamArgs {
   long long wait_limit;  // SM cycles after which a bounded wait gives up
   int withhold_step;     // test aid: step whose tile is never loaded, or -1
   long long count_offset;  // added to prev_count (a call that continues another call's positions)
-  // segmented form of the tensor-core path (mma_cl.cu): the sequence is cut into n_seg runs of seg_steps
+  // segmented form of the tensor-core path (mma_cl_seg.cu): the sequence is cut into n_seg runs of seg_steps
   // steps; a work item is (run, tile of channels, group of sequences), taken from sched[0] in order
   int n_seg, seg_steps, n_items, tiles_d;
   float* handoff_h;  // pole states between the runs of a strip, laid out like h_out
