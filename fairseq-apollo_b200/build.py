@@ -24,7 +24,9 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
 # Per-file additions.  The step loop of the segmented tensor-core forms lives at the register limit; with ptxas'
 # most aggressive register usage level it runs 2.7 % faster (5.28 -> 5.14 ms on B=64, L=32768, D=2048), while the
 # other forms of the same kernel are 3 % slower with it, hence a translation unit of their own.
-FILE_FLAGS = {"mma_cl_seg.cu": ["-Xptxas", "--register-usage-level=10"]}
+# The forms with narrow tiles (mma_cl_narrow.cu) gain ~2 % from a low level instead (shards of 8 and 16 sequences).
+FILE_FLAGS = {"mma_cl_seg.cu": ["-Xptxas", "--register-usage-level=10"],
+              "mma_cl_narrow.cu": ["-Xptxas", "--register-usage-level=2"]}
 
 
 def nvcc():

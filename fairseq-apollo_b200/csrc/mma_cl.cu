@@ -1,6 +1,7 @@
 // Dispatch of the tensor-core kernel (mma_cl_kernel.cuh): which form of it a call takes.  The
 // segmented forms are launched from mma_cl_seg.cu, a translation unit of its own because the register
-// allocation that suits their step loop (ptxas --register-usage-level) does not suit the others.
+// allocation that suits their step loop (ptxas --register-usage-level) does not suit the others; for the
+// same reason the forms with tiles narrower than 56 channels are launched from mma_cl_narrow.cu.
 #include "mma_cl_kernel.cuh"
 
 namespace mega {
@@ -99,43 +100,26 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
     else if (norm) tile = 22;  // 16 channels, two warps per column: twice the strips, half as long a step
     else tile = ctas(32) >= 111 ? 4 : 2;
   }
-  if (a_in.cplx) {
-    // complex poles (fused TimestepNorm -> MultiHeadComplexEMA): the matrices of a channel take
-    // 2.4 KB, so the 16-channel tile with two warps per column (three CTAs per SM) serves all sizes
-    if (!ema) return false;
-    if (!norm)  // the complex layer alone
-      return a_in.silu ? launch_variant<false, 2, true, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-                       : launch_variant<false, 2, false, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
-    if (want_xn)
-      return a_in.silu ? launch_variant<true, 2, true, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
-                       : launch_variant<true, 2, false, 2, true, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
-    return a_in.silu ? launch_variant<true, 2, true, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-                     : launch_variant<true, 2, false, 2, false, true, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
-  }
-  if (masked) {
-    // masked forms: 56-channel tile for large problems, the 16-channel two-warp tile otherwise
-    tile = (tile == 7 || tile == 8) ? 7 : 22;
-#define MEGA_MASKED(SILU, XN, EMA)                                                                                  \
-  (tile == 7 ? launch_variant<true, 7, SILU, 1, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, \
-                                                                         ysb, ysl)                                   \
-             : launch_variant<true, 2, SILU, 2, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, \
-                                                                         ysb, ysl))
-    if (!norm) {  // the EMA alone
-#define MEGA_MASKED_EMA(SILU)                                                                                          \
-  (tile == 7 ? launch_variant<false, 7, SILU, 1, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-             : launch_variant<false, 2, SILU, 2, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
-      return a_in.silu ? MEGA_MASKED_EMA(true) : MEGA_MASKED_EMA(false);
-#undef MEGA_MASKED_EMA
-    }
+  // The tile code as the forms allow it; everything narrower than 56 channels (and the complex forms, which
+  // always run the 16-channel tile) is launched from mma_cl_narrow.cu.
+  if (masked || want_xn) tile = (tile == 7 || tile == 8) ? 7 : 22;
+  else if (!ema && (tile == 2 || tile == 4)) tile = 22;
+  if (a_in.cplx || !(tile == 7 || tile == 8 || tile == 71))
+    return mma_cl_narrow(tile, dtype, x, y, xn, xsb, xsl, ysb, ysl, norm, a_in, s);
+  if (masked) {  // 56-channel tile
+    if (!norm)  // the EMA alone
+      return a_in.silu ? launch_variant<false, 7, true, 1, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                       : launch_variant<false, 7, false, 1, false, true, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
+#define MEGA_MASKED(SILU, XN, EMA) \
+  launch_variant<true, 7, SILU, 1, XN, EMA, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
     if (!ema) return MEGA_MASKED(false, false, false);
     if (want_xn) return a_in.silu ? MEGA_MASKED(true, true, true) : MEGA_MASKED(false, true, true);
     return a_in.silu ? MEGA_MASKED(true, false, true) : MEGA_MASKED(false, false, true);
 #undef MEGA_MASKED
   }
   if (!ema) {
-    if (tile == 2 || tile == 4) tile = 22;
     // more than one wave of wide tiles: the segmented form, as for the fused pair
-    if ((tile == 7 || tile == 8) && !masked && a_in.B >= 4 && ctas(64) > 148 && g_options[OPT_MMA_TILE].load() == 0) {
+    if (a_in.B >= 4 && ctas(64) > 148 && g_options[OPT_MMA_TILE].load() == 0) {
       const int nsteps = (a_in.L + kStep - 1) / kStep;
       const double plain = (double)((ctas(tile == 7 ? 56 : 64) + 147) / 148);
       int best = 0;
@@ -150,31 +134,16 @@ bool mma_cl_try(int dtype, const void* x, void* y, void* xn, long long xsb, long
       }
       if (best != 0 && mma_cl_segmented(dtype, x, y, xsb, xsl, ysb, ysl, true, a_in, best, s)) return true;
     }
-    return tile == 22  ? launch_variant<true, 2, false, 2, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-           : tile == 7 ? launch_variant<true, 7, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
-                       : launch_variant<true, 8, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
+    return tile == 7 ? launch_variant<true, 7, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)
+                     : launch_variant<true, 8, false, 1, false, false>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s);
   }
-  if (want_xn) {
-    // with the second output: 56-channel tiles for large problems (the 64-channel tile has no
-    // room for the two extra buffers), the 16-channel two-warp tile otherwise
-    tile = (tile == 7 || tile == 8) ? 7 : 22;
-    if (tile == 7)
-      return a_in.silu ? launch_variant<true, 7, true, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
-                       : launch_variant<true, 7, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
-    return a_in.silu ? launch_variant<true, 2, true, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
-                     : launch_variant<true, 2, false, 2, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
-  }
+  if (want_xn)  // 56-channel tiles (the 64-channel tile has no room for the two extra buffers)
+    return a_in.silu ? launch_variant<true, 7, true, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl)
+                     : launch_variant<true, 7, false, 1, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s, xn, ysb, ysl);
 #define MEGA_MMA_VARIANT(NORM, SILU)                                                           \
   (tile == 71 ? launch_variant<NORM, 7, SILU, 1, false, true, false, 1, false, true>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-   : tile == 222 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-   : tile == 224 ? launch_variant<NORM, 2, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-   : tile == 422 ? launch_variant<NORM, 4, SILU, 2, false, true, false, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-   : tile == 124 ? launch_variant<NORM, 1, SILU, 2, false, true, false, 4>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s) \
-   : tile == 22  ? launch_variant<NORM, 2, SILU, 2>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)     \
    : tile == 7 ? launch_variant<NORM, 7, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
-   : tile == 8 ? launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
-   : tile == 4 ? launch_variant<NORM, 4, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s)        \
-               : launch_variant<NORM, 2, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
+               : launch_variant<NORM, 8, SILU>(dtype, x, y, xsb, xsl, ysb, ysl, a_in, s))
   if (norm) return a_in.silu ? MEGA_MMA_VARIANT(true, true) : MEGA_MMA_VARIANT(true, false);
   return a_in.silu ? MEGA_MMA_VARIANT(false, true) : MEGA_MMA_VARIANT(false, false);
 #undef MEGA_MMA_VARIANT
@@ -184,6 +153,8 @@ cudaError_t mma_cl_read_device_error(int* v, bool reset) {
   int v2 = 0;
   cudaError_t e = read_device_error(v, reset);
   if (e == cudaSuccess) e = mma_cl_seg_read_device_error(&v2, reset);
+  if (e == cudaSuccess && *v == 0) *v = v2;
+  if (e == cudaSuccess) e = mma_cl_narrow_read_device_error(&v2, reset);
   if (e == cudaSuccess && *v == 0) *v = v2;
   return e;
 }

@@ -52,6 +52,10 @@ bool mma_cl_runs(int dtype, const void* x, void* y, long long xsb, long long xsl
 bool mma_cl_segmented(int dtype, const void* x, void* y, long long xsb, long long xsl, long long ysb, long long ysl,
                       bool norm, const StreamArgs& a, int n_seg, cudaStream_t s);
 cudaError_t mma_cl_seg_read_device_error(int* v, bool reset);
+// (mma_cl_narrow.cu) launches of the forms with tiles narrower than 56 channels and of the complex forms
+bool mma_cl_narrow(int tile, int dtype, const void* x, void* y, void* xn, long long xsb, long long xsl, long long ysb,
+                   long long ysl, bool norm, const StreamArgs& a, cudaStream_t s);
+cudaError_t mma_cl_narrow_read_device_error(int* v, bool reset);
 cudaError_t mma_cl_read_device_error(int* v, bool reset);
 
 }  // namespace mega
