@@ -19,7 +19,11 @@
  *     "length last" and the (B, L, D) "channel last" memory orders (and the
  *     time-major (L, B, D) order) are views of the same entry points.
  *   - Padding masks are uint8 (B, L) contiguous, non-zero = padded position.
- *   - Re-entrant: no global state except a launch counter.
+ *   - Re-entrant: no global state except a launch counter, the test switches of
+ *     mega_set_option and, for the fused TimestepNorm -> EMA / EMA / TimestepNorm
+ *     calls on large bf16 problems, fixed scratch arrays in device memory (owned by
+ *     the library, never allocated or freed by a call): such calls on different
+ *     streams are ordered against one another by an event, on the device.
  *
  * "Replaces" comments cite the reference interface each entry point stands in
  * for, as file:line within the fairseq-apollo checkout.
