@@ -474,6 +474,41 @@ def test_segmented_form_timestep_norm_alone():
     assert _lib.device_error() == 0
 
 
+def test_segmented_form_calls_on_two_streams():
+    """Two calls that take the segmented form by themselves (more than 148 wide tiles) on two streams
+    without any synchronisation between them: the library orders the second behind the first on the
+    device (they share its scratch), and each gives the bits it gives alone."""
+    M, O = _mods()
+    from fairseq_apollo_b200 import _lib
+    free, _ = torch.cuda.mem_get_info()
+    if free < 12 * 2 ** 30:
+        pytest.skip("needs ~6 GiB of device memory")
+    gen = torch.Generator().manual_seed(79)
+    bsz, length, dim = 16, 8192, 5120
+    prm = [t.cuda() for t in make_ema_params(gen, dim, 16)]
+    p, q, g = M.ops.ema_coeffs(*prm[:4])
+    pc = torch.full((bsz,), 2, dtype=torch.int64).cuda()
+    pm, pv = torch.zeros(bsz, dim).cuda(), torch.ones(bsz, dim).cuda()
+    gamma, beta = torch.ones(dim).cuda(), torch.zeros(dim).cuda()
+    xs = [torch.randn(bsz, length, dim, device="cuda", dtype=torch.bfloat16) * (1.0 + 0.5 * k) for k in range(2)]
+    alone = []
+    for x in xs:
+        alone.append(M.ops.tsn_ema_forward(x, pc, pm, pv, gamma, beta, 1e-5, p, q, g, prm[4])["y"])
+        assert "segmented" in _lib.last_kernel(), _lib.last_kernel()
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = []
+    for x, st in zip(xs, streams):
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            outs.append(M.ops.tsn_ema_forward(x, pc, pm, pv, gamma, beta, 1e-5, p, q, g, prm[4])["y"])
+    for st in streams:
+        st.synchronize()
+    for y, y0 in zip(outs, alone):
+        assert torch.equal(y, y0)
+    assert _lib.device_error() == 0
+
+
 def test_segmented_form_falls_back():
     """A number of steps that the runs do not divide takes the unsegmented kernel."""
     M, O = _mods()
