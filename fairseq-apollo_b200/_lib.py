@@ -41,6 +41,7 @@ SIGNATURES = {
     "mega_gate_mul_silu": [c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_output": [c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_p],
     "mega_gate_qk": [c_p, c_l, c_p, c_p, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_d, c_p],
+    "mega_gate_qk_rotary": [c_p, c_l, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_l, c_p, c_l, c_i, c_l, c_i, c_d, c_p],
     "mega_timestep_norm_fwd_train": [c_p, c_p, c_i, c_i, c_i, c_i, c_l, c_l, c_l, c_l, c_l, c_l, c_p, c_p, c_p,
                                      c_p, c_p, c_p, c_i, c_d, c_p, c_p, c_p, c_p, c_p, c_p, c_p],
     "mega_timestep_norm_bwd": [c_p, c_p, c_p, c_i, c_i, c_i, c_i] + [c_l] * 9 + [c_p] * 9 + [c_i] + [c_p] * 5,

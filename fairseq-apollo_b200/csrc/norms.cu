@@ -412,6 +412,45 @@ __global__ void gate_qk_kernel(const T* z, long long ldz, const float* gamma, co
   }
 }
 
+// The same with the rotary position embedding of the block applied to both results (pairs of
+// features (2j, 2j + 1) of row r rotated by the angle of position r % period and frequency j;
+// rot (positions, cols / 2, 2) holds (cos, sin)): a lane owns whole pairs, the rotation runs in fp32
+// on the unrounded affine results.
+template <typename T>
+__global__ void gate_qk_rotary_kernel(const T* z, long long ldz, const float* gamma, const float* beta,
+                                      const float* rot, int period, int q_offset, T* qo, long long ldq, T* ko,
+                                      long long ldk, long long rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int half = cols >> 1;
+  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = (((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+    const T* zr = z + r * ldz;
+    float ss = 0.f;
+    for (int j = lane; j < half; j += 32) {
+      const float a = Elem<T>::ld(zr + 2 * j), b = Elem<T>::ld(zr + 2 * j + 1);
+      ss = fmaf(a, a, fmaf(b, b, ss));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.f / fmaxf(sqrtf(ss), eps);
+    const int pos = (int)(r % period);
+    const float2* rk = reinterpret_cast<const float2*>(rot) + (size_t)pos * half;
+    const float2* rq = reinterpret_cast<const float2*>(rot) + (size_t)(pos + q_offset) * half;
+    for (int j = lane; j < half; j += 32) {
+      const int c = 2 * j;
+      const float a = Elem<T>::ld(zr + c) * inv, b = Elem<T>::ld(zr + c + 1) * inv;
+      const float qa = fmaf(a, gamma[c] + 1.f, beta[c]), qb = fmaf(b, gamma[c + 1] + 1.f, beta[c + 1]);
+      const float ka = fmaf(a, gamma[cols + c] + 1.f, beta[cols + c]);
+      const float kb = fmaf(b, gamma[cols + c + 1] + 1.f, beta[cols + c + 1]);
+      const float2 wq = __ldg(rq + j), wk = __ldg(rk + j);
+      Elem<T>::st(qo + r * ldq + c, qa * wq.x - qb * wq.y);
+      Elem<T>::st(qo + r * ldq + c + 1, qa * wq.y + qb * wq.x);
+      Elem<T>::st(ko + r * ldk + c, ka * wk.x - kb * wk.y);
+      Elem<T>::st(ko + r * ldk + c + 1, ka * wk.y + kb * wk.x);
+    }
+  }
+}
+
 }  // namespace mega
 
 using namespace mega;
@@ -620,4 +659,21 @@ extern "C" int mega_gate_qk(const void* z, int64_t ld_z, const float* gamma, con
                                     beta, (T*)q, (long long)ld_q, (T*)k, (long long)ld_k, (long long)rows, cols,
                                     (float)eps));
   return check_launch("gate_qk");
+}
+
+extern "C" int mega_gate_qk_rotary(const void* z, int64_t ld_z, const float* gamma, const float* beta, const float* rot,
+                                   int positions, int period, int q_offset, void* q, int64_t ld_q, void* k,
+                                   int64_t ld_k, int dtype, int64_t rows, int cols, double eps, mega_stream_t stream) {
+  if (!z || !gamma || !beta || !rot || !q || !k) return MEGA_ERR_NULL;
+  if (!valid_dtype(dtype)) return MEGA_ERR_DTYPE;
+  if (rows <= 0 || cols <= 0 || (cols & 1) || period <= 0 || q_offset < 0 || period + q_offset > positions)
+    return MEGA_ERR_SHAPE;
+  if (ld_z < cols || ld_q < cols || ld_k < cols) return MEGA_ERR_STRIDE;
+  if (!aligned_to(rot, 8)) return MEGA_ERR_ALIGN;
+  const long long blocks = (rows + 7) / 8;  // 8 warps per block, one row per warp and pass
+  const unsigned grid = (unsigned)(blocks > 148 * 8 ? 148 * 8 : blocks);
+  MEGA_DISPATCH_DTYPE(dtype, launch(gate_qk_rotary_kernel<T>, grid, 256, 0, stream, (const T*)z, (long long)ld_z, gamma,
+                                    beta, rot, period, q_offset, (T*)q, (long long)ld_q, (T*)k, (long long)ld_k,
+                                    (long long)rows, cols, (float)eps));
+  return check_launch("gate_qk_rotary");
 }

@@ -275,9 +275,18 @@ class MovingAverageGatedAttention(IncrementalStateMixin, nn.Module):
         base = self.mx_proj(mx)
         D, S, E = self.embed_dim, self.zdim, self.hdim
         u, z, r, hx = base[..., :D], base[..., D:D + S], base[..., D + S:D + S + E], base[..., D + S + E:]
+        # rotary positions in the same kernel as the query / key affine: the plain (non-incremental) call of the
+        # efficient-attention branch, where row (b, t) sits at position t % period of its chunk
+        period = self.chunk_size if 1 < self.chunk_size < seq_len else seq_len
+        fused_rotary = (fused_elementwise and self.efficient_attn is not None and saved_state is None
+                        and isinstance(self.rel_pos_bias, RotaryEmbedding) and seq_len % period == 0
+                        and period <= self.rel_pos_bias.max_positions)
         if fused_elementwise:
             v = ops.gate_silu(v_lin)
-            q, k = ops.gate_qk(z, self.gamma, self.beta, eps=1e-5)
+            if fused_rotary:
+                q, k = ops.gate_qk_rotary(z, self.gamma, self.beta, self.rel_pos_bias._angles(0, period), period)
+            else:
+                q, k = ops.gate_qk(z, self.gamma, self.beta, eps=1e-5)
         else:
             v = F.silu(v_lin)
             zn = F.normalize(z, p=2, dim=-1, eps=1e-5)
@@ -318,8 +327,11 @@ class MovingAverageGatedAttention(IncrementalStateMixin, nn.Module):
         attn_weights = None
         if self.efficient_attn is not None:
             assert isinstance(self.rel_pos_bias, RotaryEmbedding)
-            qidx = k.size(1) - 1 if k.size(1) != q.size(1) else 0
-            qr, kr = self.rel_pos_bias(q, k, qidx=qidx)
+            if fused_rotary:
+                qr, kr = q, k
+            else:
+                qidx = k.size(1) - 1 if k.size(1) != q.size(1) else 0
+                qr, kr = self.rel_pos_bias(q, k, qidx=qidx)
             attn = self.efficient_attn(qr.to(v.dtype), kr.to(v.dtype), v).view(bsz, seq_len, E)
         else:
             if self.attention_activation == 'softmax':

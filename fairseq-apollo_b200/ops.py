@@ -397,6 +397,31 @@ def gate_qk(z, gamma, beta, eps=1e-5):
     return q, k
 
 
+def gate_qk_rotary(z, gamma, beta, rot, period, q_offset=0, eps=1e-5):
+    """gate_qk with the block's rotary embedding applied to both results in the same kernel.
+    rot: complex64 (positions, S / 2) unit phasors (the table RotaryEmbedding keeps) or their float32
+    (positions, S / 2, 2) view; row r of the flattened z is position r % period (+ q_offset for the query).
+    Returns (q, k) in z's dtype."""
+    _cuda(z, gamma, beta, rot)
+    z_, rows, cols, ldz = _rows(z)
+    g = gamma.detach().to(torch.float32).contiguous()
+    b = beta.detach().to(torch.float32).contiguous()
+    if g.shape != (2, cols) or b.shape != (2, cols):
+        raise ValueError("gate_qk_rotary: gamma and beta must be (2, %d)" % cols)
+    r = torch.view_as_real(rot) if rot.is_complex() else rot
+    r = r.to(torch.float32).contiguous()
+    if r.dim() != 3 or r.shape[1] * 2 != cols or r.shape[2] != 2:
+        raise ValueError("gate_qk_rotary: rot must be (positions, %d) complex or (positions, %d, 2) float" % (cols // 2, cols // 2))
+    q = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    k = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    with torch.cuda.device(z.device):
+        _lib.check(_lib.lib().mega_gate_qk_rotary(z_.data_ptr(), ldz, g.data_ptr(), b.data_ptr(), r.data_ptr(),
+                                                  r.shape[0], int(period), int(q_offset), q.data_ptr(), cols,
+                                                  k.data_ptr(), cols, _dt(z), rows, cols, float(eps), _stream()),
+                   "gate_qk_rotary")
+    return q, k
+
+
 # ------------------------------------------------------------------------ training
 def _like(x):
     return torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) \

@@ -290,6 +290,18 @@ MEGA_API int mega_gate_output(const void* residual, int64_t ld_res, const void* 
 MEGA_API int mega_gate_qk(const void* z, int64_t ld_z, const float* gamma, const float* beta, void* q,
                  int64_t ld_q, void* k, int64_t ld_k, int dtype, int64_t rows, int cols, double eps,
                  mega_stream_t stream);
+/*
+ * mega_gate_qk followed by the block's rotary position embedding on both results
+ * (fairseq/modules/relative_positional_bias.py:47-97 as MovingAverageGatedAttention applies it,
+ * moving_average_gated_attention.py:217-221): the pair of features (2j, 2j + 1) of row r is rotated by
+ * the angle of position (r % period) [+ q_offset for the query] and frequency j.  rot: fp32
+ * (positions, cols / 2, 2) = (cos, sin) of those angles, 8-byte aligned; period + q_offset <= positions;
+ * cols even.  The rotation runs in fp32 on the unrounded affine results; q, k come back in `dtype`.
+ */
+MEGA_API int mega_gate_qk_rotary(const void* z, int64_t ld_z, const float* gamma, const float* beta,
+                        const float* rot, int positions, int period, int q_offset,
+                        void* q, int64_t ld_q, void* k, int64_t ld_k,
+                        int dtype, int64_t rows, int cols, double eps, mega_stream_t stream);
 
 /*
  * ---- Training: forward with saved statistics, and backward ---------------------------------

@@ -131,3 +131,54 @@ def test_reference_nffn_on_gpu():
     with torch.no_grad():
         y = ff.cuda()(g["x"].cuda())
     assert rel_l2(y, g["y"]) < 1e-5
+
+
+def _own_block(g, **kw):
+    """This package's own block class, built with the fixture's arguments and loaded (strict) with the state
+    dict of the block the reference built."""
+    import fairseq_apollo_b200 as M
+    dim, zdim, hdim, ndim, chunk, groups = [int(v) for v in g["dims"]]
+    args = dict(chunk_size=chunk, moving_layer='cema', moving_act='silu', norm_num_groups=groups,
+                rel_pos_bias='rotary', efficient_attn=False)
+    args.update(kw)
+    blk = M.MovingAverageGatedAttention(dim, zdim, hdim, ndim, **args).eval()
+    blk.load_state_dict(_state_dict(g), strict=True)
+    return blk.cuda(), chunk
+
+
+@pytest.mark.parametrize("efficient", [False, True])
+def test_own_block_class_matches_reference_outputs(efficient):
+    """The package's MovingAverageGatedAttention (fused norm -> EMA -> SiLU, gates, and for the efficient
+    branch the rotary embedding inside the query / key kernel) against the outputs of the reference block
+    on CPU: fp32 to 1e-4, the block cast to bf16 to 2e-2; token-by-token continuation equals the full call."""
+    M, _ = _block_module()   # (skips when the reference sources are not staged, like the tests above)
+    g = golden("mega_block_causal")
+    blk, chunk = _own_block(g, efficient_attn=efficient)
+    x = g["x"].cuda()
+    with torch.no_grad():
+        if efficient:
+            y, _ = blk(x)
+        else:
+            y, _ = blk(x, attn_mask=_causal_mask(chunk, x.device, x.dtype))
+    assert rel_l2(y, g["y"]) < 1e-4
+    blk_h = _own_block(g, efficient_attn=True)[0].bfloat16()
+    with torch.no_grad():
+        y_h, _ = blk_h(x.bfloat16())
+    assert rel_l2(y_h.float(), g["y"]) < 2e-2
+    if efficient:
+        with torch.no_grad():
+            st = {}
+            outs = [blk(x[:, i:i + chunk], incremental_state=st)[0] for i in range(0, 2 * chunk, chunk)]
+            outs += [blk(x[:, i:i + 1].contiguous(), incremental_state=st)[0] for i in range(2 * chunk, x.size(1))]
+        assert rel_l2(torch.cat(outs, 1), y) < 1e-4
+
+
+def test_own_block_class_with_padding():
+    M, _ = _block_module()
+    g = golden("mega_block_causal_padded")
+    blk, chunk = _own_block(g)
+    x, mask = g["x"].cuda(), g["mask"].bool().cuda()
+    with torch.no_grad():
+        y, _ = blk(x, padding_mask=mask, attn_mask=_causal_mask(chunk, x.device, x.dtype))
+    keep = ~mask
+    assert rel_l2(y[keep], g["y"].cuda()[keep]) < 1e-4

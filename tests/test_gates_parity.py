@@ -71,3 +71,34 @@ def test_gate_qk_zero_row():
     b = torch.arange(32, dtype=torch.float32, device="cuda").view(2, 16)
     q, k = M.ops.gate_qk(z, g, b)
     assert torch.equal(q, b[0].expand(3, 16)) and torch.equal(k, b[1].expand(3, 16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gate_qk_rotary(dtype):
+    """gate_qk with the rotary embedding in the same kernel against gate_qk's definition followed by the
+    complex multiplication the reference's RotaryEmbedding performs, on a column slice, with chunks of 16
+    positions and a query offset."""
+    import fairseq_apollo_b200 as M
+    gen = torch.Generator().manual_seed(11)
+    bsz, length, S, period = 3, 48, 64, 16
+    base = torch.randn(bsz, length, S + 40, generator=gen).to(dtype).cuda()
+    z = base[..., 8:8 + S]
+    gamma = (torch.randn(2, S, generator=gen) * 0.2).cuda()
+    beta = (torch.randn(2, S, generator=gen) * 0.2).cuda()
+    t = torch.arange(40, dtype=torch.float32)
+    freqs = 1.0 / torch.tensor([10000 ** (j / S) for j in range(0, S, 2)], dtype=torch.float32)
+    ang = torch.outer(t, freqs)
+    table = torch.polar(torch.ones_like(ang), ang).cuda()
+    for q_offset in (0, 5):
+        q, k = M.ops.gate_qk_rotary(z, gamma, beta, table, period, q_offset)
+        zn = torch.nn.functional.normalize(z.float(), p=2, dim=-1, eps=1e-5)
+        q0 = zn * (gamma[0] + 1) + beta[0]
+        k0 = zn * (gamma[1] + 1) + beta[1]
+        pos = torch.arange(length, device="cuda") % period
+
+        def rot(x, p):
+            xc = torch.view_as_complex(x.reshape(bsz, length, S // 2, 2).contiguous())
+            return torch.view_as_real(xc * table[p]).flatten(2)
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert rel_l2(q.float(), rot(q0, pos + q_offset)) < tol
+        assert rel_l2(k.float(), rot(k0, pos)) < tol
